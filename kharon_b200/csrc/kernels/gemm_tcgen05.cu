@@ -1,0 +1,459 @@
+// bf16 GEMM family on the 5th-generation tensor cores (sm_100a).
+//
+//   C[M,N] (+)= op(A) * op(B)          fp32 accumulation in TMEM
+//
+// A is either K-major ([M,K] row-major) or M-major ([K,M] row-major); B is either K-major
+// ([N,K] row-major, i.e. an nn.Linear weight) or N-major ([K,N] row-major).  That covers
+// the three products of a linear layer without any transposed copies:
+//   forward        Y  = X  * W^T      A K-major,  B K-major     (reference mm_nt_bf16o, kernels.cu:34-39)
+//   input grad     dX = dY * W        A K-major,  B N-major     (reference mm_nn_bf16o, kernels.cu:55-60)
+//   weight grad    dW = dY^T * X      A M-major,  B N-major     (reference mm_tn_bf16[_acc], kernels.cu:41-53)
+//
+// Structure: persistent CTAs (one per SM), 6 warps.  Warp 0 streams operand tiles with TMA
+// into a ring of 128-byte-swizzled shared-memory stages; one lane of warp 1 issues
+// tcgen05.mma (128 x BN x 16 per instruction) into one of two TMEM accumulator buffers and
+// commits stage-release / accumulator-ready mbarriers; warps 2-5 drain the other
+// accumulator with tcgen05.ld and run the fused epilogue, so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// Fused epilogues replace the reference's separate elementwise kernels
+// (add_bias_k kernels.cu:174, bias_gelu_k :292, bias_residual_k :274, gelu_bwd_k :431,
+// add_k :262) and the beta=1 weight-gradient accumulation.
+//
+// Every mbarrier wait is bounded: on expiry the CTA stores a code in the library error word,
+// all roles unwind, TMEM is released and the kernel returns.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "common.cuh"
+
+__device__ int g_kh_error_word = 0;
+int* kh_error_word_dev() {
+  static int* ptr[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kh_error_word) == cudaSuccess) ptr[dev] = (int*)p;
+  }
+  return ptr[dev];
+}
+
+// ------------------------------------------------------------------------------- host util
+static thread_local std::string g_host_err;
+void kh_set_error(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_host_err = buf;
+}
+extern "C" const char* kh_cuda_last_error() { return g_host_err.c_str(); }
+extern "C" int kh_cuda_error_word(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_kh_error_word, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_kh_error_word, &z, sizeof(int));
+  }
+  return v;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct TmapKey {
+  uint64_t base, rows, cols, ld;
+  uint32_t br, bc;
+  bool operator==(const TmapKey& o) const { return memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x632BE59BD9B4E019ull) + (h << 6) + (h >> 2);
+    h ^= (k.cols * 31 + k.ld) + (h << 6) + (h >> 2);
+    h ^= ((uint64_t)k.br << 32 | k.bc) + (h << 6) + (h >> 2);
+    return (size_t)h;
+  }
+};
+const CUtensorMap* kh_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                                   uint32_t box_rows, uint32_t box_cols) {
+  static std::unordered_map<TmapKey, CUtensorMap*, TmapHash> cache;
+  static std::mutex mu;
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = (uint64_t)base; key.rows = rows; key.cols = cols; key.ld = ld; key.br = box_rows; key.bc = box_cols;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { kh_set_error("cuTensorMapEncodeTiled is not available from the driver"); return nullptr; }
+  if (((uint64_t)base & 15) || ((ld * 2) & 15)) {
+    kh_set_error("TMA operand needs a 16-byte aligned base and row pitch (base %p, ld %llu elements)", base,
+                 (unsigned long long)ld);
+    return nullptr;
+  }
+  CUtensorMap* m = new CUtensorMap;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    delete m;
+    kh_set_error("cuTensorMapEncodeTiled failed with %d (rows %llu cols %llu ld %llu box %ux%u)", (int)rc,
+                 (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_rows, box_cols);
+    return nullptr;
+  }
+  if (cache.size() > 4096) {   // buffers come from long-lived arenas; this only bounds pathological churn
+    for (auto& kv : cache) delete kv.second;
+    cache.clear();
+  }
+  cache[key] = m;
+  return m;
+}
+
+// ------------------------------------------------------------------------------- kernel
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_BIAS_RESID = 3, EPI_DGELU = 4, EPI_RESID = 5 };
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;          // operand majors (0 = K-major, 1 = M/N-major)
+  void* C; int ldc;        // output, bf16 or fp32
+  int out_fp32, accumulate;
+  int epi;
+  const bf16* bias;        // [N]
+  bf16* aux; int ldaux;    // EPI_BIAS_GELU: pre-activation out; EPI_BIAS_RESID/EPI_RESID: residual in; EPI_DGELU: pre-activation in
+  float alpha;             // scales the accumulator before the epilogue
+  int* err;                // library error word
+};
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN> struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + Cfg::STAGES * Cfg::STAGE_BYTES);
+  // bars: full[STAGES], empty[STAGES], tfull[2], tempty[2], then tmem base word + abort flag
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * Cfg::STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * Cfg::STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tma_a); tma_prefetch_desc(&tma_b); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile id -> (tm, tn): bands of 8 M-tiles, N fastest inside a band keeps both panels in L2
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int GROUP = 8;
+    int band = t / (GROUP * tiles_n);
+    int first = band * GROUP;
+    int gsz = min(GROUP, tiles_m - first);
+    int r = t - band * GROUP * tiles_n;
+    tm = first + r % gsz;
+    tn = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        int tm, tn;
+        tile_coord(t, tm, tn);
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
+          const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
+          if (!p.a_mn) tma_load_2d(sa, &tma_a, bar_full + 8 * s, kb * BK, tm * BM);
+          else
+            for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), &tma_a, bar_full + 8 * s, tm * BM + j * 64, kb * BK);
+          if (!p.b_mn) tma_load_2d(sb, &tma_b, bar_full + 8 * s, kb * BK, tn * BN);
+          else
+            for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * (BK * 128), &tma_b, bar_full + 8 * s, tn * BN + j * 64, kb * BK);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      // K-major: LBO unused (encoded 16 B), SBO 1024; MN-major: LBO = one 64-wide slab (BK rows x 128 B), SBO 1024
+      const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, b_lbo = p.b_mn ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      const uint32_t b_kstep = p.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1, abort_flag, 4, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1;
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, 1, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+          uint64_t adesc = umma_desc_sw128(sa, a_lbo, 1024);
+          uint64_t bdesc = umma_desc_sw128(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) {
+            umma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * s);   // stage reusable once these MMAs retire
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;                    // TMEM lane quadrant this warp may access
+    int tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+      int tm, tn;
+      tile_coord(t, tm, tn);
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = tn * BN + c0;
+        if (col >= p.N) break;                 // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]) * p.alpha;
+        const bool full = (col + 32 <= p.N);
+        if (p.epi == EPI_BIAS || p.epi == EPI_BIAS_GELU || p.epi == EPI_BIAS_RESID) {
+          if (full) {
+            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              uint4 b = __ldg(bp + j);
+              float2 f0 = unpack_bf16(b.x), f1 = unpack_bf16(b.y), f2 = unpack_bf16(b.z), f3 = unpack_bf16(b.w);
+              v[8 * j + 0] += f0.x; v[8 * j + 1] += f0.y; v[8 * j + 2] += f1.x; v[8 * j + 3] += f1.y;
+              v[8 * j + 4] += f2.x; v[8 * j + 5] += f2.y; v[8 * j + 6] += f3.x; v[8 * j + 7] += f3.y;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++) if (col + i < p.N) v[i] += __bfloat162float(p.bias[col + i]);
+          }
+        }
+        if (row_ok) {
+          if (p.epi == EPI_BIAS_GELU) {
+            bf16* ap = p.aux + (size_t)row * p.ldaux + col;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                uint4 o;
+                o.x = pack_bf16(v[8 * j], v[8 * j + 1]); o.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+                o.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+                reinterpret_cast<uint4*>(ap)[j] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; i++) if (col + i < p.N) ap[i] = __float2bfloat16(v[i]);
+            }
+            // the stored pre-activation is bf16; apply GELU to the rounded value so that the
+            // backward pass (which only sees the bf16 copy) differentiates the same function
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+          } else if (p.epi == EPI_BIAS_RESID || p.epi == EPI_RESID || p.epi == EPI_DGELU) {
+            const bf16* ap = p.aux + (size_t)row * p.ldaux + col;
+            float x[32];
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                uint4 b = reinterpret_cast<const uint4*>(ap)[j];
+                float2 f0 = unpack_bf16(b.x), f1 = unpack_bf16(b.y), f2 = unpack_bf16(b.z), f3 = unpack_bf16(b.w);
+                x[8 * j + 0] = f0.x; x[8 * j + 1] = f0.y; x[8 * j + 2] = f1.x; x[8 * j + 3] = f1.y;
+                x[8 * j + 4] = f2.x; x[8 * j + 5] = f2.y; x[8 * j + 6] = f3.x; x[8 * j + 7] = f3.y;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i++) x[i] = (col + i < p.N) ? __bfloat162float(ap[i]) : 0.f;
+            }
+            if (p.epi == EPI_DGELU) {
+#pragma unroll
+              for (int i = 0; i < 32; i++) v[i] *= gelu_tanh_grad(x[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i++) v[i] += x[i];
+            }
+          }
+          if (p.out_fp32) {
+            float* cp = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                if (p.accumulate) {
+                  float4 old = reinterpret_cast<float4*>(cp)[j];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                reinterpret_cast<float4*>(cp)[j] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; i++)
+                if (col + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
+            }
+          } else {
+            bf16* cp = reinterpret_cast<bf16*>(p.C) + (size_t)row * p.ldc + col;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                uint4 o;
+                o.x = pack_bf16(v[8 * j], v[8 * j + 1]); o.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+                o.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+                reinterpret_cast<uint4*>(cp)[j] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; i++) if (col + i < p.N) cp[i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------- launcher
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParams& p, int max_ctas, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) { kh_set_error("gemm: cannot opt in to %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e)); return -1; }
+    attr_set = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  gemm_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(*ta, *tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { kh_set_error("gemm launch failed: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+// C[M,N] = alpha * op(A) op(B) with a fused epilogue.  lda/ldb/ldc/ldaux are row pitches in
+// elements of the row-major buffers described at the top of this file.  block_n = 0 lets the
+// launcher pick the tile width; max_ctas > 0 caps the grid (used to leave SMs to a
+// concurrently running communication kernel).  Returns 0 or -1 (see kh_cuda_last_error).
+extern "C" int kh_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
+                            int M, int N, int K, int out_fp32, int accumulate, int epi, const void* bias, void* aux,
+                            int ldaux, float alpha, int block_n, int max_ctas, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) { kh_set_error("gemm: empty problem %dx%dx%d", M, N, K); return -1; }
+  if (accumulate && !out_fp32) { kh_set_error("gemm: accumulate needs an fp32 output"); return -1; }
+  if ((ldc % (out_fp32 ? 4 : 8)) != 0 || ((uintptr_t)C & 15)) { kh_set_error("gemm: output pitch/base not 16-byte aligned (ldc %d)", ldc); return -1; }
+  if ((epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESID) && (!bias || ((uintptr_t)bias & 15))) { kh_set_error("gemm: bias missing or misaligned"); return -1; }
+  if ((epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESID || epi == EPI_DGELU || epi == EPI_RESID) && (!aux || (ldaux % 8) || ((uintptr_t)aux & 15))) { kh_set_error("gemm: aux operand missing or misaligned"); return -1; }
+  int bn = block_n;
+  if (bn == 0) {
+    const int tm = (M + BM - 1) / BM;
+    bn = 256;
+    if (N <= 64) bn = 64;
+    else if (N <= 128) bn = 128;
+    else if (tm * ((N + 255) / 256) < num_sms()) bn = (tm * ((N + 127) / 128) < num_sms()) ? 64 : 128;
+  }
+  if (bn != 64 && bn != 128 && bn != 256) { kh_set_error("gemm: block_n must be 64, 128 or 256"); return -1; }
+  const CUtensorMap* ta = a_mn ? kh_tmap_2d_bf16(A, K, M, lda, BK, 64) : kh_tmap_2d_bf16(A, M, K, lda, BM, BK);
+  if (!ta) return -1;
+  const CUtensorMap* tb = b_mn ? kh_tmap_2d_bf16(B, K, N, ldb, BK, 64) : kh_tmap_2d_bf16(B, N, K, ldb, bn, BK);
+  if (!tb) return -1;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.accumulate = accumulate; p.epi = epi; p.bias = (const bf16*)bias; p.aux = (bf16*)aux; p.ldaux = ldaux; p.alpha = alpha;
+  p.err = kh_error_word_dev();
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256>(ta, tb, p, max_ctas, st);
+  if (bn == 128) return launch_gemm<128>(ta, tb, p, max_ctas, st);
+  return launch_gemm<64>(ta, tb, p, max_ctas, st);
+}

@@ -1,0 +1,210 @@
+"""Operator layer: thin Python wrappers over the hand-written sm_100a kernels.
+
+Every function works in place on caller-supplied tensors (the model owns flat arenas and
+stashes, nothing here allocates on the hot path).  On CUDA tensors the native kernel runs
+on the current stream; a missing library is an error, never a fallback.  On CPU tensors
+the same operation is evaluated with PyTorch in fp32 (``reference.py``) -- that path is the
+numerical oracle of the GPU tests and what the CPU test tier exercises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native
+from . import reference as ref
+
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESID, EPI_DGELU, EPI_RESID = range(6)
+
+#: number of native kernel launches issued through this module (bench.py reports it)
+launch_count = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _lib():
+    return _native.cuda()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(rc, n=1):
+    global launch_count
+    if rc != 0:
+        raise KernelError(_lib().kh_cuda_last_error().decode())
+    launch_count += n
+
+
+def _p(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def error_word(reset: bool = True) -> int:
+    """Device-side status word: 0, or the code of the first bounded wait that ran out."""
+    return int(_lib().kh_cuda_error_word(1 if reset else 0))
+
+
+def check_device_status():
+    w = error_word()
+    if w != 0:
+        raise KernelError("a kernel gave up a bounded wait (code %d)" % w)
+
+
+# ----------------------------------------------------------------------------------- GEMM
+def gemm(a, b, out, *, a_mn=False, b_mn=False, accumulate=False, epi=EPI_NONE, bias=None, aux=None,
+         alpha=1.0, block_n=0, max_ctas=0):
+    """out[M,N] (+)= alpha * op(a) @ op(b) with a fused epilogue.
+
+    ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``); both
+    bf16, row-major, last dim contiguous.  ``out`` is bf16 or fp32 (``accumulate`` only fp32).
+    Epilogues: bias add; bias+GELU (``aux`` receives the pre-activation); bias+residual and
+    residual (``aux`` is the residual); dGELU (``out = acc * gelu'(aux)``).
+    """
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert (b.shape[0] if b_mn else b.shape[1]) == K, "gemm: inner dimensions differ"
+    assert out.shape[0] == M and out.shape[1] == N
+    if not a.is_cuda:
+        return ref.gemm(a, b, out, a_mn, b_mn, accumulate, epi, bias, aux, alpha)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+    _chk(_lib().kh_gemm_bf16(a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+                             out.data_ptr(), out.stride(0), M, N, K, int(out.dtype == torch.float32),
+                             int(accumulate), epi, _p(bias), _p(aux), aux.stride(0) if aux is not None else 0,
+                             float(alpha), block_n, max_ctas, _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------ embedding
+def embed_fwd(tok, pos, wte, wpe, out, T):
+    if not out.is_cuda:
+        return ref.embed_fwd(tok, pos, wte, wpe, out, T)
+    rows, d = out.shape
+    _chk(_lib().kh_embed_fwd(tok.data_ptr(), _p(pos), wte.data_ptr(), wpe.data_ptr(), out.data_ptr(), rows, d,
+                             wpe.shape[0] if pos is not None else T, wte.shape[0], _stream()))
+    return out
+
+
+def embed_bwd(tok, dx, dwte, dwpe, B, T):
+    """dwte[tok[r]] += dx[r]; dwpe[t] += sum_b dx[b, t] (fp32 grads, deterministic)."""
+    if not dx.is_cuda:
+        return ref.embed_bwd(tok, dx, dwte, dwpe, B, T)
+    d = dx.shape[1]
+    V = dwte.shape[0] if dwte is not None else 0
+    # the token table of one launch lives in shared memory: chunk long batches by sequences
+    max_rows = 48 * 1024
+    seq_per = max(1, max_rows // T)
+    for b0 in range(0, B, seq_per):
+        nb = min(seq_per, B - b0)
+        _chk(_lib().kh_embed_bwd(tok.data_ptr() + b0 * T * 4, dx.data_ptr() + b0 * T * d * 2, _p(dwte), _p(dwpe),
+                                 nb, T, d, V, _stream()), 2)
+
+
+def colsum(x, out, accumulate=True):
+    if not x.is_cuda:
+        return ref.colsum(x, out, accumulate)
+    _chk(_lib().kh_colsum(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], int(accumulate), _stream()))
+
+
+# ------------------------------------------------------------------------------ LayerNorm
+def layernorm_fwd(x, w, b, y, mean=None, rstd=None):
+    if not x.is_cuda:
+        return ref.layernorm_fwd(x, w, b, y, mean, rstd)
+    rows, d = x.shape
+    _chk(_lib().kh_layernorm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), _p(mean), _p(rstd), rows, d,
+                                 _stream()))
+    return y
+
+
+def layernorm_bwd_scratch_elems(rows, d):
+    """fp32 elements of the partial-sum scratch that ``layernorm_bwd`` needs."""
+    if not torch.cuda.is_available():
+        return 2 * d
+    return _lib().kh_layernorm_bwd_parts(rows, d) * 2 * d
+
+
+def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
+    """dx = LN'(dy) (+ dres); dw += ..., db += ... (fp32, deterministic two-stage reduction)."""
+    if not x.is_cuda:
+        return ref.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db)
+    rows, d = x.shape
+    assert partials.numel() >= layernorm_bwd_scratch_elems(rows, d)
+    _chk(_lib().kh_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                 _p(dres), dx.data_ptr(), dw.data_ptr(), db.data_ptr(), partials.data_ptr(), rows, d,
+                                 _stream()), 2)
+
+
+# -------------------------------------------------------------------------- cross-entropy
+def xent(logits, V, target, *, coef=None, uniform=1.0, rowloss=None, prob=None, write_grad=True):
+    """Fused softmax-cross-entropy over bf16 logits [R, ld]; optionally overwrites the logits
+    with ``scale_r * (softmax - onehot)`` (scale_r = coef[r] or ``uniform``)."""
+    if not logits.is_cuda:
+        return ref.xent(logits, V, target, coef, uniform, rowloss, prob, write_grad)
+    _chk(_lib().kh_xent(logits.data_ptr(), logits.stride(0), V, target.data_ptr(), _p(coef), float(uniform),
+                        _p(rowloss), _p(prob), int(write_grad), logits.shape[0], _stream()))
+
+
+def sum_f32(x, out, scale=1.0, accumulate=False):
+    if not x.is_cuda:
+        s = x.double().sum().float() * scale
+        out[0] = out[0] + s if accumulate else s
+        return
+    _chk(_lib().kh_sum_f32(x.data_ptr(), x.numel(), float(scale), out.data_ptr(), int(accumulate), _stream()))
+
+
+# ---------------------------------------------------------------------------------- AdamW
+def adamw(p, g, m, v, pb, *, lr, beta1, beta2, eps, wd, step, grad_scale=1.0, zero_grad=True):
+    """One fused pass: moments, decoupled decay on every element, fp32 master update, bf16
+    compute copy (``pb``, may be None) and gradient clear.  ``step`` is 1-based."""
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    if not p.is_cuda:
+        return ref.adamw(p, g, m, v, pb, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, zero_grad)
+    _chk(_lib().kh_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _p(pb), p.numel(), lr, beta1, beta2,
+                         eps, wd, bc1, bc2, grad_scale, int(zero_grad), _stream()))
+
+
+def cast_f32_bf16(x, y):
+    if not x.is_cuda:
+        y.copy_(x)
+        return
+    _chk(_lib().kh_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), _stream()))
+
+
+def add_bf16(a, b, c):
+    if not a.is_cuda:
+        c.copy_((a.float() + b.float()))
+        return
+    _chk(_lib().kh_add_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), a.numel(), _stream()))
+
+
+def flush_l2(buf):
+    """Overwrite ``buf`` (a CUDA tensor larger than L2) so the next kernel starts cold."""
+    _chk(_lib().kh_fill_u32(buf.data_ptr(), buf.numel() * buf.element_size() // 4, 0, _stream()))
+
+
+# ------------------------------------------------------------------------------ attention
+def flash_fwd(qkv, out, lse, B, T, H, hd):
+    """Causal attention over the fused projection ``qkv`` [B*T, 3*H*hd] (q | k | v blocks,
+    head-major inside each); writes ``out`` [B*T, H*hd] and ``lse`` [B, H, T] (fp32)."""
+    if not qkv.is_cuda:
+        return ref.flash_fwd(qkv, out, lse, B, T, H, hd)
+    _chk(_lib().kh_flash_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, hd, qkv.stride(0),
+                             1.0 / math.sqrt(hd), _stream()))
+
+
+def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
+    """Gradient of ``flash_fwd`` w.r.t. the fused projection: fills ``dqkv`` [B*T, 3*H*hd].
+    ``delta`` [B, H, T] fp32 is scratch for rowsum(dO * O)."""
+    if not qkv.is_cuda:
+        return ref.flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd)
+    _chk(_lib().kh_flash_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), dqkv.data_ptr(),
+                             delta.data_ptr(), B, T, H, hd, qkv.stride(0), 1.0 / math.sqrt(hd), _stream()), 3)

@@ -1,0 +1,40 @@
+"""ctypes prototypes of the CUDA kernel library (``libkharon_cuda.so``)."""
+import ctypes as C
+
+i32, i64, f32, u32 = C.c_int32, C.c_int64, C.c_float, C.c_uint32
+vp, cp, long_ = C.c_void_p, C.c_char_p, C.c_long
+
+
+def _sig(lib, name, res, *args):
+    fn = getattr(lib, name)
+    fn.restype = res
+    fn.argtypes = list(args)
+
+
+def declare(lib):
+    _sig(lib, "kh_cuda_last_error", cp)
+    _sig(lib, "kh_cuda_error_word", i32, i32)
+    _sig(lib, "kh_gemm_bf16", i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp,
+         i32, f32, i32, i32, vp)
+    _sig(lib, "kh_embed_fwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
+    _sig(lib, "kh_embed_bwd", i32, vp, vp, vp, vp, i32, i32, i32, i32, vp)
+    _sig(lib, "kh_colsum", i32, vp, i32, vp, i32, i32, i32, vp)
+    _sig(lib, "kh_layernorm_fwd", i32, vp, vp, vp, vp, vp, vp, i32, i32, vp)
+    _sig(lib, "kh_layernorm_bwd_parts", i32, i32, i32)
+    _sig(lib, "kh_layernorm_bwd", i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp)
+    _sig(lib, "kh_xent", i32, vp, i32, i32, vp, vp, f32, vp, vp, i32, i32, vp)
+    _sig(lib, "kh_sum_f32", i32, vp, long_, f32, vp, i32, vp)
+    _sig(lib, "kh_adamw", i32, vp, vp, vp, vp, vp, long_, f32, f32, f32, f32, f32, f32, f32, f32, i32, vp)
+    _sig(lib, "kh_cast_f32_bf16", i32, vp, vp, long_, vp)
+    _sig(lib, "kh_add_bf16", i32, vp, vp, vp, long_, vp)
+    _sig(lib, "kh_fill_u32", i32, vp, long_, u32, vp)
+    for name, proto in _OPTIONAL.items():
+        if hasattr(lib, name):
+            _sig(lib, name, *proto)
+
+
+# entry points that live in translation units added after the first ones; declared when present
+_OPTIONAL = {
+    "kh_flash_fwd": (i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp),
+    "kh_flash_bwd": (i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp),
+}

@@ -1,0 +1,169 @@
+"""Numerics of each CUDA kernel against the plain-PyTorch fp32 evaluation of the same op."""
+import pytest
+import torch
+
+from kharon_b200 import ops
+from kharon_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def relerr(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K,bn", [(128, 256, 64, 0), (256, 512, 256, 256), (384, 320, 192, 128), (200, 136, 72, 64),
+                                      (1024, 1024, 1024, 0), (8, 1024, 512, 0)])
+def test_gemm_majors(a_mn, b_mn, M, N, K, bn):
+    torch.manual_seed(0)
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("pitch not 16-byte aligned for this major")
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, block_n=bn)
+    want = torch.empty(M, N, device=DEV)
+    ref.gemm(a, b, want, a_mn, b_mn, False, 0, None, None, 1.0)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+    assert relerr(out, want) < 6e-3, relerr(out, want)
+
+
+def test_gemm_fp32_accumulate_and_alpha():
+    torch.manual_seed(1)
+    M, N, K = 256, 384, 320
+    a, b = _rand(K, M), _rand(K, N)
+    out = torch.randn(M, N, device=DEV)
+    base = out.clone()
+    ops.gemm(a, b, out, a_mn=True, b_mn=True, accumulate=True, alpha=0.5)
+    want = base + 0.5 * (a.float().t() @ b.float())
+    assert relerr(out, want) < 1e-5
+    ops.gemm(a, b, out, a_mn=True, b_mn=True, accumulate=False)
+    assert relerr(out, a.float().t() @ b.float()) < 1e-5
+
+
+@pytest.mark.parametrize("epi", [ops.EPI_BIAS, ops.EPI_BIAS_GELU, ops.EPI_BIAS_RESID, ops.EPI_DGELU, ops.EPI_RESID])
+@pytest.mark.parametrize("N", [512, 328])
+def test_gemm_epilogues(epi, N):
+    torch.manual_seed(2)
+    M, K = 320, 256
+    a, b = _rand(M, K, scale=0.5), _rand(N, K, scale=0.1)
+    bias = _rand(N)
+    aux = _rand(M, N)
+    aux_ref = aux.clone()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    want = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out, epi=epi, bias=bias, aux=aux)
+    ref.gemm(a, b, want, False, False, False, epi, bias, aux_ref, 1.0)
+    assert relerr(out, want) < 8e-3
+    if epi == ops.EPI_BIAS_GELU:
+        assert relerr(aux, aux_ref) < 8e-3
+
+
+def test_gemm_vocab_shapes():
+    """Head shapes: N = 50257 (ragged), and the M-major weight-gradient with M = 50304 padded."""
+    torch.manual_seed(3)
+    R, d, V, Vp = 256, 128, 50257, 50304
+    x, wte = _rand(R, d), _rand(V, d, scale=0.05)
+    logits = torch.zeros(R, Vp, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(x, wte, logits[:, :V])
+    want = x.float() @ wte.float().t()
+    assert relerr(logits[:, :V], want) < 6e-3
+    assert logits[:, V:].abs().max().item() == 0
+    dl = _rand(R, Vp, scale=0.01)
+    dl[:, V:] = 0
+    dx = torch.empty(R, d, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(dl[:, :V], wte, dx, b_mn=True)
+    assert relerr(dx, dl[:, :V].float() @ wte.float()) < 6e-3
+    dw = torch.zeros(V, d, device=DEV)
+    ops.gemm(dl[:, :V], x, dw, a_mn=True, b_mn=True, accumulate=True)
+    assert relerr(dw, dl[:, :V].float().t() @ x.float()) < 1e-4
+
+
+def test_layernorm_fwd_bwd():
+    torch.manual_seed(4)
+    for rows, d in [(64, 128), (1000, 512), (4096, 2048)]:
+        x, w, b = _rand(rows, d), _rand(d), _rand(d)
+        dy, dres = _rand(rows, d), _rand(rows, d)
+        y = torch.empty_like(x); mean = torch.empty(rows, device=DEV); rstd = torch.empty(rows, device=DEV)
+        ops.layernorm_fwd(x, w, b, y, mean, rstd)
+        y2 = torch.empty_like(x); m2 = torch.empty_like(mean); r2 = torch.empty_like(rstd)
+        ref.layernorm_fwd(x, w, b, y2, m2, r2)
+        assert relerr(y, y2) < 4e-3 and relerr(mean, m2) < 1e-4 and relerr(rstd, r2) < 1e-4
+        dx = torch.empty_like(x); dw = torch.ones(d, device=DEV); db = torch.ones(d, device=DEV)
+        part = torch.empty(ops.layernorm_bwd_scratch_elems(rows, d), device=DEV)
+        ops.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, part)
+        dx2 = torch.empty_like(x); dw2 = torch.ones(d, device=DEV); db2 = torch.ones(d, device=DEV)
+        ref.layernorm_bwd(dy, x, w, m2, r2, dres, dx2, dw2, db2)
+        assert relerr(dx, dx2) < 5e-3 and relerr(dw, dw2) < 1e-3 and relerr(db, db2) < 1e-3
+
+
+def test_xent():
+    torch.manual_seed(5)
+    for R, V, ld in [(64, 256, 256), (130, 50257, 50304), (32, 1000, 1008)]:
+        logits = torch.zeros(R, ld, device=DEV, dtype=torch.bfloat16)
+        logits[:, :V] = _rand(R, V, scale=2.0)
+        logits[:, V:] = 99.0   # padding must be ignored
+        tgt = torch.randint(0, V, (R,), device=DEV, dtype=torch.int32)
+        tgt[3] = -1
+        coef = torch.randn(R, device=DEV)
+        l2 = logits.clone()
+        rl = torch.empty(R, device=DEV); pr = torch.empty(R, device=DEV)
+        rl2 = torch.empty(R, device=DEV); pr2 = torch.empty(R, device=DEV)
+        ops.xent(logits, V, tgt, coef=coef, rowloss=rl, prob=pr)
+        ref.xent(l2, V, tgt, coef, 1.0, rl2, pr2, True)
+        assert relerr(rl, rl2) < 1e-3 and relerr(pr, pr2) < 2e-3
+        assert relerr(logits, l2) < 1e-2
+        assert logits[:, V:].abs().max().item() == 0
+        assert logits[3].abs().max().item() == 0
+
+
+def test_adamw_matches_torch_and_emits_bf16():
+    torch.manual_seed(6)
+    n = 100003
+    p = torch.randn(n + 1, device=DEV)[:n]
+    p = torch.randn(n, device=DEV); g = torch.randn(n, device=DEV)
+    m = torch.zeros(n, device=DEV); v = torch.zeros(n, device=DEV)
+    pb = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    pt = torch.nn.Parameter(p.clone()); pt.grad = g.clone()
+    opt = torch.optim.AdamW([pt], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in (1, 2, 3):
+        gg = g.clone()
+        ops.adamw(p, gg, m, v, pb, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, step=step)
+        assert gg.abs().max().item() == 0
+        opt.step()
+        assert torch.allclose(p, pt.data, rtol=1e-5, atol=1e-6)
+        assert torch.equal(pb, p.to(torch.bfloat16))
+
+
+def test_embed_and_colsum():
+    torch.manual_seed(7)
+    B, T, d, V = 4, 64, 128, 300
+    tok = torch.randint(0, V, (B * T,), device=DEV, dtype=torch.int32)
+    tok[5] = tok[17] = tok[200] = 11
+    wte, wpe = _rand(V, d), _rand(T, d)
+    out = torch.empty(B * T, d, device=DEV, dtype=torch.bfloat16)
+    ops.embed_fwd(tok, None, wte, wpe, out, T)
+    want = torch.empty_like(out); ref.embed_fwd(tok, None, wte, wpe, want, T)
+    assert relerr(out, want) < 4e-3
+    dx = _rand(B * T, d)
+    dwte = torch.ones(V, d, device=DEV); dwpe = torch.ones(T, d, device=DEV)
+    ops.embed_bwd(tok, dx, dwte, dwpe, B, T)
+    dwte2 = torch.ones(V, d, device=DEV); dwpe2 = torch.ones(T, d, device=DEV)
+    ref.embed_bwd(tok, dx, dwte2, dwpe2, B, T)
+    assert relerr(dwte, dwte2) < 1e-5 and relerr(dwpe, dwpe2) < 1e-5
+    x = _rand(777, 322)
+    cs = torch.ones(322, device=DEV)
+    ops.colsum(x, cs, accumulate=True)
+    assert relerr(cs, 1 + x.float().sum(0)) < 1e-5
+
+
+def test_bounded_wait_status_word_is_clean():
+    assert ops.error_word() == 0
