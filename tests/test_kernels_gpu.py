@@ -121,7 +121,8 @@ def test_xent():
         ref.xent(l2, V, tgt, coef, 1.0, rl2, pr2, True)
         assert relerr(rl, rl2) < 1e-3 and relerr(pr, pr2) < 2e-3
         assert relerr(logits, l2) < 1e-2
-        assert logits[:, V:].abs().max().item() == 0
+        if ld > V:
+            assert logits[:, V:].abs().max().item() == 0
         assert logits[3].abs().max().item() == 0
 
 
@@ -163,6 +164,32 @@ def test_embed_and_colsum():
     cs = torch.ones(322, device=DEV)
     ops.colsum(x, cs, accumulate=True)
     assert relerr(cs, 1 + x.float().sum(0)) < 1e-5
+
+
+@pytest.mark.parametrize("B,T,H,hd", [(2, 256, 4, 64), (1, 512, 2, 128), (3, 64, 2, 64), (2, 200, 2, 128), (1, 1024, 1, 64)])
+def test_flash_fwd_bwd(B, T, H, hd):
+    torch.manual_seed(8)
+    d = H * hd
+    qkv = _rand(B * T, 3 * d, scale=1.0)
+    out = torch.zeros(B * T, d, device=DEV, dtype=torch.bfloat16)
+    lse = torch.zeros(B, H, T, device=DEV)
+    ops.flash_fwd(qkv, out, lse, B, T, H, hd)
+    out2 = torch.empty_like(out); lse2 = torch.empty_like(lse)
+    ref.flash_fwd(qkv, out2, lse2, B, T, H, hd)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+    assert relerr(out, out2) < 1e-2, relerr(out, out2)
+    assert relerr(lse, lse2) < 1e-3
+    dout = _rand(B * T, d)
+    dqkv = torch.zeros_like(qkv); delta = torch.empty(B, H, T, device=DEV)
+    ops.flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd)
+    dqkv2 = torch.zeros_like(qkv)
+    ref.flash_bwd(qkv, out2, dout, lse2, dqkv2, B, T, H, hd)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+    for i, name in enumerate("qkv"):
+        e = relerr(dqkv[:, i * d:(i + 1) * d], dqkv2[:, i * d:(i + 1) * d])
+        assert e < 2e-2, (name, e)
 
 
 def test_bounded_wait_status_word_is_clean():
