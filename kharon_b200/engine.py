@@ -1,0 +1,219 @@
+"""Training engine: one optimizer step of a GPT on a tensor x pipeline x data-parallel mesh.
+
+``TrainEngine.train_step(idx, tgt)`` is the public call a user makes: it takes the step's
+token ids for this data-parallel replica ([M * mbatch * seq] int32, normally in pinned host
+memory), copies them to the device, runs the micro-batches through the 1F1B schedule,
+reduces gradients, applies AdamW and returns the loss as a device tensor (``float(...)`` /
+``engine.loss()`` is the only device->host read).
+
+What runs where (reference: src/pp_train.c:108-116):
+
+* pipeline   the C++ schedule generator emits the 1F1B op list for this stage; sends and
+             receives are NCCL point-to-point (``batch_isend_irecv`` so that a send and its
+             matching receive are one group, the deadlock-free form of comms.cu:68-74).
+* tensor     the model's ``tp_allreduce`` seam: NCCL all-reduce (baseline) or the fused
+             in-kernel NVLink path of ``parallel.fused`` when enabled.
+* data       ZeRO-1: gradients are reduce-scattered (average), AdamW updates this rank's
+             slice of the flat arena and emits the bf16 copy of that slice, and only the bf16
+             compute copy is all-gathered.  The fp32 master outside the rank's slice is
+             refreshed only when a checkpoint is written (src/core/adamw.c:21-58 kept the fp32
+             master replicated and gathered 4 bytes per parameter every step).
+* tied head  with more than one stage the last stage owns a copy of the embedding matrix;
+             the two copies receive the sum of both gradients each step and therefore stay
+             identical.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import time
+
+import torch
+import torch.distributed as dist
+
+from . import _native, ops
+from .models import GPT, Config
+from .parallel.mesh import Mesh
+
+PP_RECV_ACT, PP_SEND_ACT, PP_RECV_GRAD, PP_SEND_GRAD, PP_FWD, PP_BWD, PP_SEND_ACT_RECV_GRAD, PP_SEND_GRAD_RECV_ACT = range(8)
+
+
+def pp_schedule(stage: int, n_stages: int, n_micro: int):
+    """1F1B op list [(op, a0, a1)] of one stage from the native generator."""
+    cap = 8 * (n_micro + n_stages) + 16
+    buf = (C.c_int32 * (3 * cap))()
+    n = _native.rt_check(_native.rt().kh_pp_schedule(stage, n_stages, n_micro, buf, cap))
+    return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
+
+
+def pp_num_slots(stage: int, n_stages: int, n_micro: int) -> int:
+    return int(_native.rt().kh_pp_num_slots(stage, n_stages, n_micro))
+
+
+class TrainEngine:
+    def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
+                 dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
+                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False):
+        self.mesh = mesh or Mesh.single()
+        c = self.mesh.c
+        self.device = torch.device(device)
+        if layers % c.pp:
+            raise ValueError("layers (%d) must divide evenly over %d pipeline stages" % (layers, c.pp))
+        self.total_layers = layers
+        self.n_micro = n_micro
+        self.fused_mb = bool(fuse_microbatches and c.pp == 1)
+        if self.fused_mb:            # one pass over M x mbatch sequences: identical math, larger GEMMs
+            mbatch, n_micro = mbatch * n_micro, 1
+        self.M, self.mbatch, self.seq = n_micro, mbatch, seq
+        self.opt = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=wd)
+        nl = layers // c.pp
+        self.cfg = Config(nl, d_model, heads, vocab, seq, mbatch)
+        self.n_slots = pp_num_slots(c.stage, c.pp, n_micro)
+        self.model = GPT(self.cfg, self.device, dtype, tp=c.tp, tp_rank=c.tp_rank, first=c.first, last=c.last,
+                         untied_head=untied_head, n_slots=self.n_slots, dp=c.dp)
+        if init == "device":
+            self.model.init_weights_device(seed)
+        else:
+            self.model.init_weights(seed, layer0=c.stage * nl, total_layers=layers)
+        self.schedule = pp_schedule(c.stage, c.pp, n_micro)
+        R = mbatch * seq
+        dev = self.device
+        self.tok_dev = torch.zeros(n_micro * R, dtype=torch.int32, device=dev)
+        self.tgt_dev = torch.zeros(n_micro * R, dtype=torch.int32, device=dev)
+        if c.pp > 1:
+            self.recv_act = [torch.empty(R, d_model, dtype=dtype, device=dev) for _ in range(2)]
+            self.recv_grad = [torch.empty(R, d_model, dtype=dtype, device=dev) for _ in range(2)]
+        # ---- tensor parallel seam
+        self.fused = None
+        if c.tp > 1:
+            grp = self.mesh.tp_group
+            self.model.tp_allreduce = lambda t: dist.all_reduce(t, group=grp)
+            if fused_comm and self.device.type == "cuda":
+                from .parallel import fused as fused_mod
+                self.fused = fused_mod.install(self.model, self.mesh)
+        # ---- ZeRO-1
+        ps = self.model.params
+        self.zero = c.dp > 1
+        if self.zero:
+            self.shard = ps.n_padded // c.dp
+            self.lo = c.dp_rank * self.shard
+            ps.alloc_moments(self.shard)
+            self.g_shard = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+        self.timers = {}
+
+    # ------------------------------------------------------------------ helpers
+    @property
+    def tokens_per_step(self):
+        """Tokens this replica consumes per step."""
+        return self.M * self.mbatch * self.seq
+
+    def _p2p(self, ops_):
+        if not ops_:
+            return
+        for w in dist.batch_isend_irecv(ops_):
+            w.wait()
+
+    def _stage_input(self, mb):
+        R = self.mbatch * self.seq
+        s = self.model.slots[mb % self.n_slots]
+        s.tok.copy_(self.tok_dev[mb * R:(mb + 1) * R])
+        s.tgt.copy_(self.tgt_dev[mb * R:(mb + 1) * R])
+
+    # ------------------------------------------------------------------ one step
+    def train_step(self, idx, tgt):
+        """idx/tgt: int32 [M * mbatch * seq] for this replica (host or device)."""
+        m, c = self.model, self.mesh.c
+        self.tok_dev.copy_(idx.reshape(-1), non_blocking=True)
+        self.tgt_dev.copy_(tgt.reshape(-1), non_blocking=True)
+        M = self.M
+        inv = 1.0 / M
+        cur_act = cur_grad = None
+        out_act = {}
+        in_grad = {}
+        n_loss = 0
+        for op, a0, a1 in self.schedule:
+            if op == PP_FWD:
+                self._stage_input(a0)
+                y = m.forward(slot=a1, x_in=cur_act, compute_loss=False)
+                out_act[a0] = y
+            elif op == PP_BWD:
+                dxo = None if c.last else cur_grad
+                g = m.backward(slot=a1, dx_out=dxo, inv_mb=inv, loss_scale=inv, accumulate_loss=n_loss > 0)
+                n_loss += 1
+                in_grad[a0] = g
+            elif op == PP_RECV_ACT:
+                cur_act = self.recv_act[a0 & 1]
+                self._p2p([dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
+            elif op == PP_SEND_ACT:
+                self._p2p([dist.P2POp(dist.isend, out_act.pop(a0), c.next_rank)])
+            elif op == PP_RECV_GRAD:
+                cur_grad = self.recv_grad[a0 & 1]
+                self._p2p([dist.P2POp(dist.irecv, cur_grad, c.next_rank)])
+            elif op == PP_SEND_GRAD:
+                self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank)])
+            elif op == PP_SEND_ACT_RECV_GRAD:     # a0 = micro-batch sent, a1 = micro-batch whose grad arrives
+                cur_grad = self.recv_grad[a1 & 1]
+                self._p2p([dist.P2POp(dist.isend, out_act.pop(a0), c.next_rank),
+                           dist.P2POp(dist.irecv, cur_grad, c.next_rank)])
+            elif op == PP_SEND_GRAD_RECV_ACT:     # a0 = micro-batch whose grad is sent, a1 = next activation
+                cur_act = self.recv_act[a1 & 1]
+                self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank),
+                           dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
+        self._tie_embedding_grads()
+        self.optimizer_step()
+        return m.loss_acc
+
+    def _tie_embedding_grads(self):
+        m = self.model
+        if self.mesh.c.pp > 1 and not m.untied_head and self.mesh.tie_group is not None:
+            g = m.params.grad["wte"] if m.first else m.params.grad["head_w"]
+            dist.all_reduce(g, group=self.mesh.tie_group)
+
+    def optimizer_step(self):
+        m, ps, o = self.model, self.model.params, self.opt
+        if not self.zero:
+            m.adamw_step(o["lr"], o["beta1"], o["beta2"], o["eps"], o["wd"])
+            return
+        grp = self.mesh.dp_group
+        if self.fused is not None and getattr(self.fused, "zero_step", None) is not None:
+            self.fused.zero_step(self)
+            return
+        dist.reduce_scatter_tensor(self.g_shard, ps.g, op=dist.ReduceOp.AVG, group=grp)
+        m.step += 1
+        lo, hi = self.lo, self.lo + self.shard
+        wb = None if ps.wb is ps.w else ps.wb[lo:hi]
+        ops.adamw(ps.w[lo:hi], self.g_shard, ps.m, ps.v, wb, lr=o["lr"], beta1=o["beta1"], beta2=o["beta2"],
+                  eps=o["eps"], wd=o["wd"], step=m.step, grad_scale=1.0, zero_grad=False)
+        ps.g.zero_()
+        # only the compute copy travels; the fp32 master stays sharded
+        tgt_full = ps.wb if ps.wb is not ps.w else ps.w
+        dist.all_gather_into_tensor(tgt_full, tgt_full[lo:hi], group=grp)
+
+    def loss(self) -> float:
+        """Mean loss of the last step (valid on the last pipeline stage)."""
+        return float(self.model.loss_acc.item())
+
+    # ------------------------------------------------------------------ checkpoint
+    def gather_master(self):
+        """Rebuild the full fp32 master on every rank of the data-parallel group (ZeRO-1 keeps
+        only this rank's slice current between checkpoints)."""
+        if self.zero:
+            ps = self.model.params
+            dist.all_gather_into_tensor(ps.w, ps.w[self.lo:self.lo + self.shard].clone(), group=self.mesh.dp_group)
+
+    def ckpt_path(self, prefix):
+        return prefix if self.mesh.world == 1 else "%s.r%d" % (prefix, self.mesh.rank)
+
+    def save(self, prefix, rng_state=0):
+        self.gather_master()
+        self.model.save(self.ckpt_path(prefix), rng_state)
+
+    def load(self, prefix):
+        rng = self.model.load(self.ckpt_path(prefix))
+        return rng
+
+    def memory_report(self):
+        out = {"params_arena_mb": self.model.params.param_bytes / 1e6,
+               "optimizer_state_mb": 2 * self.model.params.m.numel() * 4 / 1e6}
+        if self.device.type == "cuda":
+            out["cuda_allocated_gb"] = torch.cuda.memory_allocated(self.device) / 1e9
+        return out

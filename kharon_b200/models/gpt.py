@@ -1,0 +1,360 @@
+"""Pre-norm GELU GPT with explicit forward and backward passes (no autograd tape).
+
+Architecture = the PyTorch model of the reference's tests/gen_reference.py:59-118: learned
+absolute positions, fused qkv projection, causal attention, tanh-GELU MLP of width 4d,
+LayerNorm eps 1e-5, weight-tied head, mean cross-entropy.  The op order follows the
+reference's gpt.c (forward :399-438, backward :493-543, TP :443-485/:569-625, pipeline
+stage :665-772) but every elementwise step is folded into a GEMM epilogue or a fused kernel:
+
+  forward / layer   LN -> GEMM(+bias) -> flash attention -> GEMM(+bias+residual)
+                    -> LN -> GEMM(+bias, GELU) -> GEMM(+bias+residual)
+  backward / layer  colsum, GEMM(dW+=), GEMM(dX * gelu'), colsum, GEMM(dW+=), GEMM(dX),
+                    LN-bwd(+residual grad), colsum, GEMM(dW+=), GEMM(dX), flash-bwd, colsum,
+                    GEMM(dW+=), GEMM(dX), LN-bwd(+residual grad)
+
+The same code runs in three modes: bf16 on a B200 (native kernels), bf16 on CPU (emulated,
+for the CPU test tier) and fp32 on CPU (the numerical oracle).
+
+Tensor parallelism (Megatron): qkv/fc are column-parallel, proj/fcproj row-parallel.  The
+partial sums of the row-parallel products and of the two input-gradient products are summed
+by ``tp_allreduce`` -- a callback installed by the parallel layer (None = single rank), the
+same seam the reference uses (model.h:88-89).  Rank 0 of the TP group folds bias+residual
+into its partial product so the sum needs no extra pass.
+
+Pipeline parallelism: a stage owns ``n_layer`` consecutive layers; ``first`` embeds,
+``last`` applies the final norm, head and loss.  Activations are stashed per ``slot`` so
+that several micro-batches can be in flight (1F1B).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from .layout import Config, ParamStore, LAYER_FIELDS
+
+
+def _pad64(n):
+    return (n + 63) // 64 * 64
+
+
+class _Slot:
+    """Activation stash of one in-flight micro-batch."""
+
+    def __init__(self, cfg: Config, tp, dev, dt, first, last, Vp):
+        R, d = cfg.batch * cfg.seq, cfg.d_model
+        dl, fo, Hl = d // tp, 4 * d // tp, cfg.n_head // tp
+        e = lambda *s: torch.empty(*s, dtype=dt, device=dev)
+        f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
+        self.x = [e(R, d) for _ in range(cfg.n_layer + 1)]   # residual stream: x[l] enters layer l
+        self.layers = []
+        for _ in range(cfg.n_layer):
+            self.layers.append(dict(
+                ln1=e(R, d), mean1=f(R), rstd1=f(R), qkv=e(R, 3 * dl), att=e(R, dl), lse=f(cfg.batch, Hl, cfg.seq),
+                xmid=e(R, d), ln2=e(R, d), mean2=f(R), rstd2=f(R), pre=e(R, fo), act=e(R, fo)))
+        self.tok = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.tgt = torch.zeros(R, dtype=torch.int32, device=dev)
+        if last:
+            self.lnf, self.meanf, self.rstdf = e(R, d), f(R), f(R)
+            self.logits = torch.zeros(R, Vp, dtype=dt, device=dev)
+            self.rowloss = f(R)
+            self.prob = f(R)
+
+
+class GPT:
+    def __init__(self, cfg: Config, device="cpu", dtype=torch.bfloat16, tp=1, tp_rank=0, first=True, last=True,
+                 untied_head=False, n_slots=1, dp=1):
+        assert cfg.d_model % cfg.n_head == 0 and cfg.n_head % tp == 0
+        self.cfg, self.tp, self.tp_rank = cfg, tp, tp_rank
+        self.first, self.last = first, last
+        self.device, self.dtype = torch.device(device), dtype
+        # a separate head matrix exists on the last stage of a multi-stage pipeline (tied to the
+        # first stage's wte by a gradient exchange) or when an untied head is requested
+        self.has_head = last and (untied_head or not first)
+        self.untied_head = untied_head
+        self.params = ParamStore(cfg, device, dtype, tp, self.has_head, pad_to=dp)
+        self.params.alloc_moments()
+        self.step = 0
+        self.Vp = _pad64(cfg.vocab)
+        self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp) for _ in range(n_slots)]
+        R, d = cfg.batch * cfg.seq, cfg.d_model
+        dl, fo = d // tp, 4 * d // tp
+        e = lambda *s: torch.empty(*s, dtype=dtype, device=self.device)
+        # backward scratch, shared by all layers and slots
+        self.s_dx = [e(R, d), e(R, d)]
+        self.s_dln = e(R, d)
+        self.s_dpre = e(R, fo)
+        self.s_datt = e(R, dl)
+        self.s_dqkv = e(R, 3 * dl)
+        self.s_delta = torch.empty(cfg.batch, cfg.n_head // tp, cfg.seq, dtype=torch.float32, device=self.device)
+        self.s_lnpart = torch.empty(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
+                                    dtype=torch.float32, device=self.device)
+        self.s_tp = e(R, d) if tp > 1 else None
+        self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.tp_allreduce = None      # callable(tensor) summing in place over the TP group
+        self.skip_loss = False
+        # fused tensor-parallel operators (installed by parallel.tp when available)
+        self.fused_tp = None
+
+    # ------------------------------------------------------------------ parameters
+    def L(self, l, name):
+        return self.params.c["l%d.%s" % (l, name)]
+
+    def G(self, l, name):
+        return self.params.grad["l%d.%s" % (l, name)]
+
+    def init_weights(self, seed: int, layer0: int = 0, total_layers: int | None = None):
+        """GPT-2 init N(0, 0.02) from the host xorshift stream, drawn in the global order of the
+        whole model so that any TP x PP sharding reassembles to the single-GPU weights
+        (src/core/gpt.c:247-264, :301-323, :638-663)."""
+        from ..utils.rng import Rng
+        cfg, tp, r = self.cfg, self.tp, self.tp_rank
+        d, V, S = cfg.d_model, cfg.vocab, cfg.seq
+        ff, dl, fo = 4 * d, d // tp, 4 * d // tp
+        total = cfg.n_layer if total_layers is None else total_layers
+        st = Rng(seed)
+        P = self.params.p
+
+        def put(name, t):
+            P[name].copy_(t.view(P[name].shape))
+
+        wte = st.normal_block(V, d, 0, V, 0, d, 0.02, keep=self.first or (self.has_head and not self.untied_head))
+        if self.first:
+            put("wte", wte)
+        if self.has_head and not self.untied_head:
+            put("head_w", wte)
+        wpe = st.normal_block(S, d, 0, S, 0, d, 0.02, keep=self.first)
+        if self.first:
+            put("wpe", wpe)
+        for gl in range(total):
+            own = layer0 <= gl < layer0 + cfg.n_layer
+            pre = "l%d." % (gl - layer0)
+            if own:
+                for n in ("ln1_w", "ln2_w"):
+                    P[pre + n].fill_(1.0)
+                for n in ("ln1_b", "ln2_b", "qkv_b", "proj_b", "fc_b", "fcproj_b"):
+                    P[pre + n].zero_()
+            # qkv: dl rows from each of the q, k, v thirds
+            parts = [st.normal_block(d, d, r * dl, (r + 1) * dl, 0, d, 0.02, keep=own) for _ in range(3)]
+            if own:
+                put(pre + "qkv_w", torch.cat(parts, 0))
+            t = st.normal_block(d, d, 0, d, r * dl, (r + 1) * dl, 0.02, keep=own)
+            if own:
+                put(pre + "proj_w", t)
+            t = st.normal_block(ff, d, r * fo, (r + 1) * fo, 0, d, 0.02, keep=own)
+            if own:
+                put(pre + "fc_w", t)
+            t = st.normal_block(d, ff, 0, d, r * fo, (r + 1) * fo, 0.02, keep=own)
+            if own:
+                put(pre + "fcproj_w", t)
+        if self.has_head and self.untied_head:
+            put("head_w", st.normal_block(V, d, 0, V, 0, d, 0.02))
+        P["lnf_w"].fill_(1.0)
+        P["lnf_b"].zero_()
+        self.params.sync_compute_copy()
+
+    def init_weights_device(self, seed: int):
+        """N(0, 0.02) drawn on the device (fast start-up for benchmarks; not stream-compatible
+        with ``init_weights``).  Replicated tensors use the same generator state on every rank."""
+        g = torch.Generator(device=self.device)
+        P = self.params.p
+        for name in self.params.names:
+            t = P[name]
+            base = name.split(".")[-1]
+            sharded = base in ("qkv_w", "proj_w", "fc_w", "fcproj_w")
+            g.manual_seed(seed * 1000003 + (hash(name) % 65536) * 31 + (self.tp_rank if sharded else 0))
+            if base.endswith("_b"):
+                t.zero_()
+            elif base in ("ln1_w", "ln2_w", "lnf_w"):
+                t.fill_(1.0)
+            else:
+                t.normal_(0.0, 0.02, generator=g)
+        self.params.sync_compute_copy()
+
+    def load_ref(self, tensors: dict):
+        """Load weights from a CHRN fixture (names of tests/gen_reference.py:131-141)."""
+        P = self.params.p
+        P["wte"].copy_(tensors["wte"])
+        P["wpe"].copy_(tensors["wpe"])
+        ren = {"ln1_w": "ln1.w", "ln1_b": "ln1.b", "qkv_w": "qkv.w", "qkv_b": "qkv.b", "proj_w": "proj.w",
+               "proj_b": "proj.b", "ln2_w": "ln2.w", "ln2_b": "ln2.b", "fc_w": "fc.w", "fc_b": "fc.b",
+               "fcproj_w": "fcproj.w", "fcproj_b": "fcproj.b"}
+        for l in range(self.cfg.n_layer):
+            for f in LAYER_FIELDS:
+                P["l%d.%s" % (l, f)].copy_(tensors["blk%d.%s" % (l, ren[f])])
+        P["lnf_w"].copy_(tensors["lnf.w"])
+        P["lnf_b"].copy_(tensors["lnf.b"])
+        self.params.sync_compute_copy()
+
+    def sync_bf16(self):
+        self.params.sync_compute_copy()
+
+    def zero_grads(self):
+        self.params.g.zero_()
+
+    # ------------------------------------------------------------------ inputs
+    def set_input(self, idx, tgt, slot=0):
+        s = self.slots[slot]
+        s.tok.copy_(idx.reshape(-1), non_blocking=True)
+        if tgt is not None:
+            s.tgt.copy_(tgt.reshape(-1), non_blocking=True)
+
+    # ------------------------------------------------------------------ forward
+    def _ar(self, t):
+        if self.tp_allreduce is not None:
+            self.tp_allreduce(t)
+
+    def forward_layers(self, s: _Slot):
+        cfg, tp = self.cfg, self.tp
+        B, T, Hl, hd = cfg.batch, cfg.seq, cfg.n_head // tp, cfg.head_dim
+        lead = self.tp_rank == 0
+        for l in range(cfg.n_layer):
+            a = s.layers[l]
+            x = s.x[l]
+            ops.layernorm_fwd(x, self.L(l, "ln1_w"), self.L(l, "ln1_b"), a["ln1"], a["mean1"], a["rstd1"])
+            ops.gemm(a["ln1"], self.L(l, "qkv_w"), a["qkv"], epi=ops.EPI_BIAS, bias=self.L(l, "qkv_b"))
+            ops.flash_fwd(a["qkv"], a["att"], a["lse"], B, T, Hl, hd)
+            if lead:
+                ops.gemm(a["att"], self.L(l, "proj_w"), a["xmid"], epi=ops.EPI_BIAS_RESID, bias=self.L(l, "proj_b"), aux=x)
+            else:
+                ops.gemm(a["att"], self.L(l, "proj_w"), a["xmid"])
+            self._ar(a["xmid"])
+            ops.layernorm_fwd(a["xmid"], self.L(l, "ln2_w"), self.L(l, "ln2_b"), a["ln2"], a["mean2"], a["rstd2"])
+            ops.gemm(a["ln2"], self.L(l, "fc_w"), a["act"], epi=ops.EPI_BIAS_GELU, bias=self.L(l, "fc_b"), aux=a["pre"])
+            if lead:
+                ops.gemm(a["act"], self.L(l, "fcproj_w"), s.x[l + 1], epi=ops.EPI_BIAS_RESID,
+                         bias=self.L(l, "fcproj_b"), aux=a["xmid"])
+            else:
+                ops.gemm(a["act"], self.L(l, "fcproj_w"), s.x[l + 1])
+            self._ar(s.x[l + 1])
+
+    def head_weight(self):
+        return self.params.c["head_w"] if self.has_head else self.params.c["wte"]
+
+    def head_grad(self):
+        return self.params.grad["head_w"] if self.has_head else self.params.grad["wte"]
+
+    def forward_head(self, s: _Slot):
+        cfg = self.cfg
+        ops.layernorm_fwd(s.x[cfg.n_layer], self.params.c["lnf_w"], self.params.c["lnf_b"], s.lnf, s.meanf, s.rstdf)
+        ops.gemm(s.lnf, self.head_weight(), s.logits[:, :cfg.vocab])
+
+    def forward(self, slot=0, x_in=None, loss_scale=1.0, accumulate_loss=False, compute_loss=True):
+        """Forward of one micro-batch.  First stage embeds ``tok``; other stages take ``x_in``
+        ([R, d], copied into the stash).  On the last stage the logits are left in the stash and
+        the mean cross-entropy times ``loss_scale`` is added to / stored in ``loss_acc``; returns
+        the stage output otherwise."""
+        s = self.slots[slot]
+        cfg = self.cfg
+        if self.first:
+            ops.embed_fwd(s.tok, None, self.params.c["wte"], self.params.c["wpe"], s.x[0], cfg.seq)
+        else:
+            s.x[0].copy_(x_in)
+        self.forward_layers(s)
+        if not self.last:
+            return s.x[cfg.n_layer]
+        self.forward_head(s)
+        if compute_loss and not self.skip_loss:
+            R = cfg.batch * cfg.seq
+            ops.xent(s.logits, cfg.vocab, s.tgt, rowloss=s.rowloss, write_grad=False)
+            ops.sum_f32(s.rowloss, self.loss_acc, scale=loss_scale / R, accumulate=accumulate_loss)
+        return None
+
+    def loss(self) -> float:
+        """Host read of the accumulated loss (the only device->host sync of a step)."""
+        return float(self.loss_acc.item())
+
+    # ------------------------------------------------------------------ backward
+    def backward(self, slot=0, dx_out=None, inv_mb=1.0, coef=None, loss_scale=None, accumulate_loss=False):
+        """Backward of one micro-batch; gradients accumulate into the fp32 arena.  Last stage
+        starts from the loss (``inv_mb`` = 1/M scales it; ``coef`` [R] replaces the uniform
+        cross-entropy weight for GRPO, src/core/gpt.c:558); other stages take ``dx_out``.  Returns
+        the gradient w.r.t. the stage input (None on the first stage).  With ``loss_scale`` the
+        same pass over the logits also produces the loss (mean CE x loss_scale into ``loss_acc``),
+        so a training step reads the logits once."""
+        s = self.slots[slot]
+        cfg, tp = self.cfg, self.tp
+        R, V = cfg.batch * cfg.seq, cfg.vocab
+        B, T, Hl, hd = cfg.batch, cfg.seq, cfg.n_head // tp, cfg.head_dim
+        P, Gd = self.params.c, self.params.grad
+        dx, other = self.s_dx
+        if self.last:
+            want_loss = loss_scale is not None and not self.skip_loss
+            ops.xent(s.logits, V, s.tgt, coef=coef, uniform=inv_mb / R, write_grad=True,
+                     rowloss=s.rowloss if want_loss else None)
+            if want_loss:
+                ops.sum_f32(s.rowloss, self.loss_acc, scale=loss_scale / R, accumulate=accumulate_loss)
+            dl = s.logits[:, :V]
+            ops.gemm(dl, self.head_weight(), self.s_dln, b_mn=True)
+            ops.gemm(dl, s.lnf, self.head_grad(), a_mn=True, b_mn=True, accumulate=True)
+            ops.layernorm_bwd(self.s_dln, s.x[cfg.n_layer], P["lnf_w"], s.meanf, s.rstdf, None, dx, Gd["lnf_w"],
+                              Gd["lnf_b"], self.s_lnpart)
+        else:
+            dx.copy_(dx_out)
+        for l in reversed(range(cfg.n_layer)):
+            a = s.layers[l]
+            # x[l+1] = xmid + act @ Wfp^T + b
+            ops.colsum(dx, self.G(l, "fcproj_b"))
+            ops.gemm(dx, a["act"], self.G(l, "fcproj_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(dx, self.L(l, "fcproj_w"), self.s_dpre, b_mn=True, epi=ops.EPI_DGELU, aux=a["pre"])
+            ops.colsum(self.s_dpre, self.G(l, "fc_b"))
+            ops.gemm(self.s_dpre, a["ln2"], self.G(l, "fc_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(self.s_dpre, self.L(l, "fc_w"), self.s_dln, b_mn=True)
+            self._ar(self.s_dln)
+            ops.layernorm_bwd(self.s_dln, a["xmid"], self.L(l, "ln2_w"), a["mean2"], a["rstd2"], dx, other,
+                              self.G(l, "ln2_w"), self.G(l, "ln2_b"), self.s_lnpart)
+            dx, other = other, dx
+            # xmid = x + att @ Wp^T + b
+            ops.colsum(dx, self.G(l, "proj_b"))
+            ops.gemm(dx, a["att"], self.G(l, "proj_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(dx, self.L(l, "proj_w"), self.s_datt, b_mn=True)
+            ops.flash_bwd(a["qkv"], a["att"], self.s_datt, a["lse"], self.s_dqkv, self.s_delta, B, T, Hl, hd)
+            ops.colsum(self.s_dqkv, self.G(l, "qkv_b"))
+            ops.gemm(self.s_dqkv, a["ln1"], self.G(l, "qkv_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(self.s_dqkv, self.L(l, "qkv_w"), self.s_dln, b_mn=True)
+            self._ar(self.s_dln)
+            ops.layernorm_bwd(self.s_dln, s.x[l], self.L(l, "ln1_w"), a["mean1"], a["rstd1"], dx, other,
+                              self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
+            dx, other = other, dx
+        if self.first:
+            ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T)
+            return None
+        return dx
+
+    def gather_prob(self, slot=0):
+        """p(target) per row from the logits of the last forward (src/core/kernels.cu:372-378)."""
+        s = self.slots[slot]
+        ops.xent(s.logits, self.cfg.vocab, s.tgt, prob=s.prob, write_grad=False)
+        return s.prob
+
+    # ------------------------------------------------------------------ optimizer
+    def adamw_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0):
+        """Fused AdamW over the flat arena (src/core/adamw.c:9-16); also refreshes the bf16
+        compute copy and clears the gradients for the next accumulation."""
+        self.step += 1
+        ps = self.params
+        ops.adamw(ps.w, ps.g, ps.m, ps.v, None if ps.wb is ps.w else ps.wb, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                  wd=wd, step=self.step, grad_scale=grad_scale, zero_grad=True)
+
+    # ------------------------------------------------------------------ checkpoint
+    def save(self, path, rng_state=0, moments=None):
+        from ..utils import ckpt
+        ps = self.params
+        m, v = moments if moments is not None else (ps.m[:ps.n_flat], ps.v[:ps.n_flat])
+        ckpt.save(path, self.cfg.as_list(), self.step, rng_state, ps.w[:ps.n_flat], m, v)
+
+    def load(self, path, moments=None):
+        from ..utils import ckpt
+        ps = self.params
+        m, v = moments if moments is not None else (ps.m[:ps.n_flat], ps.v[:ps.n_flat])
+        self.step, rng = ckpt.load(path, self.cfg.as_list(), ps.w[:ps.n_flat], m, v)
+        ps.sync_compute_copy()
+        return rng
+
+    def memory_bytes(self):
+        ps = self.params
+        tot = sum(t.numel() * t.element_size() for t in (ps.w, ps.g, ps.m, ps.v))
+        if ps.wb is not ps.w:
+            tot += ps.wb.numel() * ps.wb.element_size()
+        return tot
