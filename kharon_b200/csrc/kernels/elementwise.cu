@@ -56,21 +56,40 @@ extern "C" int kh_embed_fwd(const void* tok, const void* pos, const void* wte, c
   return 0;
 }
 
-// dwte[tok[r], :] += dx[r, :] -- the first row (lowest r) holding a token id owns the update and
-// folds in the later rows carrying the same id, in row order: deterministic and O(R d).
-__global__ void embed_bwd_wte_k(const int* __restrict__ tok, const bf16* __restrict__ dx, float* __restrict__ dwte,
-                                int rows, int d, int V) {
-  extern __shared__ int s_tok[];
-  for (int i = threadIdx.x; i < rows; i += blockDim.x) s_tok[i] = tok[i];
-  __syncthreads();
-  const int r = blockIdx.x;
-  const int t = s_tok[r];
+// dwte[tok[r], :] += dx[r, :], deterministic and O(R d): integer atomics (order-independent
+// results) find, per token id, its first row and its multiplicity; the first row owns the
+// update and, only when the id occurs more than once, folds in the later rows in row order.
+// `table` is int scratch of 2*V entries.
+__global__ void embed_bwd_index_k(const int* __restrict__ tok, int* __restrict__ first, int* __restrict__ cnt,
+                                  int rows, int V) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int t = tok[r];
   if (t < 0 || t >= V) return;
-  for (int i = 0; i < r; i++) if (s_tok[i] == t) return;   // an earlier row owns this id (uniform)
-  for (int e = threadIdx.x; e < d; e += blockDim.x) {
-    float acc = __bfloat162float(dx[(size_t)r * d + e]);
-    for (int i = r + 1; i < rows; i++) if (s_tok[i] == t) acc += __bfloat162float(dx[(size_t)i * d + e]);
-    dwte[(size_t)t * d + e] += acc;
+  atomicMin(first + t, r);
+  atomicAdd(cnt + t, 1);
+}
+__global__ void embed_bwd_wte_k(const int* __restrict__ tok, const bf16* __restrict__ dx, float* __restrict__ dwte,
+                                const int* __restrict__ first, const int* __restrict__ cnt, int rows, int d, int V) {
+  const int r = blockIdx.x;
+  const int t = tok[r];
+  if (t < 0 || t >= V || first[t] != r) return;
+  const int dup = cnt[t];
+  for (int e = threadIdx.x * 2; e < d; e += blockDim.x * 2) {
+    float2 acc = unpack_bf16(*reinterpret_cast<const uint32_t*>(dx + (size_t)r * d + e));
+    if (dup > 1) {
+      int left = dup - 1;
+      for (int i = r + 1; i < rows && left > 0; i++)
+        if (tok[i] == t) {
+          float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dx + (size_t)i * d + e));
+          acc.x += v.x; acc.y += v.y;
+          left--;
+        }
+    }
+    float2* o = reinterpret_cast<float2*>(dwte + (size_t)t * d + e);
+    float2 old = *o;
+    old.x += acc.x; old.y += acc.y;
+    *o = old;
   }
 }
 // dwpe[t, :] += sum_b dx[b*T + t, :]
@@ -81,46 +100,81 @@ __global__ void embed_bwd_wpe_k(const bf16* __restrict__ dx, float* __restrict__
   for (int b = 0; b < B; b++) acc += __bfloat162float(dx[(size_t)b * T * d + i]);
   dwpe[i] += acc;
 }
-extern "C" int kh_embed_bwd(const void* tok, const void* dx, void* dwte, void* dwpe, int B, int T, int d, int V,
-                            void* stream) {
+extern "C" int kh_embed_bwd(const void* tok, const void* dx, void* dwte, void* dwpe, void* table, int B, int T, int d,
+                            int V, void* stream) {
   const int rows = B * T;
-  if ((size_t)rows * 4 > 200 * 1024) { kh_set_error("embed_bwd: %d rows exceed the shared-memory token table", rows); return -1; }
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(embed_bwd_wte_k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
-  if (dwte) embed_bwd_wte_k<<<rows, 128, rows * 4, (cudaStream_t)stream>>>((const int*)tok, (const bf16*)dx, (float*)dwte, rows, d, V);
-  if (dwpe) embed_bwd_wpe_k<<<cdiv((long)T * d, 256), 256, 0, (cudaStream_t)stream>>>((const bf16*)dx, (float*)dwpe, B, T, d);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d % 2) { kh_set_error("embed_bwd: d must be even"); return -1; }
+  if (dwte) {
+    int* first = (int*)table;
+    int* cnt = first + V;
+    cudaMemsetAsync(first, 0x7f, (size_t)V * sizeof(int), st);
+    cudaMemsetAsync(cnt, 0, (size_t)V * sizeof(int), st);
+    embed_bwd_index_k<<<cdiv(rows, 256), 256, 0, st>>>((const int*)tok, first, cnt, rows, V);
+    embed_bwd_wte_k<<<rows, 128, 0, st>>>((const int*)tok, (const bf16*)dx, (float*)dwte, first, cnt, rows, d, V);
+  }
+  if (dwpe) embed_bwd_wpe_k<<<cdiv((long)T * d, 256), 256, 0, st>>>((const bf16*)dx, (float*)dwpe, B, T, d);
   KH_LAUNCH_CHECK("embed_bwd");
   return 0;
 }
 
 // ------------------------------------------------------------------------------ column sum
-// out[j] (+)= sum_r x[r, j].  Each CTA owns 64 columns; 8 row-groups of 32 threads (bf16x2
-// per thread) stride over the rows, then the 8 partials are added in a fixed order.
-__global__ void colsum_k(const bf16* __restrict__ x, int ld, float* __restrict__ out, int rows, int N, int accumulate) {
-  __shared__ float2 part[8][32];
-  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
-  const int col = blockIdx.x * 64 + lane * 2;
-  float2 acc = make_float2(0.f, 0.f);
-  if (col < N) {
-    for (int r = g; r < rows; r += 8) {
-      float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(x + (size_t)r * ld + col));
-      acc.x += v.x; acc.y += v.y;
+// out[j] (+)= sum_r x[r, j], two deterministic stages.  Stage 1: CTA (column block of 64, row
+// split s) sums its rows with 16-byte loads (8 threads span the 64 columns, 32 row lanes) and
+// writes one partial row to `scratch` [splits, N]; stage 2 adds the splits in index order.
+__global__ void colsum_part_k(const bf16* __restrict__ x, int ld, float* __restrict__ scratch, int rows, int N,
+                              int rows_per_split) {
+  __shared__ float part[32][65];
+  const int cg = threadIdx.x & 7, rg = threadIdx.x >> 3;
+  const int col = blockIdx.x * 64 + cg * 8;
+  const int r0 = blockIdx.y * rows_per_split, r1 = min(rows, r0 + rows_per_split);
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) acc[k] = 0.f;
+  if (col + 8 <= N) {
+    for (int r = r0 + rg; r < r1; r += 32) {
+      uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)r * ld + col);
+      float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), e = unpack_bf16(v.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+    }
+  } else {
+    for (int r = r0 + rg; r < r1; r += 32)
+      for (int k = 0; k < 8; k++) if (col + k < N) acc[k] += __bfloat162float(x[(size_t)r * ld + col + k]);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; k++) part[rg][cg * 8 + k] = acc[k];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < N) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 32; k++) s += part[k][threadIdx.x];
+      scratch[(size_t)blockIdx.y * N + c] = s;
     }
   }
-  part[g][lane] = acc;
-  __syncthreads();
-  if (g == 0 && col < N) {
-    float2 s = part[0][lane];
-#pragma unroll
-    for (int k = 1; k < 8; k++) { s.x += part[k][lane].x; s.y += part[k][lane].y; }
-    if (accumulate) { s.x += out[col]; if (col + 1 < N) s.y += out[col + 1]; }
-    out[col] = s.x;
-    if (col + 1 < N) out[col + 1] = s.y;
-  }
 }
-extern "C" int kh_colsum(const void* x, int ld, void* out, int rows, int N, int accumulate, void* stream) {
-  if (N % 2 || ld % 2) { kh_set_error("colsum: N and ld must be even"); return -1; }
-  colsum_k<<<cdiv(N, 64), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ld, (float*)out, rows, N, accumulate);
+__global__ void colsum_final_k(const float* __restrict__ scratch, float* __restrict__ out, int splits, int N, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float s = accumulate ? out[c] : 0.f;
+  for (int k = 0; k < splits; k++) s += scratch[(size_t)k * N + c];
+  out[c] = s;
+}
+extern "C" int kh_colsum_splits(int rows, int N) {
+  const int cb = (N + 63) / 64;
+  int splits = (592 + cb - 1) / cb;
+  const int max_by_rows = (rows + 63) / 64;
+  if (splits > max_by_rows) splits = max_by_rows;
+  return splits < 1 ? 1 : splits;
+}
+extern "C" int kh_colsum(const void* x, int ld, void* out, void* scratch, int rows, int N, int accumulate, void* stream) {
+  if (ld % 8 || ((uintptr_t)x & 15)) { kh_set_error("colsum: input pitch/base must be 16-byte aligned"); return -1; }
+  const int splits = kh_colsum_splits(rows, N);
+  const int rps = (rows + splits - 1) / splits;
+  dim3 grid(cdiv(N, 64), splits);
+  colsum_part_k<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ld, (float*)scratch, rows, N, rps);
+  colsum_final_k<<<cdiv(N, 256), 256, 0, (cudaStream_t)stream>>>((const float*)scratch, (float*)out, splits, N, accumulate);
   KH_LAUNCH_CHECK("colsum");
   return 0;
 }
@@ -175,60 +229,91 @@ extern "C" int kh_layernorm_fwd(const void* x, const void* w, const void* b, voi
   return 0;
 }
 
-// Backward.  dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * w, optionally
-// + dres (the residual-stream gradient that bypasses the norm).  Each CTA covers a contiguous
-// band of rows and writes its partial dw/db column sums to `partials` ([grid, 2, d] fp32, a
-// scratch buffer supplied by the caller); layernorm_bwd_reduce_k then adds the bands in
-// index order into the fp32 gradient buffers.
-#define LN_BWD_WARPS 8
-__global__ void layernorm_bwd_k(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                const float* __restrict__ mean, const float* __restrict__ rstd,
-                                const bf16* __restrict__ dres, bf16* __restrict__ dx, float* __restrict__ partials,
-                                int rows, int d, int rows_per_cta) {
-  extern __shared__ float s_acc[];   // [LN_BWD_WARPS][2][d]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* my_dw = s_acc + (size_t)warp * 2 * d;
-  float* my_db = my_dw + d;
-  for (int j = lane; j < d; j += 32) { my_dw[j] = 0.f; my_db[j] = 0.f; }
-  const int r0 = blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
-  for (int row = r0 + warp; row < r1; row += LN_BWD_WARPS) {
-    const bf16* dyr = dy + (size_t)row * d;
-    const bf16* xr = x + (size_t)row * d;
-    const float mu = mean[row], rs = rstd[row];
-    float s1 = 0.f, s2 = 0.f;
-    for (int j = lane * 2; j < d; j += 64) {
-      float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dyr + j));
-      float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(xr + j));
-      float2 ww = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + j));
-      float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
+// Backward, two kernels.
+//  (1) dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * w, optionally + dres (the
+//      residual-stream gradient that bypasses the norm): one warp per row, the second sweep
+//      over the row hits L1.
+//  (2) dw[j] += sum_r dy * xhat, db[j] += sum_r dy: column-oriented like colsum -- CTA (64
+//      columns, row split) accumulates in registers with 16-byte loads and writes one partial
+//      row per split to `partials` ([splits, 2, d] fp32, caller-supplied scratch); a last
+//      kernel adds the splits in index order into the fp32 gradient buffers.
+__global__ void layernorm_bwd_dx_k(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                   const float* __restrict__ mean, const float* __restrict__ rstd,
+                                   const bf16* __restrict__ dres, bf16* __restrict__ dx, int rows, int d) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* dyp = reinterpret_cast<const uint4*>(dy + (size_t)row * d);
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+  const uint4* wp = reinterpret_cast<const uint4*>(w);
+  const float mu = mean[row], rs = rstd[row];
+  const int nv = d / 8;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = lane; i < nv; i += 32) {
+    uint4 gv = dyp[i], xv = xp[i], wv = __ldg(wp + i);
+    const uint32_t* gi = &gv.x; const uint32_t* xi = &xv.x; const uint32_t* wi = &wv.x;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      float2 g = unpack_bf16(gi[k]), xx = unpack_bf16(xi[k]), ww = unpack_bf16(wi[k]);
       float g0 = g.x * ww.x, g1 = g.y * ww.y;
       s1 += g0 + g1;
-      s2 += g0 * xh0 + g1 * xh1;
-      my_dw[j] += g.x * xh0; my_dw[j + 1] += g.y * xh1;
-      my_db[j] += g.x; my_db[j + 1] += g.y;
-    }
-    s1 = warp_sum(s1) / d;
-    s2 = warp_sum(s2) / d;
-    for (int j = lane * 2; j < d; j += 64) {
-      float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dyr + j));
-      float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(xr + j));
-      float2 ww = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + j));
-      float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
-      float o0 = rs * (g.x * ww.x - s1 - xh0 * s2), o1 = rs * (g.y * ww.y - s1 - xh1 * s2);
-      if (dres) {
-        float2 rr = unpack_bf16(*reinterpret_cast<const uint32_t*>(dres + (size_t)row * d + j));
-        o0 += rr.x; o1 += rr.y;
-      }
-      *reinterpret_cast<uint32_t*>(dx + (size_t)row * d + j) = pack_bf16(o0, o1);
+      s2 += g0 * ((xx.x - mu) * rs) + g1 * ((xx.y - mu) * rs);
     }
   }
-  __syncthreads();
-  float* out = partials + (size_t)blockIdx.x * 2 * d;
-  for (int j = threadIdx.x; j < 2 * d; j += blockDim.x) {
-    float s = 0.f;
+  s1 = warp_sum(s1) / d;
+  s2 = warp_sum(s2) / d;
+  const uint4* rp = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * d) : nullptr;
+  uint4* op = reinterpret_cast<uint4*>(dx + (size_t)row * d);
+  for (int i = lane; i < nv; i += 32) {
+    uint4 gv = dyp[i], xv = xp[i], wv = __ldg(wp + i), rv = make_uint4(0, 0, 0, 0), o;
+    if (rp) rv = rp[i];
+    const uint32_t* gi = &gv.x; const uint32_t* xi = &xv.x; const uint32_t* wi = &wv.x; const uint32_t* ri = &rv.x;
+    uint32_t* oi = &o.x;
 #pragma unroll
-    for (int k = 0; k < LN_BWD_WARPS; k++) s += s_acc[(size_t)k * 2 * d + j];
-    out[j] = s;
+    for (int k = 0; k < 4; k++) {
+      float2 g = unpack_bf16(gi[k]), xx = unpack_bf16(xi[k]), ww = unpack_bf16(wi[k]), rr = unpack_bf16(ri[k]);
+      float xh0 = (xx.x - mu) * rs, xh1 = (xx.y - mu) * rs;
+      oi[k] = pack_bf16(rs * (g.x * ww.x - s1 - xh0 * s2) + rr.x, rs * (g.y * ww.y - s1 - xh1 * s2) + rr.y);
+    }
+    op[i] = o;
+  }
+}
+__global__ void layernorm_bwd_dwdb_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                     const float* __restrict__ mean, const float* __restrict__ rstd,
+                                     float* __restrict__ partials, int rows, int d, int rows_per_split) {
+  __shared__ float part[32][2][65];
+  const int cg = threadIdx.x & 7, rg = threadIdx.x >> 3;
+  const int col = blockIdx.x * 64 + cg * 8;
+  const int r0 = blockIdx.y * rows_per_split, r1 = min(rows, r0 + rows_per_split);
+  float aw[8], ab[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) { aw[k] = 0.f; ab[k] = 0.f; }
+  if (col < d) {
+    for (int r = r0 + rg; r < r1; r += 32) {
+      uint4 gv = *reinterpret_cast<const uint4*>(dy + (size_t)r * d + col);
+      uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)r * d + col);
+      const float mu = mean[r], rs = rstd[r];
+      const uint32_t* gi = &gv.x; const uint32_t* xi = &xv.x;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        float2 g = unpack_bf16(gi[k]), xx = unpack_bf16(xi[k]);
+        aw[2 * k] += g.x * ((xx.x - mu) * rs); aw[2 * k + 1] += g.y * ((xx.y - mu) * rs);
+        ab[2 * k] += g.x; ab[2 * k + 1] += g.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; k++) { part[rg][0][cg * 8 + k] = aw[k]; part[rg][1][cg * 8 + k] = ab[k]; }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int which = threadIdx.x >> 6, cc = threadIdx.x & 63;
+    const int c = blockIdx.x * 64 + cc;
+    if (c < d) {
+      float sacc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 32; k++) sacc += part[k][which][cc];
+      partials[((size_t)blockIdx.y * 2 + which) * d + c] = sacc;
+    }
   }
 }
 __global__ void layernorm_bwd_reduce_k(const float* __restrict__ partials, float* __restrict__ dw,
@@ -240,27 +325,27 @@ __global__ void layernorm_bwd_reduce_k(const float* __restrict__ partials, float
   if (j < d) dw[j] += s;
   else db[j - d] += s;
 }
-// Number of row bands (= rows of `partials`) layernorm_bwd uses for a problem size.
+// Number of row splits (= rows of `partials`, each 2*d floats) layernorm_bwd uses.
 extern "C" int kh_layernorm_bwd_parts(int rows, int d) {
-  int parts = 296;
-  if (rows < parts * 8) parts = (rows + 7) / 8;
+  const int cb = (d + 63) / 64;
+  int parts = (592 + cb - 1) / cb;
+  const int by_rows = (rows + 63) / 64;
+  if (parts > by_rows) parts = by_rows;
   return parts < 1 ? 1 : parts;
 }
 extern "C" int kh_layernorm_bwd(const void* dy, const void* x, const void* w, const void* mean, const void* rstd,
                                 const void* dres, void* dx, void* dw, void* db, void* partials, int rows, int d,
                                 void* stream) {
-  if (d % 2) { kh_set_error("layernorm_bwd: d must be even"); return -1; }
-  const size_t smem = (size_t)LN_BWD_WARPS * 2 * d * sizeof(float);
-  if (smem > 220 * 1024) { kh_set_error("layernorm_bwd: d=%d needs %zu bytes of shared memory", d, smem); return -1; }
-  static size_t attr = 0;
-  if (smem > attr) { cudaFuncSetAttribute(layernorm_bwd_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
+  if (d % 8) { kh_set_error("layernorm_bwd: d must be a multiple of 8"); return -1; }
+  cudaStream_t st = (cudaStream_t)stream;
   const int parts = kh_layernorm_bwd_parts(rows, d);
-  const int rpc = (rows + parts - 1) / parts;
-  layernorm_bwd_k<<<parts, LN_BWD_WARPS * 32, smem, (cudaStream_t)stream>>>(
-      (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean, (const float*)rstd, (const bf16*)dres,
-      (bf16*)dx, (float*)partials, rows, d, rpc);
-  layernorm_bwd_reduce_k<<<cdiv(2 * d, 128), 128, 0, (cudaStream_t)stream>>>((const float*)partials, (float*)dw,
-                                                                             (float*)db, parts, d);
+  const int rps = (rows + parts - 1) / parts;
+  layernorm_bwd_dx_k<<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+                                                     (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows, d);
+  dim3 grid(cdiv(d, 64), parts);
+  layernorm_bwd_dwdb_k<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd,
+                                              (float*)partials, rows, d, rps);
+  layernorm_bwd_reduce_k<<<cdiv(2 * d, 128), 128, 0, st>>>((const float*)partials, (float*)dw, (float*)db, parts, d);
   KH_LAUNCH_CHECK("layernorm_bwd");
   return 0;
 }

@@ -90,7 +90,10 @@ class GPT:
         self.s_delta = torch.empty(cfg.batch, cfg.n_head // tp, cfg.seq, dtype=torch.float32, device=self.device)
         self.s_lnpart = torch.empty(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
                                     dtype=torch.float32, device=self.device)
-        self.s_tp = e(R, d) if tp > 1 else None
+        cuda = self.device.type == "cuda"
+        ncs = max(ops.colsum_scratch_elems(R, n) for n in (d, fo, 3 * dl)) if cuda else 1
+        self.s_colsum = torch.empty(ncs, dtype=torch.float32, device=self.device)
+        self.s_table = torch.empty(2 * cfg.vocab, dtype=torch.int32, device=self.device)
         self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.tp_allreduce = None      # callable(tensor) summing in place over the TP group
         self.skip_loss = False
@@ -295,10 +298,10 @@ class GPT:
         for l in reversed(range(cfg.n_layer)):
             a = s.layers[l]
             # x[l+1] = xmid + act @ Wfp^T + b
-            ops.colsum(dx, self.G(l, "fcproj_b"))
+            ops.colsum(dx, self.G(l, "fcproj_b"), scratch=self.s_colsum)
             ops.gemm(dx, a["act"], self.G(l, "fcproj_w"), a_mn=True, b_mn=True, accumulate=True)
             ops.gemm(dx, self.L(l, "fcproj_w"), self.s_dpre, b_mn=True, epi=ops.EPI_DGELU, aux=a["pre"])
-            ops.colsum(self.s_dpre, self.G(l, "fc_b"))
+            ops.colsum(self.s_dpre, self.G(l, "fc_b"), scratch=self.s_colsum)
             ops.gemm(self.s_dpre, a["ln2"], self.G(l, "fc_w"), a_mn=True, b_mn=True, accumulate=True)
             ops.gemm(self.s_dpre, self.L(l, "fc_w"), self.s_dln, b_mn=True)
             self._ar(self.s_dln)
@@ -306,11 +309,11 @@ class GPT:
                               self.G(l, "ln2_w"), self.G(l, "ln2_b"), self.s_lnpart)
             dx, other = other, dx
             # xmid = x + att @ Wp^T + b
-            ops.colsum(dx, self.G(l, "proj_b"))
+            ops.colsum(dx, self.G(l, "proj_b"), scratch=self.s_colsum)
             ops.gemm(dx, a["att"], self.G(l, "proj_w"), a_mn=True, b_mn=True, accumulate=True)
             ops.gemm(dx, self.L(l, "proj_w"), self.s_datt, b_mn=True)
             ops.flash_bwd(a["qkv"], a["att"], self.s_datt, a["lse"], self.s_dqkv, self.s_delta, B, T, Hl, hd)
-            ops.colsum(self.s_dqkv, self.G(l, "qkv_b"))
+            ops.colsum(self.s_dqkv, self.G(l, "qkv_b"), scratch=self.s_colsum)
             ops.gemm(self.s_dqkv, a["ln1"], self.G(l, "qkv_w"), a_mn=True, b_mn=True, accumulate=True)
             ops.gemm(self.s_dqkv, self.L(l, "qkv_w"), self.s_dln, b_mn=True)
             self._ar(self.s_dln)
@@ -318,7 +321,7 @@ class GPT:
                               self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
             dx, other = other, dx
         if self.first:
-            ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T)
+            ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T, table=self.s_table)
             return None
         return dx
 

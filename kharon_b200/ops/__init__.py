@@ -93,25 +93,44 @@ def embed_fwd(tok, pos, wte, wpe, out, T):
     return out
 
 
-def embed_bwd(tok, dx, dwte, dwpe, B, T):
-    """dwte[tok[r]] += dx[r]; dwpe[t] += sum_b dx[b, t] (fp32 grads, deterministic)."""
+_scratch = {}
+
+
+def _scratch_buf(device, nbytes):
+    """Small per-device scratch for callers that do not pass their own (tests, one-off calls)."""
+    key = (device.index, )
+    t = _scratch.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = t
+    return t
+
+
+def embed_bwd(tok, dx, dwte, dwpe, B, T, table=None):
+    """dwte[tok[r]] += dx[r]; dwpe[t] += sum_b dx[b, t] (fp32 grads, deterministic).  ``table`` is
+    int32 scratch of 2 * vocab entries."""
     if not dx.is_cuda:
         return ref.embed_bwd(tok, dx, dwte, dwpe, B, T)
     d = dx.shape[1]
     V = dwte.shape[0] if dwte is not None else 0
-    # the token table of one launch lives in shared memory: chunk long batches by sequences
-    max_rows = 48 * 1024
-    seq_per = max(1, max_rows // T)
-    for b0 in range(0, B, seq_per):
-        nb = min(seq_per, B - b0)
-        _chk(_lib().kh_embed_bwd(tok.data_ptr() + b0 * T * 4, dx.data_ptr() + b0 * T * d * 2, _p(dwte), _p(dwpe),
-                                 nb, T, d, V, _stream()), 2)
+    if table is None and dwte is not None:
+        table = _scratch_buf(dx.device, 8 * V)
+    _chk(_lib().kh_embed_bwd(tok.data_ptr(), dx.data_ptr(), _p(dwte), _p(dwpe), _p(table), B, T, d, V, _stream()), 3)
 
 
-def colsum(x, out, accumulate=True):
+def colsum_scratch_elems(rows, N):
+    return _lib().kh_colsum_splits(rows, N) * N if torch.cuda.is_available() else 0
+
+
+def colsum(x, out, accumulate=True, scratch=None):
+    """out[j] (+)= sum_r x[r, j]; ``scratch`` holds fp32 partial rows (colsum_scratch_elems)."""
     if not x.is_cuda:
         return ref.colsum(x, out, accumulate)
-    _chk(_lib().kh_colsum(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], int(accumulate), _stream()))
+    rows, N = x.shape
+    if scratch is None:
+        scratch = _scratch_buf(x.device, 4 * colsum_scratch_elems(rows, N))
+    _chk(_lib().kh_colsum(x.data_ptr(), x.stride(0), out.data_ptr(), scratch.data_ptr(), rows, N, int(accumulate),
+                          _stream()), 2)
 
 
 # ------------------------------------------------------------------------------ LayerNorm
@@ -139,7 +158,7 @@ def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
     assert partials.numel() >= layernorm_bwd_scratch_elems(rows, d)
     _chk(_lib().kh_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                  _p(dres), dx.data_ptr(), dw.data_ptr(), db.data_ptr(), partials.data_ptr(), rows, d,
-                                 _stream()), 2)
+                                 _stream()), 3)
 
 
 # -------------------------------------------------------------------------- cross-entropy

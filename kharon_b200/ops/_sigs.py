@@ -17,8 +17,9 @@ def declare(lib):
     _sig(lib, "kh_gemm_bf16", i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp,
          i32, f32, i32, i32, vp)
     _sig(lib, "kh_embed_fwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
-    _sig(lib, "kh_embed_bwd", i32, vp, vp, vp, vp, i32, i32, i32, i32, vp)
-    _sig(lib, "kh_colsum", i32, vp, i32, vp, i32, i32, i32, vp)
+    _sig(lib, "kh_embed_bwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
+    _sig(lib, "kh_colsum", i32, vp, i32, vp, vp, i32, i32, i32, vp)
+    _sig(lib, "kh_colsum_splits", i32, i32, i32)
     _sig(lib, "kh_layernorm_fwd", i32, vp, vp, vp, vp, vp, vp, i32, i32, vp)
     _sig(lib, "kh_layernorm_bwd_parts", i32, i32, i32)
     _sig(lib, "kh_layernorm_bwd", i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp)
