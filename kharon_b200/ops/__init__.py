@@ -227,3 +227,51 @@ def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
         return ref.flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd)
     _chk(_lib().kh_flash_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), dqkv.data_ptr(),
                              delta.data_ptr(), B, T, H, hd, qkv.stride(0), 1.0 / math.sqrt(hd), _stream()), 3)
+
+
+# ------------------------------------------------------------------------------ paged KV
+def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
+    """Scatter k, v of each new token into its block: pool layout [n_blocks, bs, H, hd]."""
+    if not qkv.is_cuda:
+        return ref.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
+    _chk(_lib().kh_append_kv(qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(),
+                             slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd, ntok, _stream()))
+
+
+def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx):
+    """Causal attention of each listed token over positions 0..pos of its own sequence, K/V read
+    through the block table."""
+    if not qkv.is_cuda:
+        return ref.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok)
+    _chk(_lib().kh_paged_attn(qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                              pos.data_ptr(), slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd,
+                              1.0 / math.sqrt(hd), ntok, max_ctx, _stream()))
+
+
+def gather_rows(x, rows, out, nseq):
+    if not x.is_cuda:
+        out[:nseq].copy_(x[rows[:nseq].long()])
+        return
+    _chk(_lib().kh_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), nseq, x.shape[1], _stream()))
+
+
+def copy_blocks(kc, vc, pairs, npairs):
+    """kc, vc: [n_layer, n_blocks, bs, H, hd]; copies block pairs[2i] -> pairs[2i+1] in all layers."""
+    if npairs == 0:
+        return
+    if not kc.is_cuda:
+        for i in range(npairs):
+            s, d = int(pairs[2 * i]), int(pairs[2 * i + 1])
+            kc[:, d].copy_(kc[:, s])
+            vc[:, d].copy_(vc[:, s])
+        return
+    _chk(_lib().kh_copy_blocks(kc.data_ptr(), vc.data_ptr(), pairs.data_ptr(), npairs, kc.shape[0],
+                               kc[0, 0].numel(), kc[0].numel(), _stream()))
+
+
+def sample(logits, V, temperature, seed, step, rep, out, nseq):
+    """Greedy argmax (temperature <= 0) or a categorical draw from softmax(logits / T), on device."""
+    if not logits.is_cuda:
+        return ref.sample(logits, V, temperature, seed, step, rep, out, nseq)
+    _chk(_lib().kh_sample(logits.data_ptr(), logits.stride(0), V, float(temperature), int(seed), int(step), rep,
+                          out.data_ptr(), nseq, _stream()))

@@ -164,3 +164,38 @@ def flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd):
     dk = ds.transpose(-1, -2) @ q
     res = torch.stack([dq, dk, dv], 0).permute(1, 3, 0, 2, 4).reshape(B * T, 3 * d)
     dqkv[:, : 3 * d] = res.to(dqkv.dtype)
+
+
+def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
+    d = H * hd
+    for t in range(ntok):
+        p = int(pos[t])
+        blk = int(btab[int(slot[t]), p // bs])
+        kc[blk, p % bs] = qkv[t, d:2 * d].view(H, hd)
+        vc[blk, p % bs] = qkv[t, 2 * d:3 * d].view(H, hd)
+
+
+def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok):
+    d = H * hd
+    for t in range(ntok):
+        ctx = int(pos[t]) + 1
+        bt = btab[int(slot[t])].long()
+        nb = (ctx + bs - 1) // bs
+        K = kc[bt[:nb]].reshape(nb * bs, H, hd)[:ctx].float()
+        Vv = vc[bt[:nb]].reshape(nb * bs, H, hd)[:ctx].float()
+        q = qkv[t, :d].float().view(H, hd)
+        s = torch.einsum("he,jhe->hj", q, K) / math.sqrt(hd)
+        p = torch.softmax(s, -1)
+        out[t] = torch.einsum("hj,jhe->he", p, Vv).reshape(d).to(out.dtype)
+
+
+def sample(logits, V, temperature, seed, step, rep, out, nseq):
+    lg = logits[:nseq, :V].float()
+    if temperature <= 0:
+        idx = lg.argmax(-1)
+        out[:nseq * rep].copy_(idx.repeat_interleave(rep).to(out.dtype))
+        return
+    g = torch.Generator().manual_seed((int(seed) * 1000003 + int(step)) & 0x7FFFFFFF)
+    p = torch.softmax(lg / temperature, -1)
+    idx = torch.multinomial(p, rep, replacement=True, generator=g)
+    out[:nseq * rep].copy_(idx.reshape(-1).to(out.dtype))

@@ -160,10 +160,11 @@ def test_embed_and_colsum():
     dwte2 = torch.ones(V, d, device=DEV); dwpe2 = torch.ones(T, d, device=DEV)
     ref.embed_bwd(tok, dx, dwte2, dwpe2, B, T)
     assert relerr(dwte, dwte2) < 1e-5 and relerr(dwpe, dwpe2) < 1e-5
-    x = _rand(777, 322)
-    cs = torch.ones(322, device=DEV)
-    ops.colsum(x, cs, accumulate=True)
-    assert relerr(cs, 1 + x.float().sum(0)) < 1e-5
+    for rows, N in [(777, 322), (4096, 2048), (100, 64)]:
+        x = _rand(rows, (N + 7) // 8 * 8)[:, :N]
+        cs = torch.ones(N, device=DEV)
+        ops.colsum(x, cs, accumulate=True)
+        assert relerr(cs, 1 + x.float().sum(0)) < 1e-5
 
 
 @pytest.mark.parametrize("B,T,H,hd", [(2, 256, 4, 64), (1, 512, 2, 128), (3, 64, 2, 64), (2, 200, 2, 128), (1, 1024, 1, 64)])
