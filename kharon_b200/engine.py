@@ -177,7 +177,11 @@ class TrainEngine:
         if self.fused is not None and getattr(self.fused, "zero_step", None) is not None:
             self.fused.zero_step(self)
             return
-        dist.reduce_scatter_tensor(self.g_shard, ps.g, op=dist.ReduceOp.AVG, group=grp)
+        if dist.get_backend(grp) == "nccl":
+            dist.reduce_scatter_tensor(self.g_shard, ps.g, op=dist.ReduceOp.AVG, group=grp)
+        else:   # CPU ranks (gloo) have no reduce-scatter / AVG: same result via all-reduce
+            dist.all_reduce(ps.g, group=grp)
+            self.g_shard.copy_(ps.g[self.lo:self.lo + self.shard] / self.mesh.c.dp)
         m.step += 1
         lo, hi = self.lo, self.lo + self.shard
         wb = None if ps.wb is ps.w else ps.wb[lo:hi]
@@ -204,11 +208,15 @@ class TrainEngine:
         return prefix if self.mesh.world == 1 else "%s.r%d" % (prefix, self.mesh.rank)
 
     def save(self, prefix, rng_state=0):
+        """One CKP1 file per rank (``<prefix>.r<rank>`` on more than one rank): the rank's full
+        fp32 parameter arena plus its moments -- under ZeRO-1 only its shard of them."""
         self.gather_master()
-        self.model.save(self.ckpt_path(prefix), rng_state)
+        ps = self.model.params
+        self.model.save(self.ckpt_path(prefix), rng_state, moments=(ps.m, ps.v) if self.zero else None)
 
     def load(self, prefix):
-        rng = self.model.load(self.ckpt_path(prefix))
+        ps = self.model.params
+        rng = self.model.load(self.ckpt_path(prefix), moments=(ps.m, ps.v) if self.zero else None)
         return rng
 
     def memory_report(self):

@@ -72,8 +72,8 @@ def test_engine_gpu_matches_cpu_greedy_and_graph_replay():
     cpu = GPT(cfg, "cpu", torch.float32); cpu.init_weights(1234); cpu.params.w.mul_(6.0)
     gpu = GPT(cfg, "cuda", torch.bfloat16); gpu.init_weights(1234); gpu.params.w.mul_(6.0); gpu.sync_bf16()
     prompts = [[5, 17, 3, 9], [9, 1, 44, 23, 8, 61, 2], [70, 1]]
-    e1 = InferEngine(cpu, block_size=8, max_seqs=4)
-    e2 = InferEngine(gpu, block_size=8, max_seqs=4)
+    e1 = InferEngine(cpu, block_size=8, max_seqs=5)
+    e2 = InferEngine(gpu, block_size=8, max_seqs=5)
     a, _, _ = e1.generate(prompts, 10)
     b, st, _ = e2.generate(prompts, 10)
     b2, _, _ = e2.generate(prompts, 10)          # second pass replays the captured graphs

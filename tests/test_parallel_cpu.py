@@ -1,0 +1,173 @@
+"""Distributed code paths on CPU ranks (gloo, one process per rank): tensor, pipeline, ZeRO-1
+data parallel and their combination must reproduce the single-process loss trajectory and
+weights; per-rank checkpoints must resume bit-exactly; a rank that raises must surface as an
+error on its peers instead of a hang.  (The reference could only check this by eye on a cluster,
+scripts/ice_m4_tp.sbatch .. ice_m7_3d.sbatch.)"""
+import os
+import socket
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KW = dict(layers=4, d_model=64, heads=4, vocab=128, seq=16, mbatch=2, n_micro=4, device="cpu", dtype=torch.float32,
+          lr=1e-2, wd=0.1, eps=1e-3)   # a large eps keeps Adam from amplifying summation-order noise
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _batches(dp_rank, steps, ntok, vocab):
+    from kharon_b200.utils.rng import Rng
+    r = Rng(100 + dp_rank)
+    return [r.batch(ntok, vocab) for _ in range(steps)]
+
+
+def _single(steps, dp=1):
+    """Single-process oracle: with dp replicas the global batch is their concatenation."""
+    from kharon_b200.engine import TrainEngine
+    kw = dict(KW)
+    kw["n_micro"] = KW["n_micro"] * dp
+    e = TrainEngine(**kw)
+    per = [_batches(r, steps, KW["n_micro"] * KW["mbatch"] * KW["seq"], KW["vocab"]) for r in range(dp)]
+    losses = []
+    for s in range(steps):
+        idx = torch.cat([per[r][s][0] for r in range(dp)])
+        tgt = torch.cat([per[r][s][1] for r in range(dp)])
+        e.train_step(idx, tgt)
+        losses.append(e.loss())
+    return e, losses
+
+
+def _worker(rank, world, port, tp, pp, dp, steps, out_dir, mode):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from kharon_b200.engine import TrainEngine
+    from kharon_b200.parallel.mesh import Mesh
+    mesh = Mesh(tp, pp, dp, timeout_s=60)
+    e = TrainEngine(mesh=mesh, **KW)
+    data = _batches(mesh.c.dp_rank, steps, e.tokens_per_step, KW["vocab"])
+    losses = []
+    prefix = os.path.join(out_dir, "ck")
+    if mode == "resume":
+        e.load(prefix)
+    for s in range(e.model.step, steps):
+        e.train_step(*data[s])
+        losses.append(e.loss() if mesh.c.last else None)
+        if mode == "save_half" and e.model.step == steps // 2:
+            e.save(prefix)
+            break
+    e.gather_master()
+    torch.save(dict(losses=losses, w=e.model.params.w.clone(), coord=(mesh.c.dp_rank, mesh.c.stage, mesh.c.tp_rank),
+                    offsets=e.model.params.offsets, shapes=e.model.params.shapes, step=e.model.step),
+               os.path.join(out_dir, "%s_r%d.pt" % (mode, rank)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _launch(tp, pp, dp, steps, out_dir, mode="run"):
+    world = tp * pp * dp
+    mp.spawn(_worker, args=(world, _free_port(), tp, pp, dp, steps, out_dir, mode), nprocs=world, join=True)
+    return [torch.load(os.path.join(out_dir, "%s_r%d.pt" % (mode, r)), weights_only=False) for r in range(world)]
+
+
+def _view(res, name):
+    o = res["offsets"][name]
+    shp = res["shapes"][name]
+    n = 1
+    for k in shp:
+        n *= k
+    return res["w"][o:o + n].view(shp)
+
+
+@pytest.mark.parametrize("tp,pp,dp", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (1, 2, 2)])
+def test_mesh_matches_single_process(tp, pp, dp):
+    steps = 3
+    ref_e, ref_losses = _single(steps, dp)
+    with tempfile.TemporaryDirectory() as d:
+        res = _launch(tp, pp, dp, steps, d)
+    last = [r for r in res if r["coord"][1] == pp - 1]
+    for r in last:
+        if dp == 1:
+            assert max(abs(a - b) for a, b in zip(r["losses"], ref_losses)) < 2e-5
+    if dp > 1:   # each replica reports the loss of its own half; their mean is the global loss
+        for s in range(steps):
+            vals = [r["losses"][s] for r in last if r["coord"][2] == 0]
+            assert abs(sum(vals) / len(vals) - ref_losses[s]) < 2e-5
+    # weights after 3 steps: compare shards of a few tensors with the single-process model
+    P = ref_e.model.params.p
+    nl = KW["layers"] // pp
+    d_ = KW["d_model"]
+    for r in res:
+        _, stage, t = r["coord"]
+        gl = stage * nl      # global index of the stage's first layer
+        q = _view(r, "l0.qkv_w")
+        full = P["l%d.qkv_w" % gl]
+        want = torch.cat([full[k * d_ + t * d_ // tp: k * d_ + (t + 1) * d_ // tp] for k in range(3)], 0)
+        assert torch.allclose(q, want, rtol=1e-4, atol=2e-5)
+        fp = _view(r, "l%d.fcproj_w" % (nl - 1))
+        want = P["l%d.fcproj_w" % (gl + nl - 1)][:, t * 4 * d_ // tp:(t + 1) * 4 * d_ // tp]
+        assert torch.allclose(fp, want, rtol=1e-4, atol=2e-5)
+        if stage == 0:
+            assert torch.allclose(_view(r, "wte"), P["wte"], rtol=1e-4, atol=2e-5)
+        if stage == pp - 1 and pp > 1:      # tied copy on the last stage stays equal to the embedding
+            assert torch.allclose(_view(r, "head_w"), P["wte"], rtol=1e-4, atol=2e-5)
+
+
+def test_per_rank_checkpoint_resume_is_bit_exact():
+    tp, pp, dp, steps = 1, 2, 2, 4
+    with tempfile.TemporaryDirectory() as d:
+        full = _launch(tp, pp, dp, steps, d, "run")
+        _launch(tp, pp, dp, steps, d, "save_half")
+        assert os.path.exists(os.path.join(d, "ck.r3"))
+        res = _launch(tp, pp, dp, steps, d, "resume")
+    for a, b in zip(full, res):
+        assert b["step"] == steps
+        assert torch.equal(a["w"], b["w"])
+        if a["losses"][-1] is not None:
+            assert a["losses"][-1] == b["losses"][-1]
+
+
+def _failing_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from kharon_b200.utils.watchdog import Heartbeat
+    hb = Heartbeat(rank, world, interval_s=0.2, timeout_s=2.0)
+    t = torch.ones(4)
+    dist.all_reduce(t)
+    if rank == 1:
+        hb.stop()
+        os._exit(3)               # the rank dies between steps, with nothing in flight
+    import time
+    deadline = time.time() + 20
+    dead = []
+    while time.time() < deadline and not dead:
+        time.sleep(0.3)
+        dead = hb.dead_ranks()
+    open(os.path.join(out_dir, "seen_%d" % rank), "w").write(",".join(map(str, dead)))
+    hb.stop()
+    os._exit(0 if dead == [1] else 4)
+
+
+def test_dead_rank_is_detected_on_the_host():
+    with tempfile.TemporaryDirectory() as d:
+        ctx = mp.spawn(_failing_worker, args=(3, _free_port(), d), nprocs=3, join=False)
+        for p in ctx.processes:
+            p.join(60)
+        codes = [p.exitcode for p in ctx.processes]
+        assert codes[1] == 3 and codes[0] == 0 and codes[2] == 0, codes
+        assert open(os.path.join(d, "seen_0")).read() == "1"
