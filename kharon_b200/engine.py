@@ -98,7 +98,8 @@ class TrainEngine:
             self.lo = c.dp_rank * self.shard
             ps.alloc_moments(self.shard)
             self.g_shard = torch.zeros(self.shard, dtype=torch.float32, device=dev)
-        self.timers = {}
+        self.plans = {}
+        self.use_plans = self.device.type == "cuda"
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -115,8 +116,24 @@ class TrainEngine:
     def _stage_input(self, mb):
         R = self.mbatch * self.seq
         s = self.model.slots[mb % self.n_slots]
-        s.tok.copy_(self.tok_dev[mb * R:(mb + 1) * R])
-        s.tgt.copy_(self.tgt_dev[mb * R:(mb + 1) * R])
+        ops.plan_call(s.tok.copy_, self.tok_dev[mb * R:(mb + 1) * R])
+        ops.plan_call(s.tgt.copy_, self.tgt_dev[mb * R:(mb + 1) * R])
+
+    def _compute(self, key, fn):
+        """Run one forward/backward of the schedule.  On a GPU the first execution records the
+        exact native calls (buffers are static per micro-batch slot) and later steps replay them,
+        which removes the per-launch Python marshalling from the critical path."""
+        if not self.use_plans:
+            return fn()
+        hit = self.plans.get(key)
+        if hit is not None:
+            hit[0].replay()
+            return hit[1]
+        plan = ops.LaunchPlan()
+        with plan.record():
+            out = fn()
+        self.plans[key] = (plan, out)
+        return out
 
     # ------------------------------------------------------------------ one step
     def train_step(self, idx, tgt):
@@ -132,14 +149,14 @@ class TrainEngine:
         n_loss = 0
         for op, a0, a1 in self.schedule:
             if op == PP_FWD:
-                self._stage_input(a0)
-                y = m.forward(slot=a1, x_in=cur_act, compute_loss=False)
-                out_act[a0] = y
+                out_act[a0] = self._compute(("F", a0, a1), lambda: (
+                    self._stage_input(a0), m.forward(slot=a1, x_in=cur_act, compute_loss=False))[1])
             elif op == PP_BWD:
                 dxo = None if c.last else cur_grad
-                g = m.backward(slot=a1, dx_out=dxo, inv_mb=inv, loss_scale=inv, accumulate_loss=n_loss > 0)
+                first_loss = n_loss == 0
+                in_grad[a0] = self._compute(("B", a0, a1), lambda: m.backward(
+                    slot=a1, dx_out=dxo, inv_mb=inv, loss_scale=inv, accumulate_loss=not first_loss))
                 n_loss += 1
-                in_grad[a0] = g
             elif op == PP_RECV_ACT:
                 cur_act = self.recv_act[a0 & 1]
                 self._p2p([dist.P2POp(dist.irecv, cur_act, c.prev_rank)])

@@ -206,7 +206,7 @@ class GPT:
     # ------------------------------------------------------------------ forward
     def _ar(self, t):
         if self.tp_allreduce is not None:
-            self.tp_allreduce(t)
+            ops.plan_call(self.tp_allreduce, t)
 
     def forward_layers(self, s: _Slot):
         cfg, tp = self.cfg, self.tp
@@ -253,7 +253,7 @@ class GPT:
         if self.first:
             ops.embed_fwd(s.tok, None, self.params.c["wte"], self.params.c["wpe"], s.x[0], cfg.seq)
         else:
-            s.x[0].copy_(x_in)
+            ops.plan_call(s.x[0].copy_, x_in)
         self.forward_layers(s)
         if not self.last:
             return s.x[cfg.n_layer]
@@ -294,7 +294,7 @@ class GPT:
             ops.layernorm_bwd(self.s_dln, s.x[cfg.n_layer], P["lnf_w"], s.meanf, s.rstdf, None, dx, Gd["lnf_w"],
                               Gd["lnf_b"], self.s_lnpart)
         else:
-            dx.copy_(dx_out)
+            ops.plan_call(dx.copy_, dx_out)
         for l in reversed(range(cfg.n_layer)):
             a = s.layers[l]
             # x[l+1] = xmid + act @ Wfp^T + b

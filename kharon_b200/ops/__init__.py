@@ -33,11 +33,73 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+#: when a list, every native call is also appended as (function, args, launches) -- see ``LaunchPlan``
+_recording = None
+
+
 def _chk(rc, n=1):
     global launch_count
     if rc != 0:
         raise KernelError(_lib().kh_cuda_last_error().decode())
     launch_count += n
+
+
+def _call(fn, n, *args):
+    """Invoke a native entry point; remember the exact call when a plan is being recorded."""
+    if _recording is not None:
+        _recording.append((fn, args, n))
+    _chk(fn(*args), n)
+
+
+class LaunchPlan:
+    """Record-and-replay of a fixed sequence of native calls.
+
+    A training micro-batch issues the same kernels on the same static buffers every step, so
+    the Python-side argument marshalling (shape checks, data_ptr/stride lookups) only needs to
+    happen once: ``with plan.record():`` runs the code normally while logging each native call
+    (and any host callable registered through ``plan_call``, e.g. a collective); ``plan.replay()``
+    re-issues exactly those calls.  The stream handle is part of the recorded arguments, so a
+    plan must be replayed on the stream it was recorded on.
+    """
+
+    def __init__(self):
+        self.calls = None
+
+    def record(self):
+        plan = self
+
+        class _Ctx:
+            def __enter__(self_):
+                global _recording
+                assert _recording is None, "nested launch-plan recording"
+                _recording = []
+
+            def __exit__(self_, et, ev, tb):
+                global _recording
+                calls, _recording = _recording, None
+                if et is None:
+                    plan.calls = calls
+                return False
+        return _Ctx()
+
+    def replay(self):
+        global launch_count
+        err = 0
+        for fn, args, n in self.calls:
+            if n < 0:
+                fn(*args)            # host callable
+            else:
+                err |= fn(*args)
+                launch_count += n
+        if err:
+            raise KernelError(_lib().kh_cuda_last_error().decode())
+
+
+def plan_call(fn, *args):
+    """Run a host-side callable (a collective, a copy) and make it part of the plan being recorded."""
+    if _recording is not None:
+        _recording.append((fn, args, -1))
+    fn(*args)
 
 
 def _p(t):
@@ -76,10 +138,10 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, accumulate=False, epi=EPI_NONE, b
         return ref.gemm(a, b, out, a_mn, b_mn, accumulate, epi, bias, aux, alpha)
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
-    _chk(_lib().kh_gemm_bf16(a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+    _call(_lib().kh_gemm_bf16, 1, a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                              out.data_ptr(), out.stride(0), M, N, K, int(out.dtype == torch.float32),
                              int(accumulate), epi, _p(bias), _p(aux), aux.stride(0) if aux is not None else 0,
-                             float(alpha), block_n, max_ctas, _stream()))
+                             float(alpha), block_n, max_ctas, _stream())
     return out
 
 
@@ -88,8 +150,8 @@ def embed_fwd(tok, pos, wte, wpe, out, T):
     if not out.is_cuda:
         return ref.embed_fwd(tok, pos, wte, wpe, out, T)
     rows, d = out.shape
-    _chk(_lib().kh_embed_fwd(tok.data_ptr(), _p(pos), wte.data_ptr(), wpe.data_ptr(), out.data_ptr(), rows, d,
-                             wpe.shape[0] if pos is not None else T, wte.shape[0], _stream()))
+    _call(_lib().kh_embed_fwd, 1, tok.data_ptr(), _p(pos), wte.data_ptr(), wpe.data_ptr(), out.data_ptr(), rows, d,
+                             wpe.shape[0] if pos is not None else T, wte.shape[0], _stream())
     return out
 
 
@@ -115,7 +177,7 @@ def embed_bwd(tok, dx, dwte, dwpe, B, T, table=None):
     V = dwte.shape[0] if dwte is not None else 0
     if table is None and dwte is not None:
         table = _scratch_buf(dx.device, 8 * V)
-    _chk(_lib().kh_embed_bwd(tok.data_ptr(), dx.data_ptr(), _p(dwte), _p(dwpe), _p(table), B, T, d, V, _stream()), 3)
+    _call(_lib().kh_embed_bwd, 3, tok.data_ptr(), dx.data_ptr(), _p(dwte), _p(dwpe), _p(table), B, T, d, V, _stream())
 
 
 def colsum_scratch_elems(rows, N):
@@ -129,8 +191,8 @@ def colsum(x, out, accumulate=True, scratch=None):
     rows, N = x.shape
     if scratch is None:
         scratch = _scratch_buf(x.device, 4 * colsum_scratch_elems(rows, N))
-    _chk(_lib().kh_colsum(x.data_ptr(), x.stride(0), out.data_ptr(), scratch.data_ptr(), rows, N, int(accumulate),
-                          _stream()), 2)
+    _call(_lib().kh_colsum, 2, x.data_ptr(), x.stride(0), out.data_ptr(), scratch.data_ptr(), rows, N, int(accumulate),
+                          _stream())
 
 
 # ------------------------------------------------------------------------------ LayerNorm
@@ -138,8 +200,8 @@ def layernorm_fwd(x, w, b, y, mean=None, rstd=None):
     if not x.is_cuda:
         return ref.layernorm_fwd(x, w, b, y, mean, rstd)
     rows, d = x.shape
-    _chk(_lib().kh_layernorm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), _p(mean), _p(rstd), rows, d,
-                                 _stream()))
+    _call(_lib().kh_layernorm_fwd, 1, x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), _p(mean), _p(rstd), rows, d,
+                                 _stream())
     return y
 
 
@@ -156,9 +218,9 @@ def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
         return ref.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db)
     rows, d = x.shape
     assert partials.numel() >= layernorm_bwd_scratch_elems(rows, d)
-    _chk(_lib().kh_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+    _call(_lib().kh_layernorm_bwd, 3, dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                  _p(dres), dx.data_ptr(), dw.data_ptr(), db.data_ptr(), partials.data_ptr(), rows, d,
-                                 _stream()), 3)
+                                 _stream())
 
 
 # -------------------------------------------------------------------------- cross-entropy
@@ -167,8 +229,8 @@ def xent(logits, V, target, *, coef=None, uniform=1.0, rowloss=None, prob=None, 
     with ``scale_r * (softmax - onehot)`` (scale_r = coef[r] or ``uniform``)."""
     if not logits.is_cuda:
         return ref.xent(logits, V, target, coef, uniform, rowloss, prob, write_grad)
-    _chk(_lib().kh_xent(logits.data_ptr(), logits.stride(0), V, target.data_ptr(), _p(coef), float(uniform),
-                        _p(rowloss), _p(prob), int(write_grad), logits.shape[0], _stream()))
+    _call(_lib().kh_xent, 1, logits.data_ptr(), logits.stride(0), V, target.data_ptr(), _p(coef), float(uniform),
+                        _p(rowloss), _p(prob), int(write_grad), logits.shape[0], _stream())
 
 
 def sum_f32(x, out, scale=1.0, accumulate=False):
@@ -176,7 +238,7 @@ def sum_f32(x, out, scale=1.0, accumulate=False):
         s = x.double().sum().float() * scale
         out[0] = out[0] + s if accumulate else s
         return
-    _chk(_lib().kh_sum_f32(x.data_ptr(), x.numel(), float(scale), out.data_ptr(), int(accumulate), _stream()))
+    _call(_lib().kh_sum_f32, 1, x.data_ptr(), x.numel(), float(scale), out.data_ptr(), int(accumulate), _stream())
 
 
 # ---------------------------------------------------------------------------------- AdamW
@@ -187,27 +249,27 @@ def adamw(p, g, m, v, pb, *, lr, beta1, beta2, eps, wd, step, grad_scale=1.0, ze
     bc2 = 1.0 - beta2 ** step
     if not p.is_cuda:
         return ref.adamw(p, g, m, v, pb, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, zero_grad)
-    _chk(_lib().kh_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _p(pb), p.numel(), lr, beta1, beta2,
-                         eps, wd, bc1, bc2, grad_scale, int(zero_grad), _stream()))
+    _call(_lib().kh_adamw, 1, p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _p(pb), p.numel(), lr, beta1, beta2,
+                         eps, wd, bc1, bc2, grad_scale, int(zero_grad), _stream())
 
 
 def cast_f32_bf16(x, y):
     if not x.is_cuda:
         y.copy_(x)
         return
-    _chk(_lib().kh_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), _stream()))
+    _call(_lib().kh_cast_f32_bf16, 1, x.data_ptr(), y.data_ptr(), x.numel(), _stream())
 
 
 def add_bf16(a, b, c):
     if not a.is_cuda:
         c.copy_((a.float() + b.float()))
         return
-    _chk(_lib().kh_add_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), a.numel(), _stream()))
+    _call(_lib().kh_add_bf16, 1, a.data_ptr(), b.data_ptr(), c.data_ptr(), a.numel(), _stream())
 
 
 def flush_l2(buf):
     """Overwrite ``buf`` (a CUDA tensor larger than L2) so the next kernel starts cold."""
-    _chk(_lib().kh_fill_u32(buf.data_ptr(), buf.numel() * buf.element_size() // 4, 0, _stream()))
+    _call(_lib().kh_fill_u32, 1, buf.data_ptr(), buf.numel() * buf.element_size() // 4, 0, _stream())
 
 
 # ------------------------------------------------------------------------------ attention
@@ -216,8 +278,8 @@ def flash_fwd(qkv, out, lse, B, T, H, hd):
     head-major inside each); writes ``out`` [B*T, H*hd] and ``lse`` [B, H, T] (fp32)."""
     if not qkv.is_cuda:
         return ref.flash_fwd(qkv, out, lse, B, T, H, hd)
-    _chk(_lib().kh_flash_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, hd, qkv.stride(0),
-                             1.0 / math.sqrt(hd), _stream()))
+    _call(_lib().kh_flash_fwd, 1, qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, hd, qkv.stride(0),
+                             1.0 / math.sqrt(hd), _stream())
 
 
 def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
@@ -225,8 +287,8 @@ def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
     ``delta`` [B, H, T] fp32 is scratch for rowsum(dO * O)."""
     if not qkv.is_cuda:
         return ref.flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd)
-    _chk(_lib().kh_flash_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), dqkv.data_ptr(),
-                             delta.data_ptr(), B, T, H, hd, qkv.stride(0), 1.0 / math.sqrt(hd), _stream()), 3)
+    _call(_lib().kh_flash_bwd, 3, qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), dqkv.data_ptr(),
+                             delta.data_ptr(), B, T, H, hd, qkv.stride(0), 1.0 / math.sqrt(hd), _stream())
 
 
 # ------------------------------------------------------------------------------ paged KV
@@ -234,8 +296,8 @@ def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
     """Scatter k, v of each new token into its block: pool layout [n_blocks, bs, H, hd]."""
     if not qkv.is_cuda:
         return ref.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
-    _chk(_lib().kh_append_kv(qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(),
-                             slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd, ntok, _stream()))
+    _call(_lib().kh_append_kv, 1, qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(),
+                             slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd, ntok, _stream())
 
 
 def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx):
@@ -243,16 +305,16 @@ def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx):
     through the block table."""
     if not qkv.is_cuda:
         return ref.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok)
-    _chk(_lib().kh_paged_attn(qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+    _call(_lib().kh_paged_attn, 1, qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
                               pos.data_ptr(), slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd,
-                              1.0 / math.sqrt(hd), ntok, max_ctx, _stream()))
+                              1.0 / math.sqrt(hd), ntok, max_ctx, _stream())
 
 
 def gather_rows(x, rows, out, nseq):
     if not x.is_cuda:
         out[:nseq].copy_(x[rows[:nseq].long()])
         return
-    _chk(_lib().kh_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), nseq, x.shape[1], _stream()))
+    _call(_lib().kh_gather_rows, 1, x.data_ptr(), rows.data_ptr(), out.data_ptr(), nseq, x.shape[1], _stream())
 
 
 def copy_blocks(kc, vc, pairs, npairs):
@@ -265,13 +327,13 @@ def copy_blocks(kc, vc, pairs, npairs):
             kc[:, d].copy_(kc[:, s])
             vc[:, d].copy_(vc[:, s])
         return
-    _chk(_lib().kh_copy_blocks(kc.data_ptr(), vc.data_ptr(), pairs.data_ptr(), npairs, kc.shape[0],
-                               kc[0, 0].numel(), kc[0].numel(), _stream()))
+    _call(_lib().kh_copy_blocks, 1, kc.data_ptr(), vc.data_ptr(), pairs.data_ptr(), npairs, kc.shape[0],
+                               kc[0, 0].numel(), kc[0].numel(), _stream())
 
 
 def sample(logits, V, temperature, seed, step, rep, out, nseq):
     """Greedy argmax (temperature <= 0) or a categorical draw from softmax(logits / T), on device."""
     if not logits.is_cuda:
         return ref.sample(logits, V, temperature, seed, step, rep, out, nseq)
-    _chk(_lib().kh_sample(logits.data_ptr(), logits.stride(0), V, float(temperature), int(seed), int(step), rep,
-                          out.data_ptr(), nseq, _stream()))
+    _call(_lib().kh_sample, 1, logits.data_ptr(), logits.stride(0), V, float(temperature), int(seed), int(step), rep,
+                          out.data_ptr(), nseq, _stream())
