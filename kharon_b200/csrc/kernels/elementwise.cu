@@ -71,19 +71,44 @@ __global__ void embed_bwd_index_k(const int* __restrict__ tok, int* __restrict__
 }
 __global__ void embed_bwd_wte_k(const int* __restrict__ tok, const bf16* __restrict__ dx, float* __restrict__ dwte,
                                 const int* __restrict__ first, const int* __restrict__ cnt, int rows, int d, int V) {
+  __shared__ int s_list[64];
+  __shared__ int s_n;
   const int r = blockIdx.x;
   const int t = tok[r];
   if (t < 0 || t >= V || first[t] != r) return;
   const int dup = cnt[t];
+  int n_list = 0;
+  if (dup > 1) {
+    // warp 0 collects the later rows with the same id, in row order (ballot + prefix popcount)
+    if (threadIdx.x < 32) {
+      int n = 0;
+      for (int base = r + 1; base < rows && n < dup - 1; base += 32) {
+        const int i = base + threadIdx.x;
+        const bool hit = i < rows && tok[i] == t;
+        const unsigned mask = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+          const int at = n + __popc(mask & ((1u << threadIdx.x) - 1));
+          if (at < 64) s_list[at] = i;
+        }
+        n += __popc(mask);
+      }
+      if (threadIdx.x == 0) s_n = n;
+    }
+    __syncthreads();
+    n_list = s_n;
+  }
   for (int e = threadIdx.x * 2; e < d; e += blockDim.x * 2) {
     float2 acc = unpack_bf16(*reinterpret_cast<const uint32_t*>(dx + (size_t)r * d + e));
-    if (dup > 1) {
-      int left = dup - 1;
-      for (int i = r + 1; i < rows && left > 0; i++)
+    if (n_list <= 64) {
+      for (int k = 0; k < n_list; k++) {
+        float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dx + (size_t)s_list[k] * d + e));
+        acc.x += v.x; acc.y += v.y;
+      }
+    } else {   // very frequent id: plain ordered scan
+      for (int i = r + 1; i < rows; i++)
         if (tok[i] == t) {
           float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dx + (size_t)i * d + e));
           acc.x += v.x; acc.y += v.y;
-          left--;
         }
     }
     float2* o = reinterpret_cast<float2*>(dwte + (size_t)t * d + e);
@@ -119,12 +144,16 @@ extern "C" int kh_embed_bwd(const void* tok, const void* dx, void* dwte, void* d
 }
 
 // ------------------------------------------------------------------------------ column sum
-// out[j] (+)= sum_r x[r, j], two deterministic stages.  Stage 1: CTA (column block of 64, row
-// split s) sums its rows with 16-byte loads (8 threads span the 64 columns, 32 row lanes) and
-// writes one partial row to `scratch` [splits, N]; stage 2 adds the splits in index order.
-__global__ void colsum_part_k(const bf16* __restrict__ x, int ld, float* __restrict__ scratch, int rows, int N,
-                              int rows_per_split) {
+// out[j] (+)= sum_r x[r, j], deterministic.  CTA (column block of 64, row split s) sums its rows
+// with 16-byte loads (8 threads span the 64 columns, 32 row lanes) and writes one partial row
+// to `scratch`; the CTA that finishes last for a column block (ticket counter) adds the splits
+// in index order, so the result does not depend on which CTA that is.
+// scratch layout: [KH_COUNTER_SLOTS ints, zero between launches][splits x N floats].
+#define KH_COUNTER_SLOTS 1024
+__global__ void colsum_k(const bf16* __restrict__ x, int ld, float* __restrict__ out, int* __restrict__ counters,
+                         float* __restrict__ scratch, int rows, int N, int rows_per_split, int accumulate) {
   __shared__ float part[32][65];
+  __shared__ int s_last;
   const int cg = threadIdx.x & 7, rg = threadIdx.x >> 3;
   const int col = blockIdx.x * 64 + cg * 8;
   const int r0 = blockIdx.y * rows_per_split, r1 = min(rows, r0 + rows_per_split);
@@ -144,22 +173,25 @@ __global__ void colsum_part_k(const bf16* __restrict__ x, int ld, float* __restr
 #pragma unroll
   for (int k = 0; k < 8; k++) part[rg][cg * 8 + k] = acc[k];
   __syncthreads();
-  if (threadIdx.x < 64) {
-    const int c = blockIdx.x * 64 + threadIdx.x;
-    if (c < N) {
-      float s = 0.f;
+  const int c = blockIdx.x * 64 + threadIdx.x;
+  if (threadIdx.x < 64 && c < N) {
+    float sacc = 0.f;
 #pragma unroll
-      for (int k = 0; k < 32; k++) s += part[k][threadIdx.x];
-      scratch[(size_t)blockIdx.y * N + c] = s;
-    }
+    for (int k = 0; k < 32; k++) sacc += part[k][threadIdx.x];
+    scratch[(size_t)blockIdx.y * N + c] = sacc;
   }
-}
-__global__ void colsum_final_k(const float* __restrict__ scratch, float* __restrict__ out, int splits, int N, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
-  float s = accumulate ? out[c] : 0.f;
-  for (int k = 0; k < splits; k++) s += scratch[(size_t)k * N + c];
-  out[c] = s;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(counters + blockIdx.x, 1) == (int)gridDim.y - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 64 && c < N) {
+    float sacc = accumulate ? out[c] : 0.f;
+    for (int k = 0; k < (int)gridDim.y; k++) sacc += __ldcg(scratch + (size_t)k * N + c);
+    out[c] = sacc;
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 extern "C" int kh_colsum_splits(int rows, int N) {
   const int cb = (N + 63) / 64;
@@ -168,13 +200,16 @@ extern "C" int kh_colsum_splits(int rows, int N) {
   if (splits > max_by_rows) splits = max_by_rows;
   return splits < 1 ? 1 : splits;
 }
+// fp32 elements of scratch kh_colsum needs (counter slots included); must start zeroed
+extern "C" long kh_colsum_scratch_elems(int rows, int N) { return KH_COUNTER_SLOTS + (long)kh_colsum_splits(rows, N) * N; }
 extern "C" int kh_colsum(const void* x, int ld, void* out, void* scratch, int rows, int N, int accumulate, void* stream) {
   if (ld % 8 || ((uintptr_t)x & 15)) { kh_set_error("colsum: input pitch/base must be 16-byte aligned"); return -1; }
+  if ((N + 63) / 64 > KH_COUNTER_SLOTS) { kh_set_error("colsum: N=%d exceeds %d column blocks", N, KH_COUNTER_SLOTS); return -1; }
   const int splits = kh_colsum_splits(rows, N);
   const int rps = (rows + splits - 1) / splits;
   dim3 grid(cdiv(N, 64), splits);
-  colsum_part_k<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ld, (float*)scratch, rows, N, rps);
-  colsum_final_k<<<cdiv(N, 256), 256, 0, (cudaStream_t)stream>>>((const float*)scratch, (float*)out, splits, N, accumulate);
+  colsum_k<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ld, (float*)out, (int*)scratch,
+                                                    (float*)scratch + KH_COUNTER_SLOTS, rows, N, rps, accumulate);
   KH_LAUNCH_CHECK("colsum");
   return 0;
 }
@@ -280,8 +315,10 @@ __global__ void layernorm_bwd_dx_k(const bf16* __restrict__ dy, const bf16* __re
 }
 __global__ void layernorm_bwd_dwdb_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                      const float* __restrict__ mean, const float* __restrict__ rstd,
-                                     float* __restrict__ partials, int rows, int d, int rows_per_split) {
+                                     int* __restrict__ counters, float* __restrict__ partials,
+                                     float* __restrict__ dw, float* __restrict__ db, int rows, int d, int rows_per_split) {
   __shared__ float part[32][2][65];
+  __shared__ int s_last;
   const int cg = threadIdx.x & 7, rg = threadIdx.x >> 3;
   const int col = blockIdx.x * 64 + cg * 8;
   const int r0 = blockIdx.y * rows_per_split, r1 = min(rows, r0 + rows_per_split);
@@ -305,27 +342,29 @@ __global__ void layernorm_bwd_dwdb_k(const bf16* __restrict__ dy, const bf16* __
 #pragma unroll
   for (int k = 0; k < 8; k++) { part[rg][0][cg * 8 + k] = aw[k]; part[rg][1][cg * 8 + k] = ab[k]; }
   __syncthreads();
-  if (threadIdx.x < 128) {
-    const int which = threadIdx.x >> 6, cc = threadIdx.x & 63;
-    const int c = blockIdx.x * 64 + cc;
-    if (c < d) {
-      float sacc = 0.f;
+  const int which = threadIdx.x >> 6, cc = threadIdx.x & 63;
+  const int c = blockIdx.x * 64 + cc;
+  if (threadIdx.x < 128 && c < d) {
+    float sacc = 0.f;
 #pragma unroll
-      for (int k = 0; k < 32; k++) sacc += part[k][which][cc];
-      partials[((size_t)blockIdx.y * 2 + which) * d + c] = sacc;
-    }
+    for (int k = 0; k < 32; k++) sacc += part[k][which][cc];
+    partials[((size_t)blockIdx.y * 2 + which) * d + c] = sacc;
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(counters + blockIdx.x, 1) == (int)gridDim.y - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 128 && c < d) {
+    float* dst = which ? db : dw;
+    float sacc = dst[c];
+    for (int k = 0; k < (int)gridDim.y; k++) sacc += __ldcg(partials + ((size_t)k * 2 + which) * d + c);
+    dst[c] = sacc;
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
-__global__ void layernorm_bwd_reduce_k(const float* __restrict__ partials, float* __restrict__ dw,
-                                       float* __restrict__ db, int nparts, int d) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= 2 * d) return;
-  float s = 0.f;
-  for (int k = 0; k < nparts; k++) s += partials[(size_t)k * 2 * d + j];
-  if (j < d) dw[j] += s;
-  else db[j - d] += s;
-}
-// Number of row splits (= rows of `partials`, each 2*d floats) layernorm_bwd uses.
+// Number of row splits layernorm_bwd uses; its scratch is KH_COUNTER_SLOTS + splits * 2 * d floats, zeroed once.
 extern "C" int kh_layernorm_bwd_parts(int rows, int d) {
   const int cb = (d + 63) / 64;
   int parts = (592 + cb - 1) / cb;
@@ -333,10 +372,14 @@ extern "C" int kh_layernorm_bwd_parts(int rows, int d) {
   if (parts > by_rows) parts = by_rows;
   return parts < 1 ? 1 : parts;
 }
+extern "C" long kh_layernorm_bwd_scratch_elems(int rows, int d) {
+  return KH_COUNTER_SLOTS + (long)kh_layernorm_bwd_parts(rows, d) * 2 * d;
+}
 extern "C" int kh_layernorm_bwd(const void* dy, const void* x, const void* w, const void* mean, const void* rstd,
                                 const void* dres, void* dx, void* dw, void* db, void* partials, int rows, int d,
                                 void* stream) {
   if (d % 8) { kh_set_error("layernorm_bwd: d must be a multiple of 8"); return -1; }
+  if ((d + 63) / 64 > KH_COUNTER_SLOTS) { kh_set_error("layernorm_bwd: d=%d is too wide", d); return -1; }
   cudaStream_t st = (cudaStream_t)stream;
   const int parts = kh_layernorm_bwd_parts(rows, d);
   const int rps = (rows + parts - 1) / parts;
@@ -344,8 +387,8 @@ extern "C" int kh_layernorm_bwd(const void* dy, const void* x, const void* w, co
                                                      (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows, d);
   dim3 grid(cdiv(d, 64), parts);
   layernorm_bwd_dwdb_k<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd,
-                                              (float*)partials, rows, d, rps);
-  layernorm_bwd_reduce_k<<<cdiv(2 * d, 128), 128, 0, st>>>((const float*)partials, (float*)dw, (float*)db, parts, d);
+                                              (int*)partials, (float*)partials + KH_COUNTER_SLOTS, (float*)dw,
+                                              (float*)db, rows, d, rps);
   KH_LAUNCH_CHECK("layernorm_bwd");
   return 0;
 }

@@ -437,11 +437,16 @@ extern "C" int kh_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int
   if ((epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESID || epi == EPI_DGELU || epi == EPI_RESID) && (!aux || (ldaux % 8) || ((uintptr_t)aux & 15))) { kh_set_error("gemm: aux operand missing or misaligned"); return -1; }
   int bn = block_n;
   if (bn == 0) {
-    const int tm = (M + BM - 1) / BM;
+    // waves x relative tile time; narrower tiles reuse the A panel less and run at lower efficiency
+    const int tm = (M + BM - 1) / BM, sms = num_sms();
+    auto waves = [&](int w) { return (tm * ((N + w - 1) / w) + sms - 1) / sms; };
+    const float c256 = waves(256) * 1.0f, c128 = waves(128) * 0.7f, c64 = waves(64) * 0.5f;
     bn = 256;
+    float best = c256;
+    if (c128 < best) { best = c128; bn = 128; }
+    if (c64 < best) { best = c64; bn = 64; }
     if (N <= 64) bn = 64;
-    else if (N <= 128) bn = 128;
-    else if (tm * ((N + 255) / 256) < num_sms()) bn = (tm * ((N + 127) / 128) < num_sms()) ? 64 : 128;
+    else if (N <= 128 && bn == 256) bn = 128;
   }
   if (bn != 64 && bn != 128 && bn != 256) { kh_set_error("gemm: block_n must be 64, 128 or 256"); return -1; }
   const CUtensorMap* ta = a_mn ? kh_tmap_2d_bf16(A, K, M, lda, BK, 64) : kh_tmap_2d_bf16(A, M, K, lda, BM, BK);

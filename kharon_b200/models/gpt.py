@@ -88,11 +88,11 @@ class GPT:
         self.s_datt = e(R, dl)
         self.s_dqkv = e(R, 3 * dl)
         self.s_delta = torch.empty(cfg.batch, cfg.n_head // tp, cfg.seq, dtype=torch.float32, device=self.device)
-        self.s_lnpart = torch.empty(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
+        self.s_lnpart = torch.zeros(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
                                     dtype=torch.float32, device=self.device)
         cuda = self.device.type == "cuda"
         ncs = max(ops.colsum_scratch_elems(R, n) for n in (d, fo, 3 * dl)) if cuda else 1
-        self.s_colsum = torch.empty(ncs, dtype=torch.float32, device=self.device)
+        self.s_colsum = torch.zeros(ncs, dtype=torch.float32, device=self.device)
         self.s_table = torch.empty(2 * cfg.vocab, dtype=torch.int32, device=self.device)
         self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.tp_allreduce = None      # callable(tensor) summing in place over the TP group

@@ -163,7 +163,7 @@ def _scratch_buf(device, nbytes):
     key = (device.index, )
     t = _scratch.get(key)
     if t is None or t.numel() < nbytes:
-        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _scratch[key] = t
     return t
 
@@ -181,17 +181,18 @@ def embed_bwd(tok, dx, dwte, dwpe, B, T, table=None):
 
 
 def colsum_scratch_elems(rows, N):
-    return _lib().kh_colsum_splits(rows, N) * N if torch.cuda.is_available() else 0
+    return int(_lib().kh_colsum_scratch_elems(rows, N)) if torch.cuda.is_available() else 0
 
 
 def colsum(x, out, accumulate=True, scratch=None):
-    """out[j] (+)= sum_r x[r, j]; ``scratch`` holds fp32 partial rows (colsum_scratch_elems)."""
+    """out[j] (+)= sum_r x[r, j]; ``scratch`` (colsum_scratch_elems fp32, zero-initialised once and
+    left zeroed by every call) holds ticket counters and partial rows."""
     if not x.is_cuda:
         return ref.colsum(x, out, accumulate)
     rows, N = x.shape
     if scratch is None:
         scratch = _scratch_buf(x.device, 4 * colsum_scratch_elems(rows, N))
-    _call(_lib().kh_colsum, 2, x.data_ptr(), x.stride(0), out.data_ptr(), scratch.data_ptr(), rows, N, int(accumulate),
+    _call(_lib().kh_colsum, 1, x.data_ptr(), x.stride(0), out.data_ptr(), scratch.data_ptr(), rows, N, int(accumulate),
                           _stream())
 
 
@@ -206,10 +207,11 @@ def layernorm_fwd(x, w, b, y, mean=None, rstd=None):
 
 
 def layernorm_bwd_scratch_elems(rows, d):
-    """fp32 elements of the partial-sum scratch that ``layernorm_bwd`` needs."""
+    """fp32 elements of the scratch that ``layernorm_bwd`` needs (ticket counters + partial sums;
+    zero-initialised once, every call leaves the counters at zero)."""
     if not torch.cuda.is_available():
         return 2 * d
-    return _lib().kh_layernorm_bwd_parts(rows, d) * 2 * d
+    return int(_lib().kh_layernorm_bwd_scratch_elems(rows, d))
 
 
 def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
@@ -218,7 +220,7 @@ def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
         return ref.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db)
     rows, d = x.shape
     assert partials.numel() >= layernorm_bwd_scratch_elems(rows, d)
-    _call(_lib().kh_layernorm_bwd, 3, dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+    _call(_lib().kh_layernorm_bwd, 2, dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                  _p(dres), dx.data_ptr(), dw.data_ptr(), db.data_ptr(), partials.data_ptr(), rows, d,
                                  _stream())
 

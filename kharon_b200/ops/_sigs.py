@@ -19,9 +19,9 @@ def declare(lib):
     _sig(lib, "kh_embed_fwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
     _sig(lib, "kh_embed_bwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
     _sig(lib, "kh_colsum", i32, vp, i32, vp, vp, i32, i32, i32, vp)
-    _sig(lib, "kh_colsum_splits", i32, i32, i32)
+    _sig(lib, "kh_colsum_scratch_elems", long_, i32, i32)
     _sig(lib, "kh_layernorm_fwd", i32, vp, vp, vp, vp, vp, vp, i32, i32, vp)
-    _sig(lib, "kh_layernorm_bwd_parts", i32, i32, i32)
+    _sig(lib, "kh_layernorm_bwd_scratch_elems", long_, i32, i32)
     _sig(lib, "kh_layernorm_bwd", i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp)
     _sig(lib, "kh_xent", i32, vp, i32, i32, vp, vp, f32, vp, vp, i32, i32, vp)
     _sig(lib, "kh_sum_f32", i32, vp, long_, f32, vp, i32, vp)

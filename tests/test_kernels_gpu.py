@@ -98,7 +98,7 @@ def test_layernorm_fwd_bwd():
         ref.layernorm_fwd(x, w, b, y2, m2, r2)
         assert relerr(y, y2) < 4e-3 and relerr(mean, m2) < 1e-4 and relerr(rstd, r2) < 1e-4
         dx = torch.empty_like(x); dw = torch.ones(d, device=DEV); db = torch.ones(d, device=DEV)
-        part = torch.empty(ops.layernorm_bwd_scratch_elems(rows, d), device=DEV)
+        part = torch.zeros(ops.layernorm_bwd_scratch_elems(rows, d), device=DEV)
         ops.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, part)
         dx2 = torch.empty_like(x); dw2 = torch.ones(d, device=DEV); db2 = torch.ones(d, device=DEV)
         ref.layernorm_bwd(dy, x, w, m2, r2, dres, dx2, dw2, db2)
