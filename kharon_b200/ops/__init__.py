@@ -158,9 +158,10 @@ def embed_fwd(tok, pos, wte, wpe, out, T):
 _scratch = {}
 
 
-def _scratch_buf(device, nbytes):
-    """Small per-device scratch for callers that do not pass their own (tests, one-off calls)."""
-    key = (device.index, )
+def _scratch_buf(device, nbytes, tag="colsum"):
+    """Small per-device, per-purpose scratch for callers that do not pass their own (tests,
+    one-off calls).  Buffers that hold ticket counters must not be shared with other uses."""
+    key = (device.index, tag)
     t = _scratch.get(key)
     if t is None or t.numel() < nbytes:
         t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -176,7 +177,7 @@ def embed_bwd(tok, dx, dwte, dwpe, B, T, table=None):
     d = dx.shape[1]
     V = dwte.shape[0] if dwte is not None else 0
     if table is None and dwte is not None:
-        table = _scratch_buf(dx.device, 8 * V)
+        table = _scratch_buf(dx.device, 8 * V, "embed")
     _call(_lib().kh_embed_bwd, 3, tok.data_ptr(), dx.data_ptr(), _p(dwte), _p(dwpe), _p(table), B, T, d, V, _stream())
 
 
