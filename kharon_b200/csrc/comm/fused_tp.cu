@@ -1,0 +1,412 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a).
+//
+//   gemm_comm, mode AR : out[M,N]      = sum_r A_r * op(B_r)   on every rank      (GEMM -> all-reduce)
+//   gemm_comm, mode RS : out[M/tp,N]   = rows [rank*M/tp, ...) of that sum         (GEMM -> reduce-scatter)
+//   optional gather    : A is the row-wise concatenation of per-rank shards that live in
+//                        peer memory (all-gather -> GEMM), read tile by tile with plain
+//                        (non-multicast) TMA loads through per-rank tensor maps.
+//
+// These replace the reference's cuBLAS GEMM followed by a blocking bf16 ncclAllReduce on the
+// same stream (src/core/gpt.c:686-687, 692-693, 745-746, 760-761; src/parallel/comms.cu:97-99).
+//
+// One kernel, persistent CTAs, ten warps:
+//   warp 0      TMA producer (operand tiles -> 128-byte-swizzled shared-memory ring)
+//   warp 1      tcgen05.mma issuer, two TMEM accumulator buffers
+//   warps 2-5   epilogue: TMEM -> bf16 partial tile, stored to the local output (if this rank
+//               reduces the tile) and PUSHED with plain st.global into the staging slot of every
+//               rank that reduces it; then fence + one red.release.sys per warp on that rank's
+//               arrival counter for (source rank, tile)
+//   warps 6-9   reducer: for each finished tile, wait (bounded) until every peer's partial has
+//               arrived, add the partials in rank order in fp32, add bias / residual, store.
+//               Runs concurrently with the main loop of the following tiles, so the NVLink
+//               traffic hides behind the tensor-core work.
+//
+// Determinism: partials are rounded to bf16 once, summed in fp32 in rank order 0..tp-1 on every
+// rank -> all ranks hold bit-identical results, run to run.
+// Flow control: arrival counters only grow (4 per call and tile); staging is double-buffered
+// by call parity, which is sufficient because a rank cannot be two calls ahead of a peer it
+// needs partials from.  Every wait is bounded; on expiry the error word gets code 5 and all
+// roles of the CTA unwind.  No TMA load here uses cluster multicast; peer memory is only
+// touched by st.global / red (push) and, in gather mode, by non-multicast TMA loads.
+#include "../kernels/common.cuh"
+
+#define KH_LAUNCH_CHECK(name)                                                     \
+  do {                                                                            \
+    cudaError_t e_ = cudaGetLastError();                                          \
+    if (e_ != cudaSuccess) { kh_set_error(name ": %s", cudaGetErrorString(e_)); return -1; } \
+  } while (0)
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int THREADS = 320;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int MAX_TP = 8;
+enum { MODE_AR = 0, MODE_RS = 1, MODE_LOCAL = 2 };   // LOCAL: no reduction (all-gather -> GEMM only)
+
+struct CommParams {
+  int M, N, K;
+  int a_mn, b_mn;
+  int mode, tp, rank;
+  int gather;                  // A rows come from per-rank shards (tensor maps tma_a[r])
+  bf16* out; int ldo;          // AR: [M, N]; RS: [M/tp, N]
+  const bf16* bias;            // [N] or null, added by the reducer
+  const bf16* resid; int ldr;  // residual rows aligned with `out`, or null
+  bf16* stage[MAX_TP];         // stage[r]: rank r's staging base (tp slots of M*N), parity applied by host
+  uint32_t* flags[MAX_TP];     // flags[r]: rank r's arrival counters [tp][num_tiles]
+  uint32_t* ready[MAX_TP];     // gather mode: ready[r]: rank r's "shard published" counters [tp]
+  uint32_t target;             // counter value that means "this call's partial has arrived"
+  uint32_t ready_target;
+  int* err;
+};
+
+struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded spin until *p has reached `target` (counters only grow; compare with wrap-around)
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, volatile int* abort_flag, int* err) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+    if ((it & 63) == 63) {
+      if (*abort_flag) return false;
+      const uint64_t now = kh_globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > KH_WAIT_LIMIT_NS) {
+        *abort_flag = 5;
+        atomicCAS(err, 0, 5);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+__device__ __forceinline__ bool wait_smem_count(volatile int* p, int target, volatile int* abort_flag, int* err) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (*p >= target) return true;
+    if ((it & 255) == 255) {
+      if (*abort_flag) return false;
+      const uint64_t now = kh_globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > KH_WAIT_LIMIT_NS) {
+        *abort_flag = 5;
+        atomicCAS(err, 0, 5);
+        return false;
+      }
+    }
+    __nanosleep(32);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_pub = reinterpret_cast<volatile int*>(tmem_slot + 2);   // epilogue warps that finished a tile
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int rows_per_rank = p.M / p.tp;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
+    *abort_flag = 0;
+    *s_pub = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Tiles are visited M-band by M-band starting with this rank's own rows, so that in gather mode
+  // local shards are consumed while the peers' shards are still being published.
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int GROUP = 8;
+    int band = t / (GROUP * tiles_n);
+    int first = band * GROUP;
+    int gsz = min(GROUP, tiles_m - first);
+    int r = t - band * GROUP * tiles_n;
+    int tm0 = first + r % gsz;
+    tn = r / gsz;
+    const int shift = p.gather ? (p.rank * (rows_per_rank / BM)) : 0;
+    tm = (tm0 + shift) % tiles_m;
+  };
+  // which rank reduces tile row-block tm (RS mode); AR: everyone
+  auto owner_of = [&](int tm) { return (tm * BM) / rows_per_rank; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // gather mode: tell every peer that this rank's shard is final (stream order guarantees it)
+      if (p.gather && blockIdx.x == 0) {
+        __threadfence_system();
+        for (int r = 0; r < p.tp; r++)
+          if (r != p.rank) red_release_sys_add(p.ready[r] + p.rank, 1);
+      }
+      int it = 0;
+      bool ok = true;
+      uint32_t seen = 1u << p.rank;
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        int tm, tn;
+        tile_coord(t, tm, tn);
+        int src = 0, row_in_src = tm * BM;
+        if (p.gather) {
+          src = owner_of(tm);
+          row_in_src = tm * BM - src * rows_per_rank;
+          if (!(seen & (1u << src))) {
+            if (!wait_counter(p.ready[p.rank] + src, p.ready_target, abort_flag, p.err)) { ok = false; break; }
+            seen |= 1u << src;
+          }
+        }
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
+          if (!p.a_mn) tma_load_2d(sa, &maps.a[src], bar_full + 8 * s, kb * BK, row_in_src);
+          else
+            for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), &maps.a[src], bar_full + 8 * s, row_in_src + j * 64, kb * BK);
+          if (!p.b_mn) tma_load_2d(sb, &maps.b, bar_full + 8 * s, kb * BK, tn * BN);
+          else
+            for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * (BK * 128), &maps.b, bar_full + 8 * s, tn * BN + j * 64, kb * BK);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, b_lbo = p.b_mn ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      const uint32_t b_kstep = p.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1, abort_flag, 4, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, 1, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const uint64_t adesc = umma_desc_sw128(sa, a_lbo, 1024), bdesc = umma_desc_sw128(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)
+            umma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(bar_empty + 8 * s);
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- epilogue: publish partial tiles
+    const int q = warp & 3;
+    int tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+      int tm, tn;
+      tile_coord(t, tm, tn);
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
+      const bool mine = owner < 0 || owner == p.rank;
+      const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = tn * BN + c0;
+        if (col >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        tmem_ld_wait();
+        uint4 o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          o[j].x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+          o[j].y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+          o[j].z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+          o[j].w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        }
+        if (row_ok) {
+          const int nvec = min(4, (p.N - col) / 8);     // N is a multiple of 8 (checked on the host)
+          if (mine) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)out_row * p.ldo + col);
+            for (int j = 0; j < nvec; j++) dst[j] = o[j];
+          }
+          for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
+            if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
+            // slot `rank` of peer pr's staging, full [M, N] addressing
+            uint4* dst = reinterpret_cast<uint4*>(p.stage[pr] + ((size_t)p.rank * p.M + row) * p.N + col);
+            for (int j = 0; j < nvec; j++) dst[j] = o[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar_tempty + 8 * acc);
+        for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
+          if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
+          red_release_sys_add(p.flags[pr] + (size_t)p.rank * num_tiles + t, 1);
+        }
+        atomicAdd(const_cast<int*>(s_pub), 1);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- reducer warps
+    const int rw = warp - 6;
+    int tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && p.mode != MODE_LOCAL && t < num_tiles; t += gridDim.x, tcount++) {
+      int tm, tn;
+      tile_coord(t, tm, tn);
+      const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
+      int good = 1;
+      if (lane == 0) {
+        good = wait_smem_count(s_pub, 4 * (tcount + 1), abort_flag, p.err) ? 1 : 0;
+        if (good && (owner < 0 || owner == p.rank)) {
+          for (int pr = 0; pr < p.tp && good; pr++) {
+            if (pr == p.rank) continue;
+            good = wait_counter(p.flags[p.rank] + (size_t)pr * num_tiles + t, p.target, abort_flag, p.err) ? 1 : 0;
+          }
+        }
+      }
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { ok = false; break; }
+      if (owner >= 0 && owner != p.rank) continue;      // another rank reduces this tile
+      __threadfence();
+      const int col = tn * BN + lane * 8;
+      if (col >= p.N) continue;
+      float bias8[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) bias8[k] = 0.f;
+      if (p.bias) {
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+        float2 f0 = unpack_bf16(b.x), f1 = unpack_bf16(b.y), f2 = unpack_bf16(b.z), f3 = unpack_bf16(b.w);
+        bias8[0] = f0.x; bias8[1] = f0.y; bias8[2] = f1.x; bias8[3] = f1.y; bias8[4] = f2.x; bias8[5] = f2.y; bias8[6] = f3.x; bias8[7] = f3.y;
+      }
+      const int row_end = min(p.M, (tm + 1) * BM);
+      for (int row = tm * BM + rw; row < row_end; row += 4) {
+        const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+        bf16* optr = p.out + (size_t)out_row * p.ldo + col;
+        float a8[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) a8[k] = bias8[k];
+        for (int r = 0; r < p.tp; r++) {
+          const uint4* src = (r == p.rank)
+                                 ? reinterpret_cast<const uint4*>(optr)
+                                 : reinterpret_cast<const uint4*>(p.stage[p.rank] + ((size_t)r * p.M + row) * p.N + col);
+          uint4 v = __ldcg(src);
+          float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+          a8[0] += f0.x; a8[1] += f0.y; a8[2] += f1.x; a8[3] += f1.y; a8[4] += f2.x; a8[5] += f2.y; a8[6] += f3.x; a8[7] += f3.y;
+        }
+        if (p.resid) {
+          uint4 v = *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col);
+          float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+          a8[0] += f0.x; a8[1] += f0.y; a8[2] += f1.x; a8[3] += f1.y; a8[4] += f2.x; a8[5] += f2.y; a8[6] += f3.x; a8[7] += f3.y;
+        }
+        uint4 o;
+        o.x = pack_bf16(a8[0], a8[1]); o.y = pack_bf16(a8[2], a8[3]); o.z = pack_bf16(a8[4], a8[5]); o.w = pack_bf16(a8[6], a8[7]);
+        *reinterpret_cast<uint4*>(optr) = o;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+int g_sms = 0;
+int num_sms() {
+  if (!g_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sms <= 0) g_sms = 148;
+  }
+  return g_sms;
+}
+
+}  // namespace
+
+// Fused tensor-parallel GEMM.  `a_ptrs`: one pointer (local A) or, when gather != 0, tp pointers
+// to the per-rank row shards [M/tp, K] (or [K, M/tp] when a_mn) mapped into this process.
+// `stage_ptrs`, `flag_ptrs`, `ready_ptrs`: tp entries each, index r = rank r's buffer as seen from
+// this process (own entry = local buffer).  Staging holds tp slots of M*N bf16; flags hold
+// tp * ceil(M/128) * ceil(N/256) counters; ready holds tp counters.  `call_no` is this buffer set's
+// 1-based call count (identical on all ranks).  Returns 0 or -1.
+extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn, const void* B, int ldb, int b_mn,
+                            void* out, int ldo, int M, int N, int K, int mode, int gather, int tp, int rank,
+                            const unsigned long long* stage_ptrs, const unsigned long long* flag_ptrs,
+                            const unsigned long long* ready_ptrs, unsigned call_no, unsigned gather_no,
+                            const void* bias, const void* resid, int ldr, int max_ctas, void* stream) {
+  if (tp < 2 || tp > MAX_TP || rank < 0 || rank >= tp) { kh_set_error("gemm_comm: bad tp/rank %d/%d", rank, tp); return -1; }
+  if (M % (tp * BM)) { kh_set_error("gemm_comm: M=%d must be a multiple of tp*128", M); return -1; }
+  if (N % 8 || ldo % 8 || ((uintptr_t)out & 15)) { kh_set_error("gemm_comm: N and the output pitch must be multiples of 8"); return -1; }
+  Maps maps;
+  const int rows_a = gather ? M / tp : M;
+  for (int r = 0; r < (gather ? tp : 1); r++) {
+    const void* A = (const void*)a_ptrs[r];
+    const CUtensorMap* ta = a_mn ? kh_tmap_2d_bf16(A, K, rows_a, lda, BK, 64) : kh_tmap_2d_bf16(A, rows_a, K, lda, BM, BK);
+    if (!ta) return -1;
+    maps.a[r] = *ta;
+  }
+  const CUtensorMap* tb = b_mn ? kh_tmap_2d_bf16(B, K, N, ldb, BK, 64) : kh_tmap_2d_bf16(B, N, K, ldb, BN, BK);
+  if (!tb) return -1;
+  maps.b = *tb;
+  CommParams p = {};
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.tp = tp; p.rank = rank; p.gather = gather;
+  p.out = (bf16*)out; p.ldo = ldo; p.bias = (const bf16*)bias; p.resid = (const bf16*)resid; p.ldr = ldr;
+  for (int r = 0; r < tp; r++) {
+    p.stage[r] = (bf16*)stage_ptrs[r];
+    p.flags[r] = (uint32_t*)flag_ptrs[r];
+    p.ready[r] = ready_ptrs ? (uint32_t*)ready_ptrs[r] : nullptr;
+  }
+  p.target = 4u * call_no;
+  p.ready_target = gather_no;
+  p.err = kh_error_word_dev();
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_comm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) { kh_set_error("gemm_comm: shared memory opt-in failed: %s", cudaGetErrorString(e)); return -1; }
+    attr = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  gemm_comm_kernel<<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(maps, p);
+  KH_LAUNCH_CHECK("gemm_comm");
+  return 0;
+}

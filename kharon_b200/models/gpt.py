@@ -208,29 +208,33 @@ class GPT:
         if self.tp_allreduce is not None:
             ops.plan_call(self.tp_allreduce, t)
 
+    def _row_parallel(self, a, w, out, bias=None, resid=None, b_mn=False):
+        """out = sum over the TP group of a @ op(w) (+ bias + resid).  Single rank: one GEMM with a
+        fused epilogue.  TP: the fused GEMM + all-reduce kernel when installed, otherwise the
+        baseline -- rank 0 folds bias + residual into its partial product and an NCCL all-reduce
+        sums the partials (src/core/gpt.c:686-687)."""
+        if self.tp > 1 and self.fused_tp is not None:
+            self.fused_tp.gemm_ar(a, w, out, b_mn=b_mn, bias=bias, resid=resid)
+            return
+        if bias is not None and self.tp_rank == 0:
+            ops.gemm(a, w, out, b_mn=b_mn, epi=ops.EPI_BIAS_RESID, bias=bias, aux=resid)
+        else:
+            ops.gemm(a, w, out, b_mn=b_mn)
+        self._ar(out)
+
     def forward_layers(self, s: _Slot):
         cfg, tp = self.cfg, self.tp
         B, T, Hl, hd = cfg.batch, cfg.seq, cfg.n_head // tp, cfg.head_dim
-        lead = self.tp_rank == 0
         for l in range(cfg.n_layer):
             a = s.layers[l]
             x = s.x[l]
             ops.layernorm_fwd(x, self.L(l, "ln1_w"), self.L(l, "ln1_b"), a["ln1"], a["mean1"], a["rstd1"])
             ops.gemm(a["ln1"], self.L(l, "qkv_w"), a["qkv"], epi=ops.EPI_BIAS, bias=self.L(l, "qkv_b"))
             ops.flash_fwd(a["qkv"], a["att"], a["lse"], B, T, Hl, hd)
-            if lead:
-                ops.gemm(a["att"], self.L(l, "proj_w"), a["xmid"], epi=ops.EPI_BIAS_RESID, bias=self.L(l, "proj_b"), aux=x)
-            else:
-                ops.gemm(a["att"], self.L(l, "proj_w"), a["xmid"])
-            self._ar(a["xmid"])
+            self._row_parallel(a["att"], self.L(l, "proj_w"), a["xmid"], self.L(l, "proj_b"), x)
             ops.layernorm_fwd(a["xmid"], self.L(l, "ln2_w"), self.L(l, "ln2_b"), a["ln2"], a["mean2"], a["rstd2"])
             ops.gemm(a["ln2"], self.L(l, "fc_w"), a["act"], epi=ops.EPI_BIAS_GELU, bias=self.L(l, "fc_b"), aux=a["pre"])
-            if lead:
-                ops.gemm(a["act"], self.L(l, "fcproj_w"), s.x[l + 1], epi=ops.EPI_BIAS_RESID,
-                         bias=self.L(l, "fcproj_b"), aux=a["xmid"])
-            else:
-                ops.gemm(a["act"], self.L(l, "fcproj_w"), s.x[l + 1])
-            self._ar(s.x[l + 1])
+            self._row_parallel(a["act"], self.L(l, "fcproj_w"), s.x[l + 1], self.L(l, "fcproj_b"), a["xmid"])
 
     def head_weight(self):
         return self.params.c["head_w"] if self.has_head else self.params.c["wte"]
@@ -303,8 +307,7 @@ class GPT:
             ops.gemm(dx, self.L(l, "fcproj_w"), self.s_dpre, b_mn=True, epi=ops.EPI_DGELU, aux=a["pre"])
             ops.colsum(self.s_dpre, self.G(l, "fc_b"), scratch=self.s_colsum)
             ops.gemm(self.s_dpre, a["ln2"], self.G(l, "fc_w"), a_mn=True, b_mn=True, accumulate=True)
-            ops.gemm(self.s_dpre, self.L(l, "fc_w"), self.s_dln, b_mn=True)
-            self._ar(self.s_dln)
+            self._row_parallel(self.s_dpre, self.L(l, "fc_w"), self.s_dln, b_mn=True)
             ops.layernorm_bwd(self.s_dln, a["xmid"], self.L(l, "ln2_w"), a["mean2"], a["rstd2"], dx, other,
                               self.G(l, "ln2_w"), self.G(l, "ln2_b"), self.s_lnpart)
             dx, other = other, dx
@@ -315,8 +318,7 @@ class GPT:
             ops.flash_bwd(a["qkv"], a["att"], self.s_datt, a["lse"], self.s_dqkv, self.s_delta, B, T, Hl, hd)
             ops.colsum(self.s_dqkv, self.G(l, "qkv_b"), scratch=self.s_colsum)
             ops.gemm(self.s_dqkv, a["ln1"], self.G(l, "qkv_w"), a_mn=True, b_mn=True, accumulate=True)
-            ops.gemm(self.s_dqkv, self.L(l, "qkv_w"), self.s_dln, b_mn=True)
-            self._ar(self.s_dln)
+            self._row_parallel(self.s_dqkv, self.L(l, "qkv_w"), self.s_dln, b_mn=True)
             ops.layernorm_bwd(self.s_dln, s.x[l], self.L(l, "ln1_w"), a["mean1"], a["rstd1"], dx, other,
                               self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
             dx, other = other, dx

@@ -1,0 +1,142 @@
+"""Fused tensor-parallel GEMM + collective (the product path; NCCL all-reduce is the baseline).
+
+``FusedTP`` owns the symmetric (peer-mapped) staging buffers and arrival counters that the
+``kh_gemm_comm`` kernel needs and exposes
+
+* ``gemm_ar``  partial GEMM on every rank, summed across the TP group inside the kernel
+               (GEMM -> reduce-scatter -> all-gather over NVLink P2P stores), bias / residual
+               added in the reduction;
+* ``gemm_rs``  same, but each rank keeps only its row shard (GEMM -> reduce-scatter);
+* ``ag_gemm``  all-gather -> GEMM: the A operand is the concatenation of per-rank row shards
+               that live in symmetric memory and are read tile by tile with TMA.
+
+Buffers come from ``torch.distributed._symmetric_memory`` (allocation and address exchange
+only); all data movement is issued from inside the kernel.  Call counters are kept on the host
+and are identical on all ranks because every rank issues the same sequence of calls.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .. import _native, ops
+
+MODE_AR, MODE_RS = 0, 1
+
+
+def _symm_alloc(nbytes, device, group):
+    import torch.distributed._symmetric_memory as symm_mem
+    t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+    name = group.group_name if hasattr(group, "group_name") else group
+    h = symm_mem.rendezvous(t, name)
+    return t, h
+
+
+class _Ctx:
+    """Staging + counters for one (M, N, mode) shape."""
+
+    def __init__(self, M, N, tp, rank, device, group):
+        self.M, self.N, self.tp, self.rank = M, N, tp, rank
+        tiles = ((M + 127) // 128) * ((N + 255) // 256)
+        self.slot_bytes = tp * M * N * 2
+        self.flag_bytes = tp * tiles * 4
+        total = 2 * self.slot_bytes + self.flag_bytes + 256
+        self.buf, self.h = _symm_alloc(total, device, group)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.h.barrier()
+        base = [int(p) for p in self.h.buffer_ptrs]
+        self.stage = [[b + par * self.slot_bytes for b in base] for par in (0, 1)]
+        self.flags = [b + 2 * self.slot_bytes for b in base]
+        self.ready = [b + 2 * self.slot_bytes + self.flag_bytes for b in base]
+        U = C.c_uint64 * tp
+        self.c_stage = [U(*self.stage[0]), U(*self.stage[1])]
+        self.c_flags = U(*self.flags)
+        self.c_ready = U(*self.ready)
+        self.calls = 0
+        self.gathers = 0
+
+
+class FusedTP:
+    def __init__(self, mesh, device):
+        self.group = mesh.tp_group
+        self.tp, self.rank = mesh.c.tp, mesh.c.tp_rank
+        self.device = torch.device(device)
+        self.ctx = {}
+        self.max_ctas = 0
+
+    def _get(self, M, N, mode):
+        key = (M, N, mode)
+        c = self.ctx.get(key)
+        if c is None:
+            c = self.ctx[key] = _Ctx(M, N, self.tp, self.rank, self.device, self.group)
+        return c
+
+    def symmetric_rows(self, rows, cols, dtype=torch.bfloat16):
+        """A [rows, cols] tensor in symmetric memory plus the peers' addresses of it (for ag_gemm)."""
+        t, h = _symm_alloc(rows * cols * 2, self.device, self.group)
+        return t.view(dtype).view(rows, cols), [int(p) for p in h.buffer_ptrs], h
+
+    def _launch(self, a_ptrs, lda, a_mn, b, b_mn, out, M, N, K, mode, gather, bias, resid):
+        c = self._get(M, N, mode)
+        c.calls += 1
+        if gather:
+            c.gathers += 1
+        lib = _native.cuda()
+        rc = lib.kh_gemm_comm(a_ptrs, lda, int(a_mn), b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(),
+                              out.stride(0), M, N, K, mode, int(gather), self.tp, self.rank, c.c_stage[c.calls & 1],
+                              c.c_flags, c.c_ready, c.calls, c.gathers, ops._p(bias), ops._p(resid),
+                              resid.stride(0) if resid is not None else 0, self.max_ctas,
+                              torch.cuda.current_stream().cuda_stream)
+        ops._chk(rc)
+
+    def _gemm(self, a, b, out, a_mn, b_mn, mode, bias, resid):
+        if a_mn:
+            K, M = a.shape
+        else:
+            M, K = a.shape
+        N = b.shape[1] if b_mn else b.shape[0]
+        ptr = (C.c_uint64 * 1)(a.data_ptr())
+        # a host callable, so that a recorded launch plan re-evaluates the call counter
+        ops.plan_call(self._launch, ptr, a.stride(0), a_mn, b, b_mn, out, M, N, K, mode, 0, bias, resid)
+        return out
+
+    def gemm_ar(self, a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None):
+        """out[M,N] = sum over TP ranks of op(a) @ op(b) (+ bias + resid), identical on all ranks."""
+        return self._gemm(a, b, out, a_mn, b_mn, MODE_AR, bias, resid)
+
+    def gemm_rs(self, a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None):
+        """out[M/tp,N] = this rank's row block of the summed product (+ bias + resid rows)."""
+        return self._gemm(a, b, out, a_mn, b_mn, MODE_RS, bias, resid)
+
+    def ag_gemm(self, shard_ptrs, lda, rows_per_rank, b, out, *, b_mn=False, K=None):
+        """out[M,N] = concat_r(shard_r)[M,K] @ op(b): ``shard_ptrs`` are the tp peer addresses of the
+        row shards ([M/tp, K] each, symmetric memory).  Local product only -- no reduction."""
+        M = rows_per_rank * self.tp
+        N = b.shape[1] if b_mn else b.shape[0]
+        K = K if K is not None else (b.shape[0] if b_mn else b.shape[1])
+        ptrs = (C.c_uint64 * self.tp)(*shard_ptrs)
+        ops.plan_call(self._launch_ag, ptrs, lda, b, b_mn, out, M, N, K)
+        return out
+
+    def _launch_ag(self, ptrs, lda, b, b_mn, out, M, N, K):
+        # gather mode uses a context of its own: its "reduction" is local-only (tp slots unused)
+        c = self._get(M, N, 2)
+        c.calls += 1
+        c.gathers += 1
+        lib = _native.cuda()
+        rc = lib.kh_gemm_comm(ptrs, lda, 0, b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0),
+                              M, N, K, 2, 1, self.tp, self.rank, c.c_stage[c.calls & 1], c.c_flags, c.c_ready,
+                              c.calls, c.gathers, None, None, 0, self.max_ctas,
+                              torch.cuda.current_stream().cuda_stream)
+        ops._chk(rc)
+
+
+def install(model, mesh):
+    """Route the model's row-parallel products (and the conjugate input-gradient products)
+    through the fused GEMM + all-reduce kernel."""
+    f = FusedTP(mesh, model.device)
+    model.fused_tp = f
+    return f
