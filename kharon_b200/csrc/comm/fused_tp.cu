@@ -42,7 +42,8 @@ constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 320;
-constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_CHUNK_BYTES = BM * 64 * 2;                 // 128 rows x 64 columns bf16, one swizzle-128B box
+constexpr int SMEM = STAGES * STAGE_BYTES + 2 * EPI_CHUNK_BYTES + 1024 + 256;
 constexpr int MAX_TP = 8;
 enum { MODE_AR = 0, MODE_RS = 1, MODE_LOCAL = 2 };   // LOCAL: no reduction (all-gather -> GEMM only)
 
@@ -62,7 +63,20 @@ struct CommParams {
   int* err;
 };
 
-struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; };
+// out: the local output; st[r]: slot `rank` of rank r's staging (where this rank's partial goes)
+struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap st[MAX_TP]; };
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(m), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -113,7 +127,8 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES);
+  const uint32_t smem_epi = smem_base + STAGES * STAGE_BYTES;          // two 16 KB store staging chunks
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES + 2 * EPI_CHUNK_BYTES);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * STAGES;
   const uint32_t bar_tfull = bar_empty + 8 * STAGES;
@@ -236,51 +251,63 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       const uint32_t aph = (tcount >> 1) & 1;
       if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
       const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
       const bool mine = owner < 0 || owner == p.rank;
-      const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+      const int out_row0 = p.mode == MODE_RS ? tm * BM - p.rank * rows_per_rank : tm * BM;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const int r_in = q * 32 + lane;                       // row inside the tile
+      const bool issuer = (warp == 2 && lane == 0);
+      int chunk_no = 0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 64, chunk_no++) {
         const int col = tn * BN + c0;
         if (col >= p.N) break;
-        uint32_t r[32];
-        tmem_ld32(taddr + c0, r);
-        tmem_ld_wait();
-        uint4 o[4];
+        const uint32_t sbuf = smem_epi + (chunk_no & 1) * EPI_CHUNK_BYTES;
+        // the bulk store that last read this staging chunk must be done with it
+        if (issuer) tma_store_wait_read1();
+        epi_bar_sync();
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          o[j].x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-          o[j].y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-          o[j].z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-          o[j].w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-        }
-        if (row_ok) {
-          const int nvec = min(4, (p.N - col) / 8);     // N is a multiple of 8 (checked on the host)
-          if (mine) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)out_row * p.ldo + col);
-            for (int j = 0; j < nvec; j++) dst[j] = o[j];
+        for (int h = 0; h < 2; h++) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0 + 32 * h, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            o.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            o.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            o.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            const int chunk16 = h * 4 + j;
+            st_shared_v4(sbuf + r_in * 128 + ((chunk16 ^ (r_in & 7)) << 4), o);
           }
+        }
+        if (c0 + 64 >= BN || col + 64 >= p.N) {            // accumulator fully read: hand it back early
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (issuer) {
+          if (mine) tma_store_2d(&maps.out, sbuf, col, out_row0);
           for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
             if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
-            // slot `rank` of peer pr's staging, full [M, N] addressing
-            uint4* dst = reinterpret_cast<uint4*>(p.stage[pr] + ((size_t)p.rank * p.M + row) * p.N + col);
-            for (int j = 0; j < nvec; j++) dst[j] = o[j];
+            tma_store_2d(&maps.st[pr], sbuf, col, tm * BM);
           }
+          tma_store_commit();
         }
       }
-      tc_fence_before();
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar_tempty + 8 * acc);
+      // all bulk stores of this tile complete (globally performed) before the arrival signals
+      if (issuer) {
+        tma_store_wait_all();
+        asm volatile("fence.proxy.async;" ::: "memory");    // bulk (async-proxy) writes -> ordinary loads
+        __threadfence_system();
         for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
           if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
-          red_release_sys_add(p.flags[pr] + (size_t)p.rank * num_tiles + t, 1);
+          red_release_sys_add(p.flags[pr] + (size_t)p.rank * num_tiles + t, 4);
         }
-        atomicAdd(const_cast<int*>(s_pub), 1);
+        atomicAdd(const_cast<int*>(s_pub), 4);
       }
     }
   } else {
@@ -386,6 +413,16 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   const CUtensorMap* tb = b_mn ? kh_tmap_2d_bf16(B, K, N, ldb, BK, 64) : kh_tmap_2d_bf16(B, N, K, ldb, BN, BK);
   if (!tb) return -1;
   maps.b = *tb;
+  const int out_rows = mode == MODE_RS ? M / tp : M;
+  const CUtensorMap* to = kh_tmap_2d_bf16(out, out_rows, N, ldo, BM, 64);
+  if (!to) return -1;
+  maps.out = *to;
+  for (int r = 0; r < tp; r++) {
+    if (r == rank || mode == MODE_LOCAL) continue;
+    const CUtensorMap* ts = kh_tmap_2d_bf16((const bf16*)stage_ptrs[r] + (size_t)rank * M * N, M, N, N, BM, 64);
+    if (!ts) return -1;
+    maps.st[r] = *ts;
+  }
   CommParams p = {};
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.tp = tp; p.rank = rank; p.gather = gather;
   p.out = (bf16*)out; p.ldo = ldo; p.bias = (const bf16*)bias; p.resid = (const bf16*)resid; p.ldr = ldr;
