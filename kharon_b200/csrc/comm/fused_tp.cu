@@ -244,6 +244,19 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
     const int q = warp & 3;
     int tcount = 0;
     bool ok = true;
+    // Arrival of tile t is signalled once its bulk stores have completed; that is checked one
+    // tile later (after the next tile's first store group is queued), so the epilogue never idles
+    // on the NVLink round trip.
+    int pend_t = -1, pend_owner = -1;
+    auto signal_tile = [&](int tt, int town) {
+      asm volatile("fence.proxy.async;" ::: "memory");    // bulk (async-proxy) writes -> ordinary loads
+      __threadfence_system();
+      for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
+        if (pr == p.rank || (town >= 0 && pr != town)) continue;
+        red_release_sys_add(p.flags[pr] + (size_t)p.rank * num_tiles + tt, 4);
+      }
+      atomicAdd(const_cast<int*>(s_pub), 4);
+    };
     for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
       int tm, tn;
       tile_coord(t, tm, tn);
@@ -296,19 +309,18 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
             tma_store_2d(&maps.st[pr], sbuf, col, tm * BM);
           }
           tma_store_commit();
+          if (chunk_no == 0 && pend_t >= 0) {
+            asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // everything but the group just queued
+            signal_tile(pend_t, pend_owner);
+            pend_t = -1;
+          }
         }
       }
-      // all bulk stores of this tile complete (globally performed) before the arrival signals
-      if (issuer) {
-        tma_store_wait_all();
-        asm volatile("fence.proxy.async;" ::: "memory");    // bulk (async-proxy) writes -> ordinary loads
-        __threadfence_system();
-        for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
-          if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
-          red_release_sys_add(p.flags[pr] + (size_t)p.rank * num_tiles + t, 4);
-        }
-        atomicAdd(const_cast<int*>(s_pub), 4);
-      }
+      pend_t = t; pend_owner = owner;
+    }
+    if (warp == 2 && lane == 0 && pend_t >= 0) {
+      tma_store_wait_all();
+      signal_tile(pend_t, pend_owner);
     }
   } else {
     // ---------------------------------------------------------------- reducer warps
@@ -344,28 +356,57 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
         bias8[0] = f0.x; bias8[1] = f0.y; bias8[2] = f1.x; bias8[3] = f1.y; bias8[4] = f2.x; bias8[5] = f2.y; bias8[6] = f3.x; bias8[7] = f3.y;
       }
       const int row_end = min(p.M, (tm + 1) * BM);
-      for (int row = tm * BM + rw; row < row_end; row += 4) {
-        const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
-        bf16* optr = p.out + (size_t)out_row * p.ldo + col;
-        float a8[8];
+      // 8 rows per pass so that each lane keeps 8 x (tp + 1) independent 16-byte loads in flight
+      constexpr int RB = 8;
+      for (int row0 = tm * BM + rw * RB; row0 < row_end; row0 += 4 * RB) {
+        float a8[RB][8];
 #pragma unroll
-        for (int k = 0; k < 8; k++) a8[k] = bias8[k];
+        for (int i = 0; i < RB; i++)
+#pragma unroll
+          for (int k = 0; k < 8; k++) a8[i][k] = bias8[k];
         for (int r = 0; r < p.tp; r++) {
-          const uint4* src = (r == p.rank)
-                                 ? reinterpret_cast<const uint4*>(optr)
-                                 : reinterpret_cast<const uint4*>(p.stage[p.rank] + ((size_t)r * p.M + row) * p.N + col);
-          uint4 v = __ldcg(src);
-          float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-          a8[0] += f0.x; a8[1] += f0.y; a8[2] += f1.x; a8[3] += f1.y; a8[4] += f2.x; a8[5] += f2.y; a8[6] += f3.x; a8[7] += f3.y;
+          uint4 v[RB];
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            const int row = row0 + i;
+            const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+            const uint4* src = (r == p.rank)
+                                   ? reinterpret_cast<const uint4*>(p.out + (size_t)out_row * p.ldo + col)
+                                   : reinterpret_cast<const uint4*>(p.stage[p.rank] + ((size_t)r * p.M + row) * p.N + col);
+            v[i] = row < row_end ? __ldcg(src) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y), f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+            a8[i][0] += f0.x; a8[i][1] += f0.y; a8[i][2] += f1.x; a8[i][3] += f1.y;
+            a8[i][4] += f2.x; a8[i][5] += f2.y; a8[i][6] += f3.x; a8[i][7] += f3.y;
+          }
         }
         if (p.resid) {
-          uint4 v = *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col);
-          float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-          a8[0] += f0.x; a8[1] += f0.y; a8[2] += f1.x; a8[3] += f1.y; a8[4] += f2.x; a8[5] += f2.y; a8[6] += f3.x; a8[7] += f3.y;
+          uint4 v[RB];
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            const int row = row0 + i;
+            const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+            v[i] = row < row_end ? *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y), f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+            a8[i][0] += f0.x; a8[i][1] += f0.y; a8[i][2] += f1.x; a8[i][3] += f1.y;
+            a8[i][4] += f2.x; a8[i][5] += f2.y; a8[i][6] += f3.x; a8[i][7] += f3.y;
+          }
         }
-        uint4 o;
-        o.x = pack_bf16(a8[0], a8[1]); o.y = pack_bf16(a8[2], a8[3]); o.z = pack_bf16(a8[4], a8[5]); o.w = pack_bf16(a8[6], a8[7]);
-        *reinterpret_cast<uint4*>(optr) = o;
+#pragma unroll
+        for (int i = 0; i < RB; i++) {
+          const int row = row0 + i;
+          if (row >= row_end) break;
+          const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+          uint4 o;
+          o.x = pack_bf16(a8[i][0], a8[i][1]); o.y = pack_bf16(a8[i][2], a8[i][3]);
+          o.z = pack_bf16(a8[i][4], a8[i][5]); o.w = pack_bf16(a8[i][6], a8[i][7]);
+          *reinterpret_cast<uint4*>(p.out + (size_t)out_row * p.ldo + col) = o;
+        }
       }
     }
   }
