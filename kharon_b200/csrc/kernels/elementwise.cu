@@ -214,6 +214,46 @@ extern "C" int kh_colsum(const void* x, int ld, void* out, void* scratch, int ro
   return 0;
 }
 
+// ---- column sum for callers that cannot allocate -------------------------------------------
+// Scratch of kh_colsum_noalloc: lives in the library image, one copy per GPU that loads the
+// library, held until the process exits.  Layout as for kh_colsum: ticket counters, then partial rows.
+#define KH_NOALLOC_PARTIAL_FLOATS 65536
+static __device__ __align__(256) float g_colsum_static_scratch[KH_COUNTER_SLOTS + KH_NOALLOC_PARTIAL_FLOATS];
+
+// See kharon_cuda.h for the contract.  In host code the array's name is only a handle for the
+// runtime, not a device address, so the address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+extern "C" int kh_colsum_noalloc(const void* x, int ld, void* out, int rows, int N, int accumulate, void* stream) {
+  static float* dev_ptr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { kh_set_error("colsum_noalloc: no current device"); return -1; }
+  if (rows <= 0 || N <= 0) { kh_set_error("colsum_noalloc: empty problem %d x %d", rows, N); return -1; }
+  if (ld % 8 || ((uintptr_t)x & 15)) { kh_set_error("colsum_noalloc: input pitch/base must be 16-byte aligned"); return -1; }
+  const int splits = kh_colsum_splits(rows, N);
+  if ((N + 63) / 64 > KH_COUNTER_SLOTS || (long)splits * N > KH_NOALLOC_PARTIAL_FLOATS) {
+    kh_set_error("colsum_noalloc: %d x %d needs %ld partial floats, the built-in scratch holds %d (use kh_colsum with caller scratch)",
+                 rows, N, (long)splits * N, KH_NOALLOC_PARTIAL_FLOATS);
+    return -1;
+  }
+  if (!dev_ptr[dev]) {   // first call on this device: resolve the array's device address
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_colsum_static_scratch);
+    if (e != cudaSuccess || !ptr) { kh_set_error("colsum_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return -1; }
+    dev_ptr[dev] = ptr;
+  }
+  float* scratch = dev_ptr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array keeps whatever the previous call left; the ticket counters must start at zero
+  cudaError_t e = cudaMemsetAsync(scratch, 0, KH_COUNTER_SLOTS * sizeof(int), st);
+  if (e != cudaSuccess) { kh_set_error("colsum_noalloc: clearing the counters failed: %s", cudaGetErrorString(e)); return -1; }
+  const int rps = (rows + splits - 1) / splits;
+  dim3 grid(cdiv(N, 64), splits);
+  colsum_k<<<grid, 256, 0, st>>>((const bf16*)x, ld, (float*)out, (int*)scratch, scratch + KH_COUNTER_SLOTS, rows, N, rps,
+                                 accumulate);
+  KH_LAUNCH_CHECK("colsum_noalloc");
+  return 0;
+}
+
 // ------------------------------------------------------------------------------ LayerNorm
 // One warp per row; statistics in fp32 with a two-pass variance (eps 1e-5, biased variance).
 __global__ void layernorm_fwd_k(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
