@@ -68,8 +68,13 @@ class TrainEngine:
         nl = layers // c.pp
         self.cfg = Config(nl, d_model, heads, vocab, seq, mbatch)
         self.n_slots = pp_num_slots(c.stage, c.pp, n_micro)
+        self.zero_fused = None
+        if c.dp > 1 and fused_comm and self.device.type == "cuda":
+            from .parallel.zero_fused import ZeroFused
+            self.zero_fused = ZeroFused(self.mesh, self.device)
         self.model = GPT(self.cfg, self.device, dtype, tp=c.tp, tp_rank=c.tp_rank, first=c.first, last=c.last,
-                         untied_head=untied_head, n_slots=self.n_slots, dp=c.dp)
+                         untied_head=untied_head, n_slots=self.n_slots, dp=c.dp,
+                         alloc=self.zero_fused.alloc if self.zero_fused else None)
         if init == "device":
             self.model.init_weights_device(seed)
         else:
@@ -97,7 +102,9 @@ class TrainEngine:
             self.shard = ps.n_padded // c.dp
             self.lo = c.dp_rank * self.shard
             ps.alloc_moments(self.shard)
-            self.g_shard = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+            self.g_shard = None if self.zero_fused else torch.zeros(self.shard, dtype=torch.float32, device=dev)
+            if self.zero_fused:
+                self.zero_fused.finalize()
         self.plans = {}
         self.use_plans = self.device.type == "cuda"
 
@@ -191,8 +198,9 @@ class TrainEngine:
             m.adamw_step(o["lr"], o["beta1"], o["beta2"], o["eps"], o["wd"])
             return
         grp = self.mesh.dp_group
-        if self.fused is not None and getattr(self.fused, "zero_step", None) is not None:
-            self.fused.zero_step(self)
+        if self.zero_fused is not None:
+            m.step += 1
+            self.zero_fused.step(ps, self.shard, m.step, o)
             return
         if dist.get_backend(grp) == "nccl":
             dist.reduce_scatter_tensor(self.g_shard, ps.g, op=dist.ReduceOp.AVG, group=grp)

@@ -64,7 +64,7 @@ class _Slot:
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype=torch.bfloat16, tp=1, tp_rank=0, first=True, last=True,
-                 untied_head=False, n_slots=1, dp=1):
+                 untied_head=False, n_slots=1, dp=1, alloc=None):
         assert cfg.d_model % cfg.n_head == 0 and cfg.n_head % tp == 0
         self.cfg, self.tp, self.tp_rank = cfg, tp, tp_rank
         self.first, self.last = first, last
@@ -73,7 +73,7 @@ class GPT:
         # first stage's wte by a gradient exchange) or when an untied head is requested
         self.has_head = last and (untied_head or not first)
         self.untied_head = untied_head
-        self.params = ParamStore(cfg, device, dtype, tp, self.has_head, pad_to=dp)
+        self.params = ParamStore(cfg, device, dtype, tp, self.has_head, pad_to=4 * dp if dp > 1 else 1, alloc=alloc)
         self.params.alloc_moments()
         self.step = 0
         self.Vp = _pad64(cfg.vocab)

@@ -92,7 +92,7 @@ def layout(cfg: Config, tp: int, has_head: bool, elem_size: int):
 class ParamStore:
     """Flat arenas plus named views.  ``compute_dtype`` is torch.bfloat16 or torch.float32."""
 
-    def __init__(self, cfg: Config, device, compute_dtype=torch.bfloat16, tp=1, has_head=False, pad_to=1):
+    def __init__(self, cfg: Config, device, compute_dtype=torch.bfloat16, tp=1, has_head=False, pad_to=1, alloc=None):
         self.cfg, self.tp, self.has_head = cfg, tp, has_head
         self.device = torch.device(device)
         self.compute_dtype = compute_dtype
@@ -104,15 +104,18 @@ class ParamStore:
         # ZeRO-1 pads the flat length to a multiple of the data-parallel size
         self.n_padded = (self.n_flat + pad_to - 1) // pad_to * pad_to
         z = dict(device=self.device)
+        # ``alloc(kind, n, dtype)`` lets the parallel layer place the gradient arena and the compute
+        # copy in symmetric (peer-mapped) memory; it must return zero-filled storage
+        mk = alloc if alloc is not None else (lambda kind, n, dt: torch.zeros(n, dtype=dt, **z))
         self.w = torch.zeros(self.n_padded, dtype=torch.float32, **z)
-        self.g = torch.zeros(self.n_padded, dtype=torch.float32, **z)
+        self.g = mk("g", self.n_padded, torch.float32)
         self.offsets = {n: o // 4 for n, o in zip(names, offs4)}
         self.numels = dict(zip(names, nums))
         if compute_dtype == torch.float32:
             self.wb = self.w
         else:
             # same element offsets as the fp32 arena: one fused optimizer pass emits wb[i] from w[i]
-            self.wb = torch.zeros(self.n_padded, dtype=compute_dtype, **z)
+            self.wb = mk("wb", self.n_padded, compute_dtype)
         self.p = {n: self._view(self.w, n) for n in names}     # fp32 master views
         self.grad = {n: self._view(self.g, n) for n in names}  # fp32 gradient views
         self.c = {n: self._view(self.wb, n) for n in names}    # compute-dtype views

@@ -97,6 +97,22 @@ def _worker(rank, world, port, out_dir):
             ls.append(e.loss())
         losses[fused] = ls
     res["losses"] = losses
+    # ZeRO-1: fused reduce-scatter + AdamW + bf16 all-gather kernel vs the NCCL path, DP = world
+    mesh_dp = Mesh(1, 1, world, timeout_s=120)
+    kw["mesh"] = mesh_dp
+    zl, zw = {}, {}
+    for fused in (False, True):
+        e = TrainEngine(fused_comm=fused, **kw)
+        idx, tgt = Rng(50 + mesh_dp.c.dp_rank).batch(e.tokens_per_step, 512)
+        ls = []
+        for _ in range(6):
+            e.train_step(idx, tgt)
+            ls.append(e.loss())
+        e.gather_master()
+        zl[fused], zw[fused] = ls, e.model.params.w.clone().cpu()
+        assert e.model.params.g.abs().max().item() == 0
+    res["zero_losses"] = zl
+    res["zero_werr"] = ((zw[True] - zw[False]).norm() / zw[False].norm()).item()
     res["word2"] = ops.error_word()
     torch.save(res, os.path.join(out_dir, "r%d.pt" % rank))
     dist.barrier()
@@ -116,4 +132,7 @@ def test_fused_tp_kernels_two_gpus():
         a, b = r["losses"][False], r["losses"][True]
         assert max(abs(x - y) for x, y in zip(a, b)) < 3e-2, (a, b)
         assert b[-1] < b[0]
+        za, zb = r["zero_losses"][False], r["zero_losses"][True]
+        assert max(abs(x - y) for x, y in zip(za, zb)) < 2e-2, (za, zb)
+        assert r["zero_werr"] < 1e-3, r["zero_werr"]
     assert res[0]["losses"][True] == res[1]["losses"][True]
