@@ -106,7 +106,7 @@ def run_ours():
     L, d, H, V = arg("layers", 24), arg("d", 2048), arg("heads", 16), arg("vocab", 50257)
     S, mb, M = arg("seq", 512), arg("mbatch", 4), arg("M", 8)
     fuse = "--no-fuse" not in sys.argv
-    fused_comm = "--fused-comm" in sys.argv or os.environ.get("KHARON_FUSED_COMM", "0") == "1"
+    fused_comm = "--no-fused-comm" not in sys.argv     # in-kernel NVLink collectives (product path) vs NCCL baseline
     mesh = Mesh(tp, pp, dp) if world > 1 else Mesh.single()
     eng = TrainEngine(L, d, H, V, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                       init=arg("init", "device", str), fused_comm=fused_comm)

@@ -270,6 +270,40 @@ class InferEngine:
         ms = (self._timer() - t0) * 1e3
         return outs, self._stats(), ms
 
+    def generate_groups(self, prompts, G, n_new):
+        """``generate_group`` for several prompts at once (one GRPO rollout batch): all prompts are
+        prefilled in one step, each is forked G ways with its first tokens drawn from its own
+        logits row, then all len(prompts) * G samples decode together.  Returns
+        ([prompt][g] -> tokens, stats, ms)."""
+        lib = _native.rt()
+        lib.kh_eng_reset(self._h)
+        t0 = self._timer()
+        parents = []
+        for pr in prompts:
+            p = torch.tensor(pr, dtype=torch.int32)
+            parents.append(_native.rt_check(lib.kh_eng_add(self._h, p.data_ptr(), len(pr), 0)))
+        rc, ntok, nseq, npairs = self._plan(len(prompts))
+        assert nseq == len(prompts), "prefill of all prompts must fit one step"
+        order = self.h_seq_ids[:nseq].tolist()
+        first = self._run(ntok, nseq, rep=G).clone()
+        _native.rt_check(lib.kh_eng_commit(self._h, first.data_ptr(), nseq))
+        kids_of = {}
+        kids = torch.zeros(G, dtype=torch.int32)
+        for row, parent in enumerate(order):
+            _native.rt_check(lib.kh_eng_fork(self._h, parent, G, n_new, kids.data_ptr()))
+            lib.kh_eng_release(self._h, parent)
+            kids_of[parent] = kids.tolist()
+            for g in range(G):
+                _native.rt_check(lib.kh_eng_push(self._h, int(kids[g]), int(first[row * G + g])))
+        while self._step(len(prompts) * G):
+            pass
+        outs = [[self._tokens(k) for k in kids_of[p]] for p in parents]
+        for p in parents:
+            for k in kids_of[p]:
+                lib.kh_eng_release(self._h, k)
+        ms = (self._timer() - t0) * 1e3
+        return outs, self._stats(), ms
+
     def kv_bytes_per_position(self):
         return 2 * self.cfg.n_layer * self.Hl * self.hd * self.kc.element_size()
 

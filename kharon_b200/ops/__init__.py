@@ -276,13 +276,49 @@ def flush_l2(buf):
 
 
 # ------------------------------------------------------------------------------ attention
+_pad_cache = {}
+
+
+def _pad_bufs(qkv, B, T, H, hd, hp):
+    """Head dims below 64 run on the 64-wide kernel: q, k, v are zero-padded per head into cached
+    side buffers (zero columns change neither the scores nor the outputs)."""
+    key = (qkv.device.index, B, T, H, hd)
+    bufs = _pad_cache.get(key)
+    if bufs is None:
+        R, dp = B * T, H * hp
+        z = dict(device=qkv.device, dtype=qkv.dtype)
+        bufs = dict(qkv=torch.zeros(R, 3 * dp, **z), out=torch.zeros(R, dp, **z), dout=torch.zeros(R, dp, **z),
+                    dqkv=torch.zeros(R, 3 * dp, **z))
+        _pad_cache[key] = bufs
+    return bufs
+
+
+def _pad_in(src, dst, parts, H, hd, hp):
+    R = src.shape[0]
+    dst.view(R, parts, H, hp)[:, :, :, :hd].copy_(src[:, :parts * H * hd].reshape(R, parts, H, hd))
+
+
+def _pad_out(src, dst, parts, H, hd, hp):
+    R = src.shape[0]
+    dst[:, :parts * H * hd].copy_(src.view(R, parts, H, hp)[:, :, :, :hd].reshape(R, parts * H * hd))
+
+
 def flash_fwd(qkv, out, lse, B, T, H, hd):
     """Causal attention over the fused projection ``qkv`` [B*T, 3*H*hd] (q | k | v blocks,
     head-major inside each); writes ``out`` [B*T, H*hd] and ``lse`` [B, H, T] (fp32)."""
     if not qkv.is_cuda:
         return ref.flash_fwd(qkv, out, lse, B, T, H, hd)
-    _call(_lib().kh_flash_fwd, 1, qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, hd, qkv.stride(0),
-                             1.0 / math.sqrt(hd), _stream())
+    scale = 1.0 / math.sqrt(hd)
+    if hd not in (64, 128):
+        assert hd < 64, "head dims other than 64/128 must be below 64"
+        pb = _pad_bufs(qkv, B, T, H, hd, 64)
+        plan_call(_pad_in, qkv, pb["qkv"], 3, H, hd, 64)
+        _call(_lib().kh_flash_fwd, 1, pb["qkv"].data_ptr(), pb["out"].data_ptr(), lse.data_ptr(), B, T, H, 64,
+              pb["qkv"].stride(0), scale, _stream())
+        plan_call(_pad_out, pb["out"], out, 1, H, hd, 64)
+        return
+    _call(_lib().kh_flash_fwd, 1, qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, hd, qkv.stride(0), scale,
+          _stream())
 
 
 def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
@@ -290,8 +326,18 @@ def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
     ``delta`` [B, H, T] fp32 is scratch for rowsum(dO * O)."""
     if not qkv.is_cuda:
         return ref.flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd)
+    scale = 1.0 / math.sqrt(hd)
+    if hd not in (64, 128):
+        pb = _pad_bufs(qkv, B, T, H, hd, 64)
+        plan_call(_pad_in, qkv, pb["qkv"], 3, H, hd, 64)
+        plan_call(_pad_in, out, pb["out"], 1, H, hd, 64)
+        plan_call(_pad_in, dout, pb["dout"], 1, H, hd, 64)
+        _call(_lib().kh_flash_bwd, 3, pb["qkv"].data_ptr(), pb["out"].data_ptr(), pb["dout"].data_ptr(), lse.data_ptr(),
+              pb["dqkv"].data_ptr(), delta.data_ptr(), B, T, H, 64, pb["qkv"].stride(0), scale, _stream())
+        plan_call(_pad_out, pb["dqkv"], dqkv, 3, H, hd, 64)
+        return
     _call(_lib().kh_flash_bwd, 3, qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), dqkv.data_ptr(),
-                             delta.data_ptr(), B, T, H, hd, qkv.stride(0), 1.0 / math.sqrt(hd), _stream())
+          delta.data_ptr(), B, T, H, hd, qkv.stride(0), scale, _stream())
 
 
 # ------------------------------------------------------------------------------ paged KV
