@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def main(argv):
     exe = os.path.join(HERE, "_ref", "build", "pp_train.exe")
     if not os.path.exists(exe):
-        print(json.dumps({"impl": "reference", "unavailable": "reference build not present under baseline/_ref"}))
+        print(json.dumps({"impl": "reference", "unavailable": "reference build not present under baseline/_ref (run baseline/build_reference.sh)"}))
         return 0
     from . import reference_run
     return reference_run.run(argv)
