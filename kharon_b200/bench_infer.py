@@ -28,14 +28,32 @@ def run(argv=None):
     init = f.str("init", "host")
     as_json = f.has("json")
     reps = f.int("reps", 2, "timed repetitions per G (best is reported); the first warms graphs up")
+    tp_flag = f.int("tp", 0, "tensor-parallel degree (0 = world size under torchrun)")
+    fused = not f.has("no-fused-comm")
     f.maybe_help()
     cfg = Config(L, d, H, V, seq, 1)
-    m = GPT(cfg, device, torch.bfloat16 if bf16 else torch.float32)
+    import torch.distributed as dist
+    from .parallel.mesh import Mesh, init_distributed
+    rank, world, dev = init_distributed(None if device != "cpu" else "cpu")
+    tp = tp_flag or world
+    mesh = None
+    if world > 1:
+        device = str(dev)
+        mesh = Mesh(tp, 1, world // tp)
+    m = GPT(cfg, device, torch.bfloat16 if bf16 else torch.float32, tp=tp if mesh else 1,
+            tp_rank=mesh.c.tp_rank if mesh else 0)
+    if mesh is not None and tp > 1:
+        grp = mesh.tp_group
+        m.tp_allreduce = lambda t: dist.all_reduce(t, group=grp)
+        if fused and m.device.type == "cuda":
+            from .parallel import fused as fused_mod
+            fused_mod.install(m, mesh)
+    say = print if rank == 0 else (lambda *a, **k: None)
     if init == "device" and device != "cpu":
         m.init_weights_device(1234)
     else:
         m.init_weights(1234)
-    print("infer bench: L=%d d=%d H=%d V=%d seq=%d  prompt=%d new=%d block=%d %s" %
+    say("infer bench: L=%d d=%d H=%d V=%d seq=%d  prompt=%d new=%d block=%d %s" %
           (L, d, H, V, seq, plen, n_new, bs, "bf16" if bf16 else "fp32"))
     prompt = [(i * 131 + 7) % V for i in range(plen)]
     max_lb = (seq + bs - 1) // bs
@@ -51,7 +69,7 @@ def run(argv=None):
         per_pos = eng.kv_bytes_per_position()
         naive, paged = G * seq * per_pos, st["blocks_peak"] * bs * per_pos
         tps = st["tokens_decoded"] * 1000.0 / ms
-        print("  G=%2d: %.0f tok/s (%d toks, %.1f ms)  KV paged %.1f MB vs naive %.1f MB (%.2fx)  blocks %d/%d" %
+        say("  G=%2d: %.0f tok/s (%d toks, %.1f ms)  KV paged %.1f MB vs naive %.1f MB (%.2fx)  blocks %d/%d" %
               (G, tps, st["tokens_decoded"], ms, paged / 1e6, naive / 1e6, naive / paged, st["blocks_peak"],
                st["blocks_total"]), flush=True)
         results["decode"].append(dict(G=G, tok_s=tps, ms=ms, kv_paged_mb=paged / 1e6, kv_naive_mb=naive / 1e6,
@@ -66,14 +84,14 @@ def run(argv=None):
                 best = (outs, st, ms)
         outs, st, ms = best
         saved_mb = st["prefix_blocks_saved"] * bs * eng.kv_bytes_per_position() / 1e6
-        print("  prefix-share G=%2d: blocks saved %d (%.1f MB), %.0f tok/s  peak %d/%d" %
+        say("  prefix-share G=%2d: blocks saved %d (%.1f MB), %.0f tok/s  peak %d/%d" %
               (G, st["prefix_blocks_saved"], saved_mb, st["tokens_decoded"] * 1000.0 / ms, st["blocks_peak"],
                st["blocks_total"]), flush=True)
         results["prefix"].append(dict(G=G, saved_blocks=st["prefix_blocks_saved"], saved_mb=saved_mb,
                                       tok_s=st["tokens_decoded"] * 1000.0 / ms))
         eng.close()
     if as_json:
-        print(json.dumps(results))
+        say(json.dumps(results))
     return results
 
 

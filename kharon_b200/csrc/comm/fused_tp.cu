@@ -141,7 +141,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int rows_per_rank = p.M / p.tp;
+  const int rows_per_rank = max(1, p.M / p.tp);     // only meaningful in the row-sharded modes
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
@@ -441,7 +441,8 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
                             const unsigned long long* ready_ptrs, unsigned call_no, unsigned gather_no,
                             const void* bias, const void* resid, int ldr, int max_ctas, void* stream) {
   if (tp < 2 || tp > MAX_TP || rank < 0 || rank >= tp) { kh_set_error("gemm_comm: bad tp/rank %d/%d", rank, tp); return -1; }
-  if (M % (tp * BM)) { kh_set_error("gemm_comm: M=%d must be a multiple of tp*128", M); return -1; }
+  if ((mode == MODE_RS || gather) && M % (tp * BM)) { kh_set_error("gemm_comm: M=%d must be a multiple of tp*128 for row-sharded modes", M); return -1; }
+  if (M < 1) { kh_set_error("gemm_comm: empty problem"); return -1; }
   if (N % 8 || ldo % 8 || ((uintptr_t)out & 15)) { kh_set_error("gemm_comm: N and the output pitch must be multiples of 8"); return -1; }
   Maps maps;
   const int rows_a = gather ? M / tp : M;

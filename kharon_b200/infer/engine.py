@@ -107,7 +107,6 @@ class InferEngine:
     def _forward(self, ntok, nseq, rep=1):
         m, cfg = self.model, self.cfg
         P = m.params.c
-        lead = m.tp_rank == 0
         x, nxt = self.x
         tok, pos, slot = self.d_tok[:ntok], self.d_pos[:ntok], self.d_slot[:ntok]
         xs = x[:ntok]
@@ -119,19 +118,12 @@ class InferEngine:
             ops.append_kv(qkv, self.kc[l], self.vc[l], pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok)
             ops.paged_attn(qkv, self.kc[l], self.vc[l], att, pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok,
                            cfg.seq)
-            if lead:
-                ops.gemm(att, m.L(l, "proj_w"), xmid, epi=ops.EPI_BIAS_RESID, bias=m.L(l, "proj_b"), aux=xs)
-            else:
-                ops.gemm(att, m.L(l, "proj_w"), xmid)
-            m._ar(xmid)
+            # row-parallel products: one GEMM, or under TP the fused GEMM + all-reduce kernel / NCCL seam
+            m._row_parallel(att, m.L(l, "proj_w"), xmid, m.L(l, "proj_b"), xs)
             ops.layernorm_fwd(xmid, m.L(l, "ln2_w"), m.L(l, "ln2_b"), ln)
             ops.gemm(ln, m.L(l, "fc_w"), self.act[:ntok], epi=ops.EPI_BIAS_GELU, bias=m.L(l, "fc_b"), aux=self.pre[:ntok])
             ys = nxt[:ntok]
-            if lead:
-                ops.gemm(self.act[:ntok], m.L(l, "fcproj_w"), ys, epi=ops.EPI_BIAS_RESID, bias=m.L(l, "fcproj_b"), aux=xmid)
-            else:
-                ops.gemm(self.act[:ntok], m.L(l, "fcproj_w"), ys)
-            m._ar(ys)
+            m._row_parallel(self.act[:ntok], m.L(l, "fcproj_w"), ys, m.L(l, "fcproj_b"), xmid)
             x, nxt = nxt, x
             xs = ys
         ops.gather_rows(xs, self.d_rows, self.last, nseq)

@@ -136,3 +136,54 @@ def test_fused_tp_kernels_two_gpus():
         assert max(abs(x - y) for x, y in zip(za, zb)) < 2e-2, (za, zb)
         assert r["zero_werr"] < 1e-3, r["zero_werr"]
     assert res[0]["losses"][True] == res[1]["losses"][True]
+
+
+def _decode_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from kharon_b200 import ops
+    from kharon_b200.infer import InferEngine
+    from kharon_b200.models import GPT, Config
+    from kharon_b200.parallel import fused as fused_mod
+    from kharon_b200.parallel.mesh import Mesh, init_distributed
+    _, _, dev = init_distributed()
+    mesh = Mesh(world, 1, 1, timeout_s=120)
+    cfg = Config(2, 256, 4, 300, 96, 1)
+    prompts = [[5, 17, 3, 9], [9, 1, 44, 23, 8, 61, 2], [70, 1]]
+    outs = {}
+    for mode in ("single", "nccl", "fused"):
+        tp = 1 if mode == "single" else world
+        m = GPT(cfg, dev, torch.bfloat16, tp=tp, tp_rank=rank if tp > 1 else 0)
+        m.init_weights(1234)
+        m.params.w.mul_(6.0)
+        m.sync_bf16()
+        if tp > 1:
+            m.tp_allreduce = lambda t: dist.all_reduce(t, group=mesh.tp_group)
+            if mode == "fused":
+                fused_mod.install(m, mesh)
+        e = InferEngine(m, block_size=8, max_seqs=5)
+        toks, _, _ = e.generate(prompts, 10)
+        g, st, _ = e.generate_group(prompts[1], 4, 8)
+        outs[mode] = (toks, g)
+    torch.cuda.synchronize()
+    torch.save(dict(outs=outs, word=ops.error_word()), os.path.join(out_dir, "d%d.pt" % rank))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_decode_fused_allreduce_two_gpus():
+    """Tensor-parallel paged decode: the fused GEMM + all-reduce kernel and the NCCL seam give the
+    same greedy tokens on both ranks, and (up to bf16 near-ties) the single-GPU tokens."""
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_decode_worker, args=(2, _free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, "d%d.pt" % r), weights_only=False) for r in range(2)]
+    assert res[0]["word"] == 0 and res[1]["word"] == 0
+    assert res[0]["outs"]["fused"] == res[1]["outs"]["fused"]
+    assert res[0]["outs"]["nccl"] == res[1]["outs"]["nccl"]
+    single, fused = res[0]["outs"]["single"][0], res[0]["outs"]["fused"][0]
+    agree = sum(x == y for s, t in zip(single, fused) for x, y in zip(s, t)) / sum(len(s) for s in single)
+    assert agree > 0.85, agree
