@@ -62,3 +62,23 @@ def test_gpu_run_is_bitwise_reproducible():
         outs.append((e.loss(), e.model.params.w.clone()))
     assert outs[0][0] == outs[1][0]
     assert torch.equal(outs[0][1], outs[1][1])
+
+
+def test_gpu_checkpoint_resume_is_bit_exact(tmp_path):
+    """bf16 training on the GPU: 12 uninterrupted steps == 6 steps + CKP1 file + fresh engine + 6
+    steps, to the bit (loss and every parameter), through the public trainer entry point."""
+    from kharon_b200 import train
+
+    def run(name, steps, resume=False):
+        argv = ["--layers", "2", "--d", "128", "--heads", "2", "--seq", "64", "--batch", "4", "--steps", str(steps),
+                "--log", "1000", "--ckptevery", "0", "--ckpt", str(tmp_path / name), "--synthetic", "--vocab", "1000",
+                "--device", "cuda"]
+        return train.main(argv + (["--resume"] if resume else []))
+
+    full = run("full.ckpt", 12)
+    run("half.ckpt", 6)
+    res = run("half.ckpt", 12, resume=True)
+    assert res.model.step == 12 and res.loss() == full.loss()
+    assert torch.equal(res.model.params.w, full.model.params.w)
+    assert torch.equal(res.model.params.wb, full.model.params.wb)
+    assert torch.equal(res.model.params.v, full.model.params.v)
