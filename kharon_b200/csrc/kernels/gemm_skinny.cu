@@ -1,0 +1,219 @@
+// Weight-streaming GEMM for decode steps (M <= 64 rows): out[M,N] = x[M,K] * W[N,K]^T + epilogue.
+//
+// A decode step multiplies a handful of token rows with every weight matrix, so the product is
+// bound by reading W once, not by FLOPs, and a 128-row output tile would leave most CTAs idle.
+// This kernel swaps the operand roles (the weights are the 128-row "A" operand of tcgen05.mma, the
+// token rows are the narrow "B" operand, the accumulator in TMEM is out^T [128 weights x M]) and
+// splits K across CTAs so that every SM streams a slice of W:
+//
+//   grid = (ceil(N/128) n-tiles) x (split-K slices), one tile per CTA, at most 8 k-blocks of 64
+//   per CTA, all of whose TMA loads are issued up front (no ring to recycle);
+//   split > 1: every CTA writes its fp32 partial to scratch; the CTA that arrives last at its
+//   n-tile (integer ticket) adds the slices in index order and runs the epilogue -- the result is
+//   independent of arrival order, so decoding is reproducible.
+//
+// Epilogues as in the big GEMM: bias, bias+GELU (pre-activation kept), bias+residual.
+// The reference used the same cuBLAS call for M = 1..32 as for training (src/core/infer.c:152-180).
+// Waits are bounded (error word code 1/3).
+#include "common.cuh"
+
+#define KH_LAUNCH_CHECK(name)                                                     \
+  do {                                                                            \
+    cudaError_t e_ = cudaGetLastError();                                          \
+    if (e_ != cudaSuccess) { kh_set_error(name ": %s", cudaGetErrorString(e_)); return -1; } \
+  } while (0)
+
+namespace {
+constexpr int TN = 128, BK = 64, UMMA_K = 16, MAX_KB = 8;
+constexpr int COUNTER_SLOTS = 1024;
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_BIAS_RESID = 3 };
+
+struct SkinnyParams {
+  int M, N, K;
+  int kb_per_cta, num_kb;
+  bf16* out; int ldo;
+  int epi;
+  const bf16* bias;
+  bf16* aux; int ldaux;
+  int* counters;        // [n_tiles], zero between launches
+  float* partials;      // [split][MP][N]
+  int* err;
+};
+
+template <int MP>   // padded row count = MMA N (16, 32 or 64)
+__global__ void __launch_bounds__(128, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const SkinnyParams p) {
+  constexpr int W_BYTES = TN * BK * 2, X_BYTES = MP * BK * 2, STAGE = W_BYTES + X_BYTES;
+  constexpr int TMEM_COLS = MP < 32 ? 32 : MP;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(al + MAX_KB * STAGE);
+  const uint32_t bar_full = smem_u32(bars), bar_done = bar_full + 8 * MAX_KB;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + MAX_KB + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_last = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int nt = blockIdx.x, ks = blockIdx.y, split = gridDim.y;
+  const int kb0 = ks * p.kb_per_cta, kb1 = min(p.num_kb, kb0 + p.kb_per_cta);
+  const int nkb = kb1 - kb0;
+
+  if (tid == 0) {
+    for (int s = 0; s < MAX_KB; s++) mbar_init(bar_full + 8 * s, 1);
+    mbar_init(bar_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_x);
+  }
+  if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  bool ok = true;
+  if (tid == 0) {
+    for (int i = 0; i < nkb; i++) {
+      const uint32_t sw = base + i * STAGE, sx = sw + W_BYTES;
+      mbar_expect_tx(bar_full + 8 * i, STAGE);
+      tma_load_2d(sw, &map_w, bar_full + 8 * i, (kb0 + i) * BK, nt * TN);
+      tma_load_2d(sx, &map_x, bar_full + 8 * i, (kb0 + i) * BK, 0);
+    }
+    constexpr uint32_t idesc = umma_idesc_bf16(TN, MP, 0, 0);
+    for (int i = 0; i < nkb && ok; i++) {
+      if (!mbar_wait(bar_full + 8 * i, 0, abort_flag, 1, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t sw = base + i * STAGE, sx = sw + W_BYTES;
+      const uint64_t adesc = umma_desc_sw128(sw, 16, 1024), bdesc = umma_desc_sw128(sx, 16, 1024);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; k++)
+        umma_f16_ss(tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+    }
+    if (ok) umma_commit(bar_done);
+  }
+  if (nkb > 0 && !mbar_wait(bar_done, 0, abort_flag, 3, p.err)) ok = false;
+  tc_fence_after();
+
+  const int n = nt * TN + tid;                 // this thread's output column (weight row)
+  float v[MP];
+  if (ok && nkb > 0) {
+#pragma unroll
+    for (int c = 0; c < MP; c += 16) {
+      uint32_t r[16];
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; i++) v[c + i] = __uint_as_float(r[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < MP; i++) v[i] = 0.f;
+  }
+  tc_fence_before();
+
+  bool finish = ok;
+  if (ok && split > 1) {
+    if (n < p.N)
+      for (int m = 0; m < p.M; m++) p.partials[((size_t)ks * MP + m) * p.N + n] = v[m];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) *s_last = (atomicAdd(p.counters + nt, 1) == split - 1);
+    __syncthreads();
+    finish = *s_last != 0;
+    if (finish) {
+      __threadfence();
+      if (n < p.N)
+        for (int m = 0; m < p.M; m++) {
+          float s = 0.f;
+          for (int k = 0; k < split; k++) s += __ldcg(p.partials + ((size_t)k * MP + m) * p.N + n);
+          v[m] = s;
+        }
+      if (tid == 0) p.counters[nt] = 0;
+    }
+  }
+  if (finish && n < p.N) {
+    const float b = (p.epi != EPI_NONE) ? __bfloat162float(p.bias[n]) : 0.f;
+    for (int m = 0; m < p.M; m++) {
+      float x = v[m] + b;
+      if (p.epi == EPI_BIAS_GELU) {
+        const bf16 pre = __float2bfloat16(x);
+        p.aux[(size_t)m * p.ldaux + n] = pre;
+        x = gelu_tanh(__bfloat162float(pre));
+      } else if (p.epi == EPI_BIAS_RESID) {
+        x += __bfloat162float(p.aux[(size_t)m * p.ldaux + n]);
+      }
+      p.out[(size_t)m * p.ldo + n] = __float2bfloat16(x);
+    }
+  }
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+int g_sms = 0;
+int num_sms() {
+  if (!g_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sms <= 0) g_sms = 148;
+  }
+  return g_sms;
+}
+int pad_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+int pick_split(int N, int K) {
+  const int n_tiles = (N + TN - 1) / TN, num_kb = (K + BK - 1) / BK;
+  int split = (2 * num_sms() + n_tiles - 1) / n_tiles;       // about two CTAs per SM
+  const int min_split = (num_kb + MAX_KB - 1) / MAX_KB;
+  if (split < min_split) split = min_split;
+  if (split > num_kb) split = num_kb;
+  const int per = (num_kb + split - 1) / split;
+  return (num_kb + per - 1) / per;                            // no empty slices
+}
+
+template <int MP>
+int launch(const CUtensorMap* mw, const CUtensorMap* mx, const SkinnyParams& p, int n_tiles, int split, cudaStream_t st) {
+  constexpr int SMEM = MAX_KB * (TN * BK * 2 + MP * BK * 2) + 1024 + 128;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) { kh_set_error("gemm_skinny: shared memory opt-in failed: %s", cudaGetErrorString(e)); return -1; }
+    attr = true;
+  }
+  dim3 grid(n_tiles, split);
+  gemm_skinny_kernel<MP><<<grid, 128, SMEM, st>>>(*mw, *mx, p);
+  KH_LAUNCH_CHECK("gemm_skinny");
+  return 0;
+}
+}  // namespace
+
+// fp32 elements of scratch needed for an [M,K] x [N,K]^T product (counter slots included, zeroed once)
+extern "C" long kh_gemm_skinny_scratch_elems(int M, int N, int K) {
+  return COUNTER_SLOTS + (long)pick_split(N, K) * pad_rows(M) * N;
+}
+extern "C" int kh_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
+                              int epi, const void* bias, void* aux, int ldaux, void* scratch, void* stream) {
+  if (M < 1 || M > 64) { kh_set_error("gemm_skinny: M=%d outside [1, 64]", M); return -1; }
+  const int n_tiles = (N + TN - 1) / TN;
+  if (n_tiles > COUNTER_SLOTS) { kh_set_error("gemm_skinny: N=%d exceeds %d column tiles", N, COUNTER_SLOTS * TN); return -1; }
+  if (epi != EPI_NONE && !bias) { kh_set_error("gemm_skinny: bias missing"); return -1; }
+  if ((epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESID) && !aux) { kh_set_error("gemm_skinny: aux operand missing"); return -1; }
+  const int MP = pad_rows(M);
+  const CUtensorMap* mw = kh_tmap_2d_bf16(W, N, K, ldw, TN, BK);
+  const CUtensorMap* mx = kh_tmap_2d_bf16(x, M, K, ldx, MP, BK);
+  if (!mw || !mx) return -1;
+  SkinnyParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.num_kb = (K + BK - 1) / BK;
+  const int split = pick_split(N, K);
+  p.kb_per_cta = (p.num_kb + split - 1) / split;
+  p.out = (bf16*)out; p.ldo = ldo; p.epi = epi; p.bias = (const bf16*)bias; p.aux = (bf16*)aux; p.ldaux = ldaux;
+  p.counters = (int*)scratch; p.partials = (float*)scratch + COUNTER_SLOTS;
+  p.err = kh_error_word_dev();
+  cudaStream_t st = (cudaStream_t)stream;
+  if (MP == 16) return launch<16>(mw, mx, p, n_tiles, split, st);
+  if (MP == 32) return launch<32>(mw, mx, p, n_tiles, split, st);
+  return launch<64>(mw, mx, p, n_tiles, split, st);
+}

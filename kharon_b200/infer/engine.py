@@ -77,6 +77,12 @@ class InferEngine:
         self.logits = torch.zeros(ms_, model.Vp, dtype=self.dt, **z)
         self.d_out = torch.zeros(ms_ * 64, dtype=torch.int32, **z)
         self.h_out = torch.zeros(ms_ * 64, dtype=torch.int32, pin_memory=pin)
+        # decode steps (few rows) use the weight-streaming split-K GEMM; its scratch covers every shape used
+        self.skinny = None
+        if self.dev.type == "cuda":
+            shapes = [(3 * dl, d), (d, dl), (fo, d), (d, fo), (cfg.vocab, d)]
+            n = max(ops.gemm_skinny_scratch_elems(ops.SKINNY_MAX_ROWS, N, K) for N, K in shapes)
+            self.skinny = torch.zeros(n, dtype=torch.float32, **z)
         self.temperature, self.seed, self.step_no = 0.0, 0, 0
         self.use_graphs = bool(use_graphs and self.dev.type == "cuda" and self.tp == 1)
         self.graphs = {}
@@ -114,22 +120,36 @@ class InferEngine:
         for l in range(cfg.n_layer):
             ln, qkv, att, xmid = self.ln[:ntok], self.qkv[:ntok], self.att[:ntok], self.xmid[:ntok]
             ops.layernorm_fwd(xs, m.L(l, "ln1_w"), m.L(l, "ln1_b"), ln)
-            ops.gemm(ln, m.L(l, "qkv_w"), qkv, epi=ops.EPI_BIAS, bias=m.L(l, "qkv_b"))
+            self._lin(ln, m.L(l, "qkv_w"), qkv, ops.EPI_BIAS, m.L(l, "qkv_b"))
             ops.append_kv(qkv, self.kc[l], self.vc[l], pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok)
             ops.paged_attn(qkv, self.kc[l], self.vc[l], att, pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok,
                            cfg.seq)
             # row-parallel products: one GEMM, or under TP the fused GEMM + all-reduce kernel / NCCL seam
-            m._row_parallel(att, m.L(l, "proj_w"), xmid, m.L(l, "proj_b"), xs)
+            self._row(att, m.L(l, "proj_w"), xmid, m.L(l, "proj_b"), xs)
             ops.layernorm_fwd(xmid, m.L(l, "ln2_w"), m.L(l, "ln2_b"), ln)
-            ops.gemm(ln, m.L(l, "fc_w"), self.act[:ntok], epi=ops.EPI_BIAS_GELU, bias=m.L(l, "fc_b"), aux=self.pre[:ntok])
+            self._lin(ln, m.L(l, "fc_w"), self.act[:ntok], ops.EPI_BIAS_GELU, m.L(l, "fc_b"), self.pre[:ntok])
             ys = nxt[:ntok]
-            m._row_parallel(self.act[:ntok], m.L(l, "fcproj_w"), ys, m.L(l, "fcproj_b"), xmid)
+            self._row(self.act[:ntok], m.L(l, "fcproj_w"), ys, m.L(l, "fcproj_b"), xmid)
             x, nxt = nxt, x
             xs = ys
         ops.gather_rows(xs, self.d_rows, self.last, nseq)
         ops.layernorm_fwd(self.last[:nseq], P["lnf_w"], P["lnf_b"], self.lnf[:nseq])
-        ops.gemm(self.lnf[:nseq], m.head_weight(), self.logits[:nseq, :cfg.vocab])
+        self._lin(self.lnf[:nseq], m.head_weight(), self.logits[:nseq, :cfg.vocab])
         ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq)
+
+    def _lin(self, x, w, out, epi=ops.EPI_NONE, bias=None, aux=None):
+        """Column-parallel / replicated linear layer: skinny kernel for decode-sized inputs."""
+        if self.skinny is not None and x.shape[0] <= ops.SKINNY_MAX_ROWS:
+            ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux)
+        else:
+            ops.gemm(x, w, out, epi=epi, bias=bias, aux=aux)
+
+    def _row(self, x, w, out, bias, resid):
+        """Row-parallel linear layer (+ bias + residual); summed over the TP group when there is one."""
+        if self.tp == 1:
+            self._lin(x, w, out, ops.EPI_BIAS_RESID, bias, resid)
+        else:
+            self.model._row_parallel(x, w, out, bias, resid)
 
     def _run(self, ntok, nseq, rep=1):
         """Metadata is already in ``h_meta``; runs one step and returns the sampled ids (host)."""

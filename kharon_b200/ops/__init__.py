@@ -145,6 +145,27 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, accumulate=False, epi=EPI_NONE, b
     return out
 
 
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny_scratch_elems(M, N, K):
+    return int(_lib().kh_gemm_skinny_scratch_elems(M, N, K)) if torch.cuda.is_available() else 0
+
+
+def gemm_skinny(x, w, out, scratch, *, epi=EPI_NONE, bias=None, aux=None):
+    """out[M,N] = x[M,K] @ w[N,K]^T (+ epilogue) for M <= 64: the weight-streaming split-K kernel used
+    by decode steps.  ``scratch`` (gemm_skinny_scratch_elems fp32, zeroed once) holds ticket counters
+    and split-K partials.  Epilogues: EPI_NONE, EPI_BIAS, EPI_BIAS_GELU (aux = pre-activation out),
+    EPI_BIAS_RESID (aux = residual in)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not x.is_cuda:
+        return ref.gemm(x, w, out, False, False, False, epi, bias, aux, 1.0)
+    _call(_lib().kh_gemm_skinny, 1, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+          M, N, K, epi, _p(bias), _p(aux), aux.stride(0) if aux is not None else 0, scratch.data_ptr(), _stream())
+    return out
+
+
 # ------------------------------------------------------------------------------ embedding
 def embed_fwd(tok, pos, wte, wpe, out, T):
     if not out.is_cuda:

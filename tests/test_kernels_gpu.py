@@ -193,5 +193,29 @@ def test_flash_fwd_bwd(B, T, H, hd):
         assert e < 2e-2, (name, e)
 
 
+@pytest.mark.parametrize("M", [1, 8, 17, 32, 64])
+@pytest.mark.parametrize("N,K", [(3072, 1024), (1024, 4096), (50257, 1024), (200, 192)])
+def test_gemm_skinny(M, N, K):
+    torch.manual_seed(9)
+    x = _rand(M, K, scale=0.5)
+    w = _rand(N, K, scale=0.1)
+    bias = _rand(N)
+    ld = (N + 63) // 64 * 64
+    scratch = torch.zeros(ops.gemm_skinny_scratch_elems(M, N, K), device=DEV)
+    for epi in (ops.EPI_NONE, ops.EPI_BIAS, ops.EPI_BIAS_GELU, ops.EPI_BIAS_RESID):
+        aux = _rand(M, ld)[:, :N]
+        aux_ref = aux.clone()
+        out = torch.zeros(M, ld, device=DEV, dtype=torch.bfloat16)[:, :N]
+        want = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_skinny(x, w, out, scratch, epi=epi, bias=bias, aux=aux)
+        ref.gemm(x, w, want, False, False, False, epi, bias, aux_ref, 1.0)
+        assert relerr(out, want) < 8e-3, (epi, relerr(out, want))
+        out2 = torch.zeros_like(out)
+        ops.gemm_skinny(x, w, out2, scratch, epi=epi, bias=bias, aux=aux_ref.clone())
+        assert torch.equal(out, out2)               # split-K partials are added in a fixed order
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+
+
 def test_bounded_wait_status_word_is_clean():
     assert ops.error_word() == 0
