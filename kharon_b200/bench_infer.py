@@ -30,6 +30,7 @@ def run(argv=None):
     reps = f.int("reps", 2, "timed repetitions per G (best is reported); the first warms graphs up")
     tp_flag = f.int("tp", 0, "tensor-parallel degree (0 = world size under torchrun)")
     fused = not f.has("no-fused-comm")
+    graphs = not f.has("no-graphs")
     f.maybe_help()
     cfg = Config(L, d, H, V, seq, 1)
     import torch.distributed as dist
@@ -59,7 +60,7 @@ def run(argv=None):
     max_lb = (seq + bs - 1) // bs
     results = {"decode": [], "prefix": []}
     for G in Gs:
-        eng = InferEngine(m, bs, G * max_lb + 16, max(G, plen) * 1 + G * plen + 64, G + 1)
+        eng = InferEngine(m, bs, G * max_lb + 16, max(G, plen) * 1 + G * plen + 64, G + 1, use_graphs=graphs)
         best = None
         for _ in range(max(1, reps)):
             outs, st, ms = eng.generate([prompt] * G, n_new, max_active=G)

@@ -116,8 +116,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   bool finish = ok;
   if (ok && split > 1) {
-    if (n < p.N)
-      for (int m = 0; m < p.M; m++) p.partials[((size_t)ks * MP + m) * p.N + n] = v[m];
+    if (n < p.N) {
+#pragma unroll
+      for (int m = 0; m < MP; m++)
+        if (m < p.M) p.partials[((size_t)ks * MP + m) * p.N + n] = v[m];
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) *s_last = (atomicAdd(p.counters + nt, 1) == split - 1);
@@ -125,18 +128,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     finish = *s_last != 0;
     if (finish) {
       __threadfence();
-      if (n < p.N)
-        for (int m = 0; m < p.M; m++) {
-          float s = 0.f;
-          for (int k = 0; k < split; k++) s += __ldcg(p.partials + ((size_t)k * MP + m) * p.N + n);
-          v[m] = s;
+      if (n < p.N) {
+#pragma unroll
+        for (int m = 0; m < MP; m++) v[m] = 0.f;
+        for (int k = 0; k < split; k++) {          // slices in index order; the MP loads of a slice are independent
+#pragma unroll
+          for (int m = 0; m < MP; m++)
+            if (m < p.M) v[m] += __ldcg(p.partials + ((size_t)k * MP + m) * p.N + n);
         }
+      }
       if (tid == 0) p.counters[nt] = 0;
     }
   }
   if (finish && n < p.N) {
     const float b = (p.epi != EPI_NONE) ? __bfloat162float(p.bias[n]) : 0.f;
-    for (int m = 0; m < p.M; m++) {
+#pragma unroll
+    for (int m = 0; m < MP; m++) {
+      if (m >= p.M) break;
       float x = v[m] + b;
       if (p.epi == EPI_BIAS_GELU) {
         const bf16 pre = __float2bfloat16(x);
@@ -165,7 +173,10 @@ int num_sms() {
 int pad_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 int pick_split(int N, int K) {
   const int n_tiles = (N + TN - 1) / TN, num_kb = (K + BK - 1) / BK;
-  int split = (2 * num_sms() + n_tiles - 1) / n_tiles;       // about two CTAs per SM
+  // every CTA issues all of its loads at once (up to 8 x 16 KB in flight), so one CTA per SM already
+  // saturates HBM; more slices only lengthen the reduction
+  int split = (num_sms() + n_tiles - 1) / n_tiles;
+  if (split > 8) split = 8;
   const int min_split = (num_kb + MAX_KB - 1) / MAX_KB;
   if (split < min_split) split = min_split;
   if (split > num_kb) split = num_kb;

@@ -107,6 +107,12 @@ class TrainEngine:
                 self.zero_fused.finalize()
         self.plans = {}
         self.use_plans = self.device.type == "cuda"
+        # host -> device input staging (see _upload)
+        self._par = 0
+        if self.device.type == "cuda":
+            self.copy_stream = torch.cuda.Stream(self.device)
+            self.stage = [[torch.zeros_like(self.tok_dev), torch.zeros_like(self.tgt_dev)] for _ in range(2)]
+            self.stage_free = [None, None]
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -142,12 +148,39 @@ class TrainEngine:
         self.plans[key] = (plan, out)
         return out
 
+    def _upload(self, idx, tgt):
+        """Bring the step's token ids onto the device.  Host tensors go through a copy stream into one
+        of two staging buffers and the call returns only when that copy has completed, so the caller
+        may overwrite its (pinned) host buffers right away even while the GPU is still busy with the
+        previous step; the compute stream then moves the staged ids into place in stream order."""
+        idx, tgt = idx.reshape(-1), tgt.reshape(-1)
+        if self.device.type != "cuda" or idx.is_cuda:
+            self.tok_dev.copy_(idx, non_blocking=True)
+            self.tgt_dev.copy_(tgt, non_blocking=True)
+            return
+        self._par ^= 1
+        par = self._par
+        cur = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.copy_stream):
+            if self.stage_free[par] is not None:
+                self.copy_stream.wait_event(self.stage_free[par])    # its previous reader has finished
+            self.stage[par][0].copy_(idx, non_blocking=True)
+            self.stage[par][1].copy_(tgt, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.copy_stream)
+        done.synchronize()
+        cur.wait_event(done)
+        self.tok_dev.copy_(self.stage[par][0], non_blocking=True)
+        self.tgt_dev.copy_(self.stage[par][1], non_blocking=True)
+        free = torch.cuda.Event()
+        free.record(cur)
+        self.stage_free[par] = free
+
     # ------------------------------------------------------------------ one step
     def train_step(self, idx, tgt):
         """idx/tgt: int32 [M * mbatch * seq] for this replica (host or device)."""
         m, c = self.model, self.mesh.c
-        self.tok_dev.copy_(idx.reshape(-1), non_blocking=True)
-        self.tgt_dev.copy_(tgt.reshape(-1), non_blocking=True)
+        self._upload(idx, tgt)
         M = self.M
         inv = 1.0 / M
         cur_act = cur_grad = None
