@@ -139,7 +139,7 @@ class InferEngine:
 
     def _lin(self, x, w, out, epi=ops.EPI_NONE, bias=None, aux=None):
         """Column-parallel / replicated linear layer: skinny kernel for decode-sized inputs."""
-        if self.skinny is not None and x.shape[0] <= ops.SKINNY_MAX_ROWS:
+        if self.skinny is not None and x.shape[0] <= ops.SKINNY_BEST_ROWS:
             ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux)
         else:
             ops.gemm(x, w, out, epi=epi, bias=bias, aux=aux)
