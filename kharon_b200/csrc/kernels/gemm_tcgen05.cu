@@ -153,19 +153,27 @@ struct GemmParams {
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 
-template <int BN> struct GemmCfg {
+// PAIR: two CTAs of a cluster form one 256 x BN tile (tcgen05 cta_group::2).  Each CTA stages its
+// own 128 rows of A and its own half of B, so a pair moves and re-reads 2/3 of the shared-memory
+// bytes of two independent 128 x BN tiles.
+template <int BN, bool PAIR = false> struct GemmCfg {
+  static constexpr int BN_CTA = PAIR ? BN / 2 : BN;          // B rows (or columns) staged by one CTA
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = PAIR ? 6 : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
+  constexpr int TM = PAIR ? 2 * BM : BM;                       // rows of one scheduled tile
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;        // 0 = leader (issues the MMAs)
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -179,20 +187,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_m = (p.M + TM - 1) / TM, tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
+    // accumulator-free barrier: one arrival per epilogue warp of every CTA that reads the accumulator
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, PAIR ? 8 : 4); }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 1) {
+    if (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+  }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tma_a); tma_prefetch_desc(&tma_b); }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -212,35 +225,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      for (int t = worker; ok && t < num_tiles; t += n_workers) {
         int tm, tn;
         tile_coord(t, tm, tn);
+        const int m0 = tm * TM + (int)crank * BM;               // first A row of this CTA
+        const int n0 = tn * BN + (int)crank * Cfg::BN_CTA;      // first B row/column of this CTA
         for (int kb = 0; kb < num_kb; kb++, it++) {
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
           const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
-          mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
-          if (!p.a_mn) tma_load_2d(sa, &tma_a, bar_full + 8 * s, kb * BK, tm * BM);
-          else
-            for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), &tma_a, bar_full + 8 * s, tm * BM + j * 64, kb * BK);
-          if (!p.b_mn) tma_load_2d(sb, &tma_b, bar_full + 8 * s, kb * BK, tn * BN);
-          else
-            for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * (BK * 128), &tma_b, bar_full + 8 * s, tn * BN + j * 64, kb * BK);
+          if (!PAIR) {
+            mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
+            if (!p.a_mn) tma_load_2d(sa, &tma_a, bar_full + 8 * s, kb * BK, m0);
+            else
+              for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), &tma_a, bar_full + 8 * s, m0 + j * 64, kb * BK);
+            if (!p.b_mn) tma_load_2d(sb, &tma_b, bar_full + 8 * s, kb * BK, n0);
+            else
+              for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * (BK * 128), &tma_b, bar_full + 8 * s, n0 + j * 64, kb * BK);
+          } else {
+            // both CTAs credit the leader's barrier; the leader expects the bytes of the whole pair
+            const uint32_t lbar = mapa_shared(bar_full + 8 * s, 0);
+            if (crank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * Cfg::STAGE_BYTES);
+            if (!p.a_mn) tma_load_2d_pair(sa, &tma_a, lbar, kb * BK, m0);
+            else
+              for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &tma_a, lbar, m0 + j * 64, kb * BK);
+            if (!p.b_mn) tma_load_2d_pair(sb, &tma_b, lbar, kb * BK, n0);
+            else
+              for (int j = 0; j < Cfg::BN_CTA / 64; j++) tma_load_2d_pair(sb + j * (BK * 128), &tma_b, lbar, n0 + j * 64, kb * BK);
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+    if (lane == 0 && crank == 0) {
+      const uint32_t idesc = umma_idesc_bf16(TM, BN, p.a_mn, p.b_mn);
       // K-major: LBO unused (encoded 16 B), SBO 1024; MN-major: LBO = one 64-wide slab (BK rows x 128 B), SBO 1024
       const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, b_lbo = p.b_mn ? BK * 128 : 16;
       const uint32_t a_kstep = p.a_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
       const uint32_t b_kstep = p.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
       int it = 0, tcount = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+      for (int t = worker; ok && t < num_tiles; t += n_workers, tcount++) {
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
         if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1, abort_flag, 4, p.err)) { ok = false; break; }
@@ -256,12 +283,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           uint64_t bdesc = umma_desc_sw128(sb, b_lbo, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
-            umma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc,
-                        (kb > 0 || k > 0) ? 1u : 0u);
+            if (PAIR) umma_f16_ss_pair(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(bar_empty + 8 * s);   // stage reusable once these MMAs retire
+          // stage reusable (in both CTAs of a pair) once these MMAs retire
+          if (PAIR) umma_commit_pair(bar_empty + 8 * s, 3); else umma_commit(bar_empty + 8 * s);
         }
-        if (ok) umma_commit(bar_tfull + 8 * acc);
+        if (ok) { if (PAIR) umma_commit_pair(bar_tfull + 8 * acc, 3); else umma_commit(bar_tfull + 8 * acc); }
       }
     }
   } else {
@@ -269,14 +299,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     const int q = warp & 3;                    // TMEM lane quadrant this warp may access
     int tcount = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+    for (int t = worker; ok && t < num_tiles; t += n_workers, tcount++) {
       int tm, tn;
       tile_coord(t, tm, tn);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
+      const int row = tm * TM + (int)crank * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
@@ -380,16 +410,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));   // the leader issues the MMAs
+        else mbar_arrive(bar_tempty + 8 * acc);
+      }
     }
   }
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // no CTA leaves while its peer may still signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -405,19 +439,49 @@ static int num_sms() {
   return g_num_sms;
 }
 
+// 256-row tiles on CTA pairs.  Returns the number of clusters that can be resident (0: unsupported).
+static int g_pair_clusters = -1;
+static int launch_gemm_pair(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParams& p, int max_ctas, cudaStream_t st) {
+  using Cfg = GemmCfg<256, true>;
+  auto kern = gemm_kernel<256, true>;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+  if (g_pair_clusters < 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) { kh_set_error("gemm: cannot opt in to %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e)); return -1; }
+    cfg.gridDim = dim3(2 * (num_sms() / 2));
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess || n < 1) { cudaGetLastError(); kh_set_error("gemm: CTA-pair launch is not available: %s", cudaGetErrorString(e)); g_pair_clusters = 0; return -1; }
+    g_pair_clusters = n;
+  }
+  if (g_pair_clusters == 0) { kh_set_error("gemm: CTA-pair launch is not available"); return -1; }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
+  int clusters = tiles < g_pair_clusters ? tiles : g_pair_clusters;
+  if (max_ctas > 0 && 2 * clusters > max_ctas) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  cfg.gridDim = dim3(2 * clusters);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb, p);
+  if (e != cudaSuccess) { kh_set_error("gemm pair launch failed: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+extern "C" int kh_gemm_pair_clusters() { return g_pair_clusters; }
+
 template <int BN>
 static int launch_gemm(const CUtensorMap* ta, const CUtensorMap* tb, const GemmParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) { kh_set_error("gemm: cannot opt in to %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e)); return -1; }
     attr_set = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(*ta, *tb, p);
+  gemm_kernel<BN, false><<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(*ta, *tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kh_set_error("gemm launch failed: %s", cudaGetErrorString(e)); return -1; }
   return 0;
@@ -448,16 +512,19 @@ extern "C" int kh_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int
     if (N <= 64) bn = 64;
     else if (N <= 128 && bn == 256) bn = 128;
   }
-  if (bn != 64 && bn != 128 && bn != 256) { kh_set_error("gemm: block_n must be 64, 128 or 256"); return -1; }
+  const bool pair = (bn == 512);      // 256 x 256 tiles on CTA pairs (cta_group::2)
+  if (pair) bn = 256;
+  if (bn != 64 && bn != 128 && bn != 256) { kh_set_error("gemm: block_n must be 64, 128, 256 or 512 (CTA pairs)"); return -1; }
   const CUtensorMap* ta = a_mn ? kh_tmap_2d_bf16(A, K, M, lda, BK, 64) : kh_tmap_2d_bf16(A, M, K, lda, BM, BK);
   if (!ta) return -1;
-  const CUtensorMap* tb = b_mn ? kh_tmap_2d_bf16(B, K, N, ldb, BK, 64) : kh_tmap_2d_bf16(B, N, K, ldb, bn, BK);
+  const CUtensorMap* tb = b_mn ? kh_tmap_2d_bf16(B, K, N, ldb, BK, 64) : kh_tmap_2d_bf16(B, N, K, ldb, pair ? 128 : bn, BK);
   if (!tb) return -1;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
   p.accumulate = accumulate; p.epi = epi; p.bias = (const bf16*)bias; p.aux = (bf16*)aux; p.ldaux = ldaux; p.alpha = alpha;
   p.err = kh_error_word_dev();
   cudaStream_t st = (cudaStream_t)stream;
+  if (pair) return launch_gemm_pair(ta, tb, p, max_ctas, st);
   if (bn == 256) return launch_gemm<256>(ta, tb, p, max_ctas, st);
   if (bn == 128) return launch_gemm<128>(ta, tb, p, max_ctas, st);
   return launch_gemm<64>(ta, tb, p, max_ctas, st);

@@ -36,6 +36,28 @@ def test_gemm_majors(a_mn, b_mn, M, N, K, bn):
     assert relerr(out, want) < 6e-3, relerr(out, want)
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (384, 328, 192), (1000, 1024, 1024), (4096, 2048, 512)])
+def test_gemm_cta_pairs(a_mn, b_mn, M, N, K):
+    """256 x 256 tiles on CTA pairs (cta_group::2) against the PyTorch product, ragged edges included."""
+    torch.manual_seed(10)
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    bias, resid = _rand(N), _rand(M, N)
+    out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, block_n=512, epi=ops.EPI_BIAS_RESID, bias=bias, aux=resid)
+    want = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ref.gemm(a, b, want, a_mn, b_mn, False, ops.EPI_BIAS_RESID, bias, resid, 1.0)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+    assert relerr(out, want) < 6e-3, relerr(out, want)
+    acc = torch.ones(M, N, device=DEV)
+    ops.gemm(a, b, acc, a_mn=a_mn, b_mn=b_mn, block_n=512, accumulate=True)
+    wf = torch.empty(M, N, device=DEV)
+    ref.gemm(a, b, wf, a_mn, b_mn, False, 0, None, None, 1.0)
+    assert relerr(acc, 1 + wf) < 1e-4
+
+
 def test_gemm_fp32_accumulate_and_alpha():
     torch.manual_seed(1)
     M, N, K = 256, 384, 320
