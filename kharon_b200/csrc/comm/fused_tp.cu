@@ -364,49 +364,37 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
         for (int i = 0; i < RB; i++)
 #pragma unroll
           for (int k = 0; k < 8; k++) a8[i][k] = bias8[k];
-        auto add8 = [&](float* acc, const uint4& v) {
-          float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-        };
-        auto src_of = [&](int r, int row) -> const uint4* {
-          const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
-          return (r == p.rank) ? reinterpret_cast<const uint4*>(p.out + (size_t)out_row * p.ldo + col)
-                               : reinterpret_cast<const uint4*>(p.stage[p.rank] + ((size_t)r * p.M + row) * p.N + col);
-        };
-        const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        if (p.tp == 2) {
-          // all 3 x RB loads are issued before the first use: one memory round trip per pass
-          uint4 v0[RB], v1[RB], vr[RB];
+        for (int r = 0; r < p.tp; r++) {
+          uint4 v[RB];
 #pragma unroll
           for (int i = 0; i < RB; i++) {
             const int row = row0 + i;
-            const bool in = row < row_end;
             const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
-            v0[i] = in ? __ldcg(src_of(0, row)) : zero4;
-            v1[i] = in ? __ldcg(src_of(1, row)) : zero4;
-            vr[i] = (in && p.resid) ? *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col) : zero4;
+            const uint4* src = (r == p.rank)
+                                   ? reinterpret_cast<const uint4*>(p.out + (size_t)out_row * p.ldo + col)
+                                   : reinterpret_cast<const uint4*>(p.stage[p.rank] + ((size_t)r * p.M + row) * p.N + col);
+            v[i] = row < row_end ? __ldcg(src) : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
-          for (int i = 0; i < RB; i++) { add8(a8[i], v0[i]); add8(a8[i], v1[i]); add8(a8[i], vr[i]); }
-        } else {
-          for (int r = 0; r < p.tp; r++) {
-            uint4 v[RB];
-#pragma unroll
-            for (int i = 0; i < RB; i++) v[i] = (row0 + i) < row_end ? __ldcg(src_of(r, row0 + i)) : zero4;
-#pragma unroll
-            for (int i = 0; i < RB; i++) add8(a8[i], v[i]);
+          for (int i = 0; i < RB; i++) {
+            float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y), f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+            a8[i][0] += f0.x; a8[i][1] += f0.y; a8[i][2] += f1.x; a8[i][3] += f1.y;
+            a8[i][4] += f2.x; a8[i][5] += f2.y; a8[i][6] += f3.x; a8[i][7] += f3.y;
           }
-          if (p.resid) {
-            uint4 v[RB];
+        }
+        if (p.resid) {
+          uint4 v[RB];
 #pragma unroll
-            for (int i = 0; i < RB; i++) {
-              const int row = row0 + i;
-              const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
-              v[i] = row < row_end ? *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col) : zero4;
-            }
+          for (int i = 0; i < RB; i++) {
+            const int row = row0 + i;
+            const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+            v[i] = row < row_end ? *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col) : make_uint4(0, 0, 0, 0);
+          }
 #pragma unroll
-            for (int i = 0; i < RB; i++) add8(a8[i], v[i]);
+          for (int i = 0; i < RB; i++) {
+            float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y), f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+            a8[i][0] += f0.x; a8[i][1] += f0.y; a8[i][2] += f1.x; a8[i][3] += f1.y;
+            a8[i][4] += f2.x; a8[i][5] += f2.y; a8[i][6] += f3.x; a8[i][7] += f3.y;
           }
         }
 #pragma unroll
