@@ -52,8 +52,11 @@ def pp_num_slots(stage: int, n_stages: int, n_micro: int) -> int:
 class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
-                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False):
+                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None):
+        from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
+        self.tracer = Tracer(enabled=bool(trace))     # per-phase CUDA-event timeline (forward / backward / p2p / optimizer)
+        self.heartbeat = heartbeat                     # utils.watchdog.Heartbeat: peers are checked before every step
         c = self.mesh.c
         self.device = torch.device(device)
         if layers % c.pp:
@@ -180,7 +183,11 @@ class TrainEngine:
     def train_step(self, idx, tgt):
         """idx/tgt: int32 [M * mbatch * seq] for this replica (host or device)."""
         m, c = self.model, self.mesh.c
-        self._upload(idx, tgt)
+        if self.heartbeat is not None:
+            self.heartbeat.check()      # raises RankFailure before any kernel that would wait on a dead peer
+        tr = self.tracer
+        with tr.range("upload"):
+            self._upload(idx, tgt)
         M = self.M
         inv = 1.0 / M
         cur_act = cur_grad = None
@@ -189,34 +196,40 @@ class TrainEngine:
         n_loss = 0
         for op, a0, a1 in self.schedule:
             if op == PP_FWD:
-                out_act[a0] = self._compute(("F", a0, a1), lambda: (
-                    self._stage_input(a0), m.forward(slot=a1, x_in=cur_act, compute_loss=False))[1])
-            elif op == PP_BWD:
+                with tr.range("forward"):
+                    out_act[a0] = self._compute(("F", a0, a1), lambda: (
+                        self._stage_input(a0), m.forward(slot=a1, x_in=cur_act, compute_loss=False))[1])
+                continue
+            if op == PP_BWD:
                 dxo = None if c.last else cur_grad
                 first_loss = n_loss == 0
-                in_grad[a0] = self._compute(("B", a0, a1), lambda: m.backward(
-                    slot=a1, dx_out=dxo, inv_mb=inv, loss_scale=inv, accumulate_loss=not first_loss))
+                with tr.range("backward"):
+                    in_grad[a0] = self._compute(("B", a0, a1), lambda: m.backward(
+                        slot=a1, dx_out=dxo, inv_mb=inv, loss_scale=inv, accumulate_loss=not first_loss))
                 n_loss += 1
-            elif op == PP_RECV_ACT:
-                cur_act = self.recv_act[a0 & 1]
-                self._p2p([dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
-            elif op == PP_SEND_ACT:
-                self._p2p([dist.P2POp(dist.isend, out_act.pop(a0), c.next_rank)])
-            elif op == PP_RECV_GRAD:
-                cur_grad = self.recv_grad[a0 & 1]
-                self._p2p([dist.P2POp(dist.irecv, cur_grad, c.next_rank)])
-            elif op == PP_SEND_GRAD:
-                self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank)])
-            elif op == PP_SEND_ACT_RECV_GRAD:     # a0 = micro-batch sent, a1 = micro-batch whose grad arrives
-                cur_grad = self.recv_grad[a1 & 1]
-                self._p2p([dist.P2POp(dist.isend, out_act.pop(a0), c.next_rank),
-                           dist.P2POp(dist.irecv, cur_grad, c.next_rank)])
-            elif op == PP_SEND_GRAD_RECV_ACT:     # a0 = micro-batch whose grad is sent, a1 = next activation
-                cur_act = self.recv_act[a1 & 1]
-                self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank),
-                           dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
-        self._tie_embedding_grads()
-        self.optimizer_step()
+                continue
+            with tr.range("pipeline p2p"):
+                if op == PP_RECV_ACT:
+                    cur_act = self.recv_act[a0 & 1]
+                    self._p2p([dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
+                elif op == PP_SEND_ACT:
+                    self._p2p([dist.P2POp(dist.isend, out_act.pop(a0), c.next_rank)])
+                elif op == PP_RECV_GRAD:
+                    cur_grad = self.recv_grad[a0 & 1]
+                    self._p2p([dist.P2POp(dist.irecv, cur_grad, c.next_rank)])
+                elif op == PP_SEND_GRAD:
+                    self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank)])
+                elif op == PP_SEND_ACT_RECV_GRAD:     # a0 = micro-batch sent, a1 = micro-batch whose grad arrives
+                    cur_grad = self.recv_grad[a1 & 1]
+                    self._p2p([dist.P2POp(dist.isend, out_act.pop(a0), c.next_rank),
+                               dist.P2POp(dist.irecv, cur_grad, c.next_rank)])
+                elif op == PP_SEND_GRAD_RECV_ACT:     # a0 = micro-batch whose grad is sent, a1 = next activation
+                    cur_act = self.recv_act[a1 & 1]
+                    self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank),
+                               dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
+        with tr.range("optimizer"):
+            self._tie_embedding_grads()
+            self.optimizer_step()
         return m.loss_acc
 
     def _tie_embedding_grads(self):

@@ -39,14 +39,30 @@ def _pad64(n):
     return (n + 63) // 64 * 64
 
 
+_ALLOCATOR = None
+
+
+def set_allocator(alloc):
+    """Route activation / scratch allocations of models constructed afterwards through ``alloc``
+    (``utils.guards.GuardedAlloc`` adds canary bands around every buffer); None restores torch.empty."""
+    global _ALLOCATOR
+    _ALLOCATOR = alloc
+
+
+def _buf(shape, dtype, dev):
+    if _ALLOCATOR is not None:
+        return _ALLOCATOR.empty(shape, dtype, dev)
+    return torch.empty(*shape, dtype=dtype, device=dev)
+
+
 class _Slot:
     """Activation stash of one in-flight micro-batch."""
 
     def __init__(self, cfg: Config, tp, dev, dt, first, last, Vp):
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo, Hl = d // tp, 4 * d // tp, cfg.n_head // tp
-        e = lambda *s: torch.empty(*s, dtype=dt, device=dev)
-        f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
+        e = lambda *s: _buf(s, dt, dev)
+        f = lambda *s: _buf(s, torch.float32, dev)
         self.x = [e(R, d) for _ in range(cfg.n_layer + 1)]   # residual stream: x[l] enters layer l
         self.layers = []
         for _ in range(cfg.n_layer):
@@ -80,7 +96,7 @@ class GPT:
         self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp) for _ in range(n_slots)]
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo = d // tp, 4 * d // tp
-        e = lambda *s: torch.empty(*s, dtype=dtype, device=self.device)
+        e = lambda *s: _buf(s, dtype, self.device)
         # backward scratch, shared by all layers and slots
         self.s_dx = [e(R, d), e(R, d)]
         self.s_dln = e(R, d)

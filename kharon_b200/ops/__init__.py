@@ -362,6 +362,25 @@ def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
           delta.data_ptr(), B, T, H, hd, qkv.stride(0), scale, _stream())
 
 
+def merge_attention(o1, lse1, o2, lse2):
+    """Combine two attention results computed over disjoint key sets (same queries): the hook for
+    context parallelism -- each rank (or each KV chunk of a ring pass) runs ``flash_fwd`` on its keys
+    and the partial outputs are merged with their log-sum-exps.  ``o*``: [..., hd] , ``lse*``: [...]
+    (natural log).  Returns (o, lse) in fp32.  Not used by the built-in trainers (no sequence beyond
+    one GPU's memory is configured); the reference has no counterpart."""
+    l1, l2 = lse1.float(), lse2.float()
+    m = torch.maximum(l1, l2)
+    w1, w2 = torch.exp(l1 - m), torch.exp(l2 - m)
+    den = w1 + w2
+    o = (o1.float() * w1.unsqueeze(-1) + o2.float() * w2.unsqueeze(-1)) / den.unsqueeze(-1)
+    return o, m + torch.log(den)
+
+
+def wait_probe(flag, target: int, limit_ms: int, status):
+    """Launch the bounded-wait probe on ``flag`` (uint32/int32 CUDA tensor); see csrc/comm/wait_probe.cu."""
+    _call(_lib().kh_wait_probe, 1, flag.data_ptr(), int(target), int(limit_ms), status.data_ptr(), _stream())
+
+
 # ------------------------------------------------------------------------------ paged KV
 def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
     """Scatter k, v of each new token into its block: pool layout [n_blocks, bs, H, hd]."""

@@ -66,13 +66,22 @@ def main(argv=None):
     fused = not f.has("no-fused-comm")
     report = not f.has("no-report")
     dev_flag = f.str("device", "")
+    trace = f.has("trace", "print a per-phase device-time table (CUDA events) at the end")
+    jsonl = f.str("jsonl", "", "append one JSON object per logged step to this file")
+    hb_s = f.float("heartbeat", 0.0, "seconds after which a silent rank counts as dead (0 = off)")
     f.maybe_help()
     rank, world, device = init_distributed(dev_flag or None)
     mesh = Mesh(tp, None, dp) if world > 1 else Mesh.single()
     c = mesh.c
+    hb = None
+    if hb_s > 0 and world > 1:
+        from .utils.watchdog import Heartbeat
+        hb = Heartbeat(rank, world, interval_s=min(1.0, hb_s / 4), timeout_s=hb_s)
+    from .utils.trace import JsonlLogger
+    mlog = JsonlLogger(jsonl if rank == world - 1 else "")
     eng = TrainEngine(L, d, H, vocab, seq, mb, M, mesh=mesh, device=device,
                       dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, untied_head=untied,
-                      fused_comm=fused)
+                      fused_comm=fused, trace=trace, heartbeat=hb)
     if synthetic or not os.path.exists(data_path):
         data = SyntheticData(vocab, M * mb, seq, 42)
     else:
@@ -94,8 +103,13 @@ def main(argv=None):
             loss = eng.loss()
             if rank == last_rank:
                 print("step %5d  loss %.4f" % (st, loss), flush=True)
+                mlog.log(step=st, loss=loss)
     if ckpt:
         eng.save(ckpt, 0)
+    if trace and rank == 0:
+        print("device time per phase on rank 0:\n" + eng.tracer.format())
+    if hb is not None:
+        hb.stop()
     if not report:
         return eng
     # ---- measurement epilogue (differential timing)

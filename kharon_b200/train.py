@@ -32,7 +32,10 @@ def main(argv=None):
     resume, synthetic = f.has("resume"), f.has("synthetic")
     device = f.str("device", "cuda" if torch.cuda.is_available() else "cpu")
     dtype = torch.float32 if f.has("fp32") else torch.bfloat16
+    jsonl = f.str("jsonl", "", "append one JSON object per logged step to this file")
     f.maybe_help()
+    from .utils.trace import JsonlLogger
+    mlog = JsonlLogger(jsonl)
 
     eng = TrainEngine(layers, d, heads, vocab, seq, batch, 1, device=device, dtype=dtype, lr=lr, beta1=b1, beta2=b2,
                       wd=wd, seed=1337, init="host")
@@ -57,7 +60,9 @@ def main(argv=None):
         if st % log == 0 or st == steps:
             loss = eng.loss()          # the only host sync
             dt = time.perf_counter() - t0
-            print("step %5d  loss %.4f  %.0f tok/s" % (st, loss, (st - s0) * batch * seq / max(dt, 1e-9)), flush=True)
+            tps = (st - s0) * batch * seq / max(dt, 1e-9)
+            print("step %5d  loss %.4f  %.0f tok/s" % (st, loss, tps), flush=True)
+            mlog.log(step=st, loss=loss, tok_s=tps)
             t0, s0 = time.perf_counter(), st
         if ckptevery > 0 and st % ckptevery == 0:
             eng.save(ckpt_path, data.rng.state)

@@ -241,3 +241,53 @@ def test_gemm_skinny(M, N, K):
 
 def test_bounded_wait_status_word_is_clean():
     assert ops.error_word() == 0
+
+
+def test_bounded_wait_runs_out_and_reports_status():
+    """A wait on a flag that nothing sets gives up after its limit, reports code 5 through the status
+    word, and leaves the context usable; once the flag is set the same wait succeeds."""
+    flag = torch.zeros(1, device=DEV, dtype=torch.int32)
+    status = torch.full((1,), -1, device=DEV, dtype=torch.int32)
+    ops.wait_probe(flag, 1, 30, status)
+    torch.cuda.synchronize()
+    assert status.item() == 5 and ops.error_word() == 5      # read-and-clear
+    assert ops.error_word() == 0
+    flag.fill_(1)
+    ops.wait_probe(flag, 1, 30, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and ops.error_word() == 0
+    assert torch.ones(4, device=DEV).sum().item() == 4.0     # the context still works
+
+
+def test_guard_bands_stay_intact_through_training_steps():
+    from kharon_b200.engine import TrainEngine
+    from kharon_b200.models import gpt
+    from kharon_b200.utils.guards import GuardedAlloc
+    from kharon_b200.utils.rng import Rng
+    ga = GuardedAlloc()
+    gpt.set_allocator(ga)
+    try:
+        e = TrainEngine(layers=2, d_model=128, heads=2, vocab=1000, seq=96, mbatch=3, n_micro=2, device="cuda")
+    finally:
+        gpt.set_allocator(None)
+    idx, tgt = Rng(4).batch(e.tokens_per_step, 1000)
+    for _ in range(3):
+        e.train_step(idx, tgt)
+    torch.cuda.synchronize()
+    assert len(ga.bufs) > 40 and ga.check() == []
+    ga.bufs[0][1][3] = 0          # a damaged band is reported
+    assert ga.check() == [ga.bufs[0][0]]
+
+
+def test_merge_attention_equals_attention_over_all_keys():
+    torch.manual_seed(11)
+    H, T, hd = 2, 64, 64
+    q, k, v = (torch.randn(H, T, hd, device=DEV) for _ in range(3))
+    def attn(kk, vv):
+        s = (q @ kk.transpose(-1, -2)) / hd ** 0.5
+        return torch.softmax(s, -1) @ vv, torch.logsumexp(s, -1)
+    o_all, l_all = attn(k, v)
+    o1, l1 = attn(k[:, :40], v[:, :40])
+    o2, l2 = attn(k[:, 40:], v[:, 40:])
+    o, l = ops.merge_attention(o1, l1, o2, l2)
+    assert torch.allclose(o, o_all, atol=1e-5) and torch.allclose(l, l_all, atol=1e-5)
