@@ -274,7 +274,7 @@ def test_guard_bands_stay_intact_through_training_steps():
     for _ in range(3):
         e.train_step(idx, tgt)
     torch.cuda.synchronize()
-    assert len(ga.bufs) > 40 and ga.check() == []
+    assert len(ga.bufs) > 20 and ga.check() == []
     ga.bufs[0][1][3] = 0          # a damaged band is reported
     assert ga.check() == [ga.bufs[0][0]]
 
