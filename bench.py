@@ -109,7 +109,7 @@ def run_ours():
     fused_comm = "--no-fused-comm" not in sys.argv     # in-kernel NVLink collectives (product path) vs NCCL baseline
     mesh = Mesh(tp, pp, dp) if world > 1 else Mesh.single()
     eng = TrainEngine(L, d, H, V, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
-                      init=arg("init", "device", str), fused_comm=fused_comm)
+                      init=arg("init", "device", str), fused_comm=fused_comm, pp_split=arg("pp-split", "auto", str))
     ntok = M * mb * S                                    # per replica and step
     data = Rng(42 + mesh.c.dp_rank)
     pin = device.type == "cuda"
@@ -195,6 +195,7 @@ def run_ours():
             "config": {"model": "GPT L%d d%d H%d V%d tied" % (L, d, H, V), "global_batch": mb * M * dp, "seq_len": S,
                        "micro_batch": mb, "micro_batches": M, "parallelism": "tp%d pp%d dp%d(zero1)" % (tp, pp, dp),
                        "microbatches_fused_on_single_stage": bool(eng.fused_mb), "fused_comm": fused_comm,
+                       "layers_per_stage": eng.stage_layers,
                        "l2": "inputs larger than L2 (step working set > 20 GB)", "loss_last_step": round(final_loss, 4)},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "ms_per_step": round(ms_e2e / K, 3),

@@ -49,18 +49,43 @@ def pp_num_slots(stage: int, n_stages: int, n_micro: int) -> int:
     return int(_native.rt().kh_pp_num_slots(stage, n_stages, n_micro))
 
 
+def stage_split(layers: int, pp: int, d_model: int, vocab: int, spec=None):
+    """Layers per pipeline stage.  ``spec``: None/"even" (the reference's L/P, src/pp_train.c:73-76), a
+    list or "a,b,..." string, or "auto": the last stage also runs the head GEMMs and the loss, whose
+    cost in units of one transformer layer is about 3*V*d / (3*12*d^2) = V / (12 d); "auto" moves that
+    many layers (rounded down) from the last stage to the earlier ones so that 1F1B stages take equal time."""
+    if pp == 1:
+        return [layers]
+    if spec is None or spec == "even":
+        if layers % pp:
+            raise ValueError("layers (%d) must divide evenly over %d pipeline stages" % (layers, pp))
+        return [layers // pp] * pp
+    if isinstance(spec, str) and spec != "auto":
+        spec = [int(x) for x in spec.split(",")]
+    if spec == "auto":
+        head = vocab / (12.0 * d_model)                     # head + loss cost in layer units
+        per = (layers + head) / pp
+        last = max(1, int(round(per - head)))
+        rest = layers - last
+        base, extra = divmod(rest, pp - 1)
+        spec = [base + (1 if i < extra else 0) for i in range(pp - 1)] + [last]
+    spec = list(spec)
+    if len(spec) != pp or sum(spec) != layers or min(spec) < 1:
+        raise ValueError("pipeline split %s does not cover %d layers on %d stages" % (spec, layers, pp))
+    return spec
+
+
 class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
-                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None):
+                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
         self.tracer = Tracer(enabled=bool(trace))     # per-phase CUDA-event timeline (forward / backward / p2p / optimizer)
         self.heartbeat = heartbeat                     # utils.watchdog.Heartbeat: peers are checked before every step
         c = self.mesh.c
         self.device = torch.device(device)
-        if layers % c.pp:
-            raise ValueError("layers (%d) must divide evenly over %d pipeline stages" % (layers, c.pp))
+        self.stage_layers = stage_split(layers, c.pp, d_model, vocab, pp_split)
         self.total_layers = layers
         self.n_micro = n_micro
         self.fused_mb = bool(fuse_microbatches and c.pp == 1)
@@ -68,7 +93,8 @@ class TrainEngine:
             mbatch, n_micro = mbatch * n_micro, 1
         self.M, self.mbatch, self.seq = n_micro, mbatch, seq
         self.opt = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=wd)
-        nl = layers // c.pp
+        nl = self.stage_layers[c.stage]
+        layer0 = sum(self.stage_layers[:c.stage])
         self.cfg = Config(nl, d_model, heads, vocab, seq, mbatch)
         self.n_slots = pp_num_slots(c.stage, c.pp, n_micro)
         self.zero_fused = None
@@ -81,7 +107,7 @@ class TrainEngine:
         if init == "device":
             self.model.init_weights_device(seed)
         else:
-            self.model.init_weights(seed, layer0=c.stage * nl, total_layers=layers)
+            self.model.init_weights(seed, layer0=layer0, total_layers=layers)
         self.schedule = pp_schedule(c.stage, c.pp, n_micro)
         R = mbatch * seq
         dev = self.device

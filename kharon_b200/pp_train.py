@@ -69,6 +69,7 @@ def main(argv=None):
     trace = f.has("trace", "print a per-phase device-time table (CUDA events) at the end")
     jsonl = f.str("jsonl", "", "append one JSON object per logged step to this file")
     hb_s = f.float("heartbeat", 0.0, "seconds after which a silent rank counts as dead (0 = off)")
+    pp_split = f.str("pp-split", "even", "layers per stage: even | auto | a,b,... (auto balances the head's cost)")
     f.maybe_help()
     rank, world, device = init_distributed(dev_flag or None)
     mesh = Mesh(tp, None, dp) if world > 1 else Mesh.single()
@@ -81,7 +82,7 @@ def main(argv=None):
     mlog = JsonlLogger(jsonl if rank == world - 1 else "")
     eng = TrainEngine(L, d, H, vocab, seq, mb, M, mesh=mesh, device=device,
                       dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, untied_head=untied,
-                      fused_comm=fused, trace=trace, heartbeat=hb)
+                      fused_comm=fused, trace=trace, heartbeat=hb, pp_split=pp_split)
     if synthetic or not os.path.exists(data_path):
         data = SyntheticData(vocab, M * mb, seq, 42)
     else:

@@ -57,7 +57,7 @@ def _worker(rank, world, port, tp, pp, dp, steps, out_dir, mode):
     from kharon_b200.engine import TrainEngine
     from kharon_b200.parallel.mesh import Mesh
     mesh = Mesh(tp, pp, dp, timeout_s=60)
-    e = TrainEngine(mesh=mesh, **KW)
+    e = TrainEngine(mesh=mesh, pp_split="3,1" if mode == "uneven" else None, **KW)
     data = _batches(mesh.c.dp_rank, steps, e.tokens_per_step, KW["vocab"])
     losses = []
     prefix = os.path.join(out_dir, "ck")
@@ -124,6 +124,16 @@ def test_mesh_matches_single_process(tp, pp, dp):
             assert torch.allclose(_view(r, "wte"), P["wte"], rtol=1e-4, atol=2e-5)
         if stage == pp - 1 and pp > 1:      # tied copy on the last stage stays equal to the embedding
             assert torch.allclose(_view(r, "head_w"), P["wte"], rtol=1e-4, atol=2e-5)
+
+
+def test_uneven_pipeline_split_matches_single_process():
+    """3 + 1 layers on two stages (the head-balancing split) trains exactly like one process."""
+    steps = 3
+    _, ref_losses = _single(steps, 1)
+    with tempfile.TemporaryDirectory() as d:
+        res = _launch(1, 2, 1, steps, d, "uneven")
+    last = [r for r in res if r["coord"][1] == 1][0]
+    assert max(abs(a - b) for a, b in zip(last["losses"], ref_losses)) < 2e-5
 
 
 def test_per_rank_checkpoint_resume_is_bit_exact():
