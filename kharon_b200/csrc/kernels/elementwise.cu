@@ -515,6 +515,91 @@ extern "C" int kh_xent(void* logits, int ld, int V, const void* target, const vo
   return 0;
 }
 
+// ---- vocabulary-parallel cross-entropy (the head's vocabulary is split over tensor-parallel ranks)
+// Stage 1, per rank: stats[r] = (max, sum exp(x - max), target logit or -inf) over this rank's
+// columns [v0, v0 + V) of the vocabulary.  The ranks' triples are combined outside (tiny), then
+// stage 2 overwrites the local logits with scale_r * (exp(x - gmax) / gsum - onehot).
+__global__ void xent_stats_k(const bf16* __restrict__ logits, int ld, int V, const int* __restrict__ target, int v0,
+                             float* __restrict__ stats) {
+  __shared__ float s_m[32], s_s[32];
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  const bf16* row = logits + (size_t)r * ld;
+  const uint4* rp = reinterpret_cast<const uint4*>(row);
+  float m = -INFINITY, s = 0.f;
+  const int nv = V / 8;
+  for (int i = tid; i < nv; i += blockDim.x) {
+    uint4 v = rp[i];
+    float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), e = unpack_bf16(v.w);
+    float mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)), fmaxf(fmaxf(c.x, c.y), fmaxf(e.x, e.y)));
+    if (mx > m) { s *= __expf(m - mx); m = mx; }
+    s += __expf(a.x - m) + __expf(a.y - m) + __expf(b.x - m) + __expf(b.y - m) + __expf(c.x - m) + __expf(c.y - m) +
+         __expf(e.x - m) + __expf(e.y - m);
+  }
+  for (int i = nv * 8 + tid; i < V; i += blockDim.x) {
+    float x = __bfloat162float(row[i]);
+    if (x > m) { s *= __expf(m - x); m = x; }
+    s += __expf(x - m);
+  }
+  float wm = warp_max(m);
+  s *= (m == -INFINITY) ? 0.f : __expf(m - wm);
+  s = warp_sum(s);
+  if (lane == 0) { s_m[warp] = wm; s_s[warp] = s; }
+  __syncthreads();
+  if (warp == 0) {
+    float mm = lane < nw ? s_m[lane] : -INFINITY;
+    float ss = lane < nw ? s_s[lane] : 0.f;
+    float gm = warp_max(mm);
+    ss *= (mm == -INFINITY) ? 0.f : __expf(mm - gm);
+    ss = warp_sum(ss);
+    if (lane == 0) {
+      const int t = target[r] - v0;
+      stats[3 * r] = gm;
+      stats[3 * r + 1] = ss;
+      stats[3 * r + 2] = (t >= 0 && t < V) ? __bfloat162float(row[t]) : -INFINITY;
+    }
+  }
+}
+__global__ void xent_grad_k(bf16* __restrict__ logits, int ld, int V, const int* __restrict__ target, int v0,
+                            const float* __restrict__ gmax, const float* __restrict__ gsum,
+                            const float* __restrict__ coef, float uniform) {
+  const int r = blockIdx.x, tid = threadIdx.x;
+  bf16* row = logits + (size_t)r * ld;
+  const int tg = target[r];
+  const int t = tg - v0;                       // local index of the target (may be outside this shard)
+  const float sc = tg >= 0 ? (coef ? coef[r] : uniform) : 0.f;
+  const float mx = gmax[r], inv = sc / gsum[r];
+  uint4* wp = reinterpret_cast<uint4*>(row);
+  const int nvl = (V + 7) / 8;                 // columns beyond the slice (up to the next multiple of 8) become 0
+  for (int i = tid; i < nvl; i += blockDim.x) {
+    uint4 v = wp[i], o;
+    const uint32_t* vi = &v.x; uint32_t* oi = &o.x;
+    const int c0 = i * 8;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      float2 xv = unpack_bf16(vi[k]);
+      const int c = c0 + 2 * k;
+      float g0 = c < V ? __expf(xv.x - mx) * inv - (c == t ? sc : 0.f) : 0.f;
+      float g1 = c + 1 < V ? __expf(xv.y - mx) * inv - (c + 1 == t ? sc : 0.f) : 0.f;
+      oi[k] = pack_bf16(g0, g1);
+    }
+    wp[i] = o;
+  }
+}
+extern "C" int kh_xent_stats(const void* logits, int ld, int V, const void* target, int v0, void* stats, int rows, void* stream) {
+  if (ld % 8 || ld < V) { kh_set_error("xent_stats: ld=%d must be a multiple of 8 and >= V=%d", ld, V); return -1; }
+  xent_stats_k<<<rows, 512, 0, (cudaStream_t)stream>>>((const bf16*)logits, ld, V, (const int*)target, v0, (float*)stats);
+  KH_LAUNCH_CHECK("xent_stats");
+  return 0;
+}
+extern "C" int kh_xent_grad(void* logits, int ld, int V, const void* target, int v0, const void* gmax, const void* gsum,
+                            const void* coef, float uniform, int rows, void* stream) {
+  if (ld % 8 || ld < V) { kh_set_error("xent_grad: ld=%d must be a multiple of 8 and >= V=%d", ld, V); return -1; }
+  xent_grad_k<<<rows, 512, 0, (cudaStream_t)stream>>>((bf16*)logits, ld, V, (const int*)target, v0, (const float*)gmax,
+                                                       (const float*)gsum, (const float*)coef, uniform);
+  KH_LAUNCH_CHECK("xent_grad");
+  return 0;
+}
+
 // out[0] (+)= scale * sum_i x[i], single CTA, fixed-order tree (loss reduction on the device)
 __global__ void sum_f32_k(const float* __restrict__ x, long n, float scale, float* __restrict__ out, int accumulate) {
   __shared__ float s[1024];

@@ -78,14 +78,14 @@ def stage_split(layers: int, pp: int, d_model: int, vocab: int, spec=None):
 class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
-                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None):
+                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None, vocab_parallel=True):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
         self.tracer = Tracer(enabled=bool(trace))     # per-phase CUDA-event timeline (forward / backward / p2p / optimizer)
         self.heartbeat = heartbeat                     # utils.watchdog.Heartbeat: peers are checked before every step
         c = self.mesh.c
         self.device = torch.device(device)
-        self.stage_layers = stage_split(layers, c.pp, d_model, vocab, pp_split)
+        self.stage_layers = stage_split(layers, c.pp, d_model, vocab // (c.tp if vocab_parallel else 1), pp_split)
         self.total_layers = layers
         self.n_micro = n_micro
         self.fused_mb = bool(fuse_microbatches and c.pp == 1)
@@ -124,6 +124,9 @@ class TrainEngine:
             if fused_comm and self.device.type == "cuda":
                 from .parallel import fused as fused_mod
                 self.fused = fused_mod.install(self.model, self.mesh)
+            if c.last and vocab_parallel:
+                from .parallel.mesh import rank_of
+                self.model.enable_vocab_parallel(grp, [rank_of(c.dp_rank, c.stage, t, c.tp, c.pp) for t in range(c.tp)])
         # ---- ZeRO-1
         ps = self.model.params
         self.zero = c.dp > 1
@@ -254,6 +257,7 @@ class TrainEngine:
                     self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank),
                                dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
         with tr.range("optimizer"):
+            m.sync_head_grad()
             self._tie_embedding_grads()
             self.optimizer_step()
         return m.loss_acc

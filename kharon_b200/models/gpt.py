@@ -76,6 +76,10 @@ class _Slot:
             self.logits = torch.zeros(R, Vp, dtype=dt, device=dev)
             self.rowloss = f(R)
             self.prob = f(R)
+            if tp > 1:      # vocabulary-parallel head: per-rank softmax statistics and their combination
+                self.stats = f(R, 3)
+                self.stats_all = f(tp, R, 3)
+                self.gmax, self.gsum = f(R), f(R)
 
 
 class GPT:
@@ -115,6 +119,9 @@ class GPT:
         self.skip_loss = False
         # fused tensor-parallel operators (installed by parallel.tp when available)
         self.fused_tp = None
+        # vocabulary-parallel head (enable_vocab_parallel): this rank's rows [v0, v1) of the head matrix
+        self.vp_group = None
+        self.v0, self.v1 = 0, cfg.vocab
 
     # ------------------------------------------------------------------ parameters
     def L(self, l, name):
@@ -258,10 +265,46 @@ class GPT:
     def head_grad(self):
         return self.params.grad["head_w"] if self.has_head else self.params.grad["wte"]
 
+    def enable_vocab_parallel(self, group, src_ranks):
+        """Split the head over the TP group by vocabulary rows: every rank computes the logits, the
+        softmax gradient and the head's weight gradient only for its own slice [v0, v1); the softmax
+        statistics are combined across ranks and the input gradient is summed like any other
+        row-parallel product.  ``src_ranks[r]`` is the global rank of TP rank r (for the per-step
+        exchange of head-gradient blocks, ``sync_head_grad``).  The reference replicates the head on
+        every TP rank (src/core/gpt.c:16)."""
+        assert self.last and self.tp > 1
+        vs = (self.cfg.vocab + self.tp - 1) // self.tp
+        self.v0 = min(self.cfg.vocab, self.tp_rank * vs)
+        self.v1 = min(self.cfg.vocab, self.v0 + vs)
+        self.vp_group, self.vp_src, self.vp_block = group, list(src_ranks), vs
+
+    def _vp_combine(self, s):
+        import torch.distributed as dist
+        dist.all_gather([s.stats_all[r] for r in range(self.tp)], s.stats, group=self.vp_group)
+        m, sm, xt = s.stats_all[..., 0], s.stats_all[..., 1], s.stats_all[..., 2]
+        gm = m.max(0).values
+        gs = (sm * torch.exp(m - gm)).sum(0)
+        s.gmax.copy_(gm)
+        s.gsum.copy_(gs)
+        s.rowloss.copy_(torch.where(s.tgt >= 0, torch.log(gs) + gm - xt.max(0).values, torch.zeros_like(gm)))
+
+    def sync_head_grad(self):
+        """Vocabulary-parallel head: every TP rank holds the head gradient of its own row block only;
+        exchange the blocks so that the replicated matrix receives the same full gradient everywhere."""
+        if self.vp_group is None:
+            return
+        import torch.distributed as dist
+        g = self.head_grad()
+        for r in range(self.tp):
+            lo = min(self.cfg.vocab, r * self.vp_block)
+            hi = min(self.cfg.vocab, lo + self.vp_block)
+            if hi > lo:
+                dist.broadcast(g[lo:hi], src=self.vp_src[r], group=self.vp_group)
+
     def forward_head(self, s: _Slot):
         cfg = self.cfg
         ops.layernorm_fwd(s.x[cfg.n_layer], self.params.c["lnf_w"], self.params.c["lnf_b"], s.lnf, s.meanf, s.rstdf)
-        ops.gemm(s.lnf, self.head_weight(), s.logits[:, :cfg.vocab])
+        ops.gemm(s.lnf, self.head_weight()[self.v0:self.v1], s.logits[:, :self.v1 - self.v0])
 
     def forward(self, slot=0, x_in=None, loss_scale=1.0, accumulate_loss=False, compute_loss=True):
         """Forward of one micro-batch.  First stage embeds ``tok``; other stages take ``x_in``
@@ -279,6 +322,7 @@ class GPT:
             return s.x[cfg.n_layer]
         self.forward_head(s)
         if compute_loss and not self.skip_loss:
+            assert self.vp_group is None, "with a vocabulary-parallel head the loss comes out of backward()"
             R = cfg.batch * cfg.seq
             ops.xent(s.logits, cfg.vocab, s.tgt, rowloss=s.rowloss, write_grad=False)
             ops.sum_f32(s.rowloss, self.loss_acc, scale=loss_scale / R, accumulate=accumulate_loss)
@@ -304,13 +348,22 @@ class GPT:
         dx, other = self.s_dx
         if self.last:
             want_loss = loss_scale is not None and not self.skip_loss
-            ops.xent(s.logits, V, s.tgt, coef=coef, uniform=inv_mb / R, write_grad=True,
-                     rowloss=s.rowloss if want_loss else None)
+            if self.vp_group is None:
+                ops.xent(s.logits, V, s.tgt, coef=coef, uniform=inv_mb / R, write_grad=True,
+                         rowloss=s.rowloss if want_loss else None)
+                dl = s.logits[:, :V]
+                ops.gemm(dl, self.head_weight(), self.s_dln, b_mn=True)
+                ops.gemm(dl, s.lnf, self.head_grad(), a_mn=True, b_mn=True, accumulate=True)
+            else:
+                v0, v1 = self.v0, self.v1
+                ops.xent_stats(s.logits, v1 - v0, s.tgt, v0, s.stats)
+                ops.plan_call(self._vp_combine, s)
+                ops.xent_grad(s.logits, v1 - v0, s.tgt, v0, s.gmax, s.gsum, coef=coef, uniform=inv_mb / R)
+                dl = s.logits[:, :v1 - v0]
+                self._row_parallel(dl, self.head_weight()[v0:v1], self.s_dln, b_mn=True)
+                ops.gemm(dl, s.lnf, self.head_grad()[v0:v1], a_mn=True, b_mn=True, accumulate=True)
             if want_loss:
                 ops.sum_f32(s.rowloss, self.loss_acc, scale=loss_scale / R, accumulate=accumulate_loss)
-            dl = s.logits[:, :V]
-            ops.gemm(dl, self.head_weight(), self.s_dln, b_mn=True)
-            ops.gemm(dl, s.lnf, self.head_grad(), a_mn=True, b_mn=True, accumulate=True)
             ops.layernorm_bwd(self.s_dln, s.x[cfg.n_layer], P["lnf_w"], s.meanf, s.rstdf, None, dx, Gd["lnf_w"],
                               Gd["lnf_b"], self.s_lnpart)
         else:

@@ -258,6 +258,24 @@ def xent(logits, V, target, *, coef=None, uniform=1.0, rowloss=None, prob=None, 
                         _p(rowloss), _p(prob), int(write_grad), logits.shape[0], _stream())
 
 
+def xent_stats(logits, V, target, v0, stats):
+    """Vocabulary-parallel cross-entropy, stage 1: per row (max, sum exp(x - max), target logit or -inf)
+    over this rank's vocabulary slice [v0, v0 + V); ``stats`` is fp32 [R, 3]."""
+    if not logits.is_cuda:
+        return ref.xent_stats(logits, V, target, v0, stats)
+    _call(_lib().kh_xent_stats, 1, logits.data_ptr(), logits.stride(0), V, target.data_ptr(), int(v0), stats.data_ptr(),
+          logits.shape[0], _stream())
+
+
+def xent_grad(logits, V, target, v0, gmax, gsum, *, coef=None, uniform=1.0):
+    """Stage 2: overwrite the local logits with ``scale_r * (exp(x - gmax) / gsum - onehot)`` given the
+    statistics combined over all vocabulary slices."""
+    if not logits.is_cuda:
+        return ref.xent_grad(logits, V, target, v0, gmax, gsum, coef, uniform)
+    _call(_lib().kh_xent_grad, 1, logits.data_ptr(), logits.stride(0), V, target.data_ptr(), int(v0), gmax.data_ptr(),
+          gsum.data_ptr(), _p(coef), float(uniform), logits.shape[0], _stream())
+
+
 def sum_f32(x, out, scale=1.0, accumulate=False):
     if not x.is_cuda:
         s = x.double().sum().float() * scale

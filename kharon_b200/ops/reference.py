@@ -118,6 +118,32 @@ def xent(logits, V, target, coef, uniform, rowloss, prob, write_grad):
         logits[:, :V] = ((p - onehot) * sc[:, None]).to(logits.dtype)
 
 
+def xent_stats(logits, V, target, v0, stats):
+    lg = logits[:, :V].float()
+    m = lg.max(-1).values
+    s = torch.exp(lg - m[:, None]).sum(-1)
+    t = target.long() - v0
+    inside = (t >= 0) & (t < V)
+    xt = lg.gather(1, t.clamp(0, V - 1)[:, None]).squeeze(1)
+    stats[:, 0] = m
+    stats[:, 1] = s
+    stats[:, 2] = torch.where(inside, xt, torch.full_like(xt, float("-inf")))
+
+
+def xent_grad(logits, V, target, v0, gmax, gsum, coef, uniform):
+    R = logits.shape[0]
+    lg = logits[:, :V].float()
+    tg = target.long()
+    sc = coef.float() if coef is not None else torch.full((R,), float(uniform), device=logits.device)
+    sc = torch.where(tg >= 0, sc, torch.zeros_like(sc))
+    p = torch.exp(lg - gmax.float()[:, None]) / gsum.float()[:, None]
+    t = tg - v0
+    inside = (t >= 0) & (t < V)
+    onehot = F.one_hot(t.clamp(0, V - 1), V).float() * inside[:, None].float()
+    logits.zero_()
+    logits[:, :V] = ((p - onehot) * sc[:, None]).to(logits.dtype)
+
+
 def adamw(p, g, m, v, pb, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, zero_grad):
     gk = g * grad_scale
     m.mul_(b1).add_(gk, alpha=1.0 - b1)

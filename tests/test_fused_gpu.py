@@ -97,6 +97,19 @@ def _worker(rank, world, port, out_dir):
             ls.append(e.loss())
         losses[fused] = ls
     res["losses"] = losses
+    # vocabulary-parallel head (the default) against the replicated head, odd vocabulary
+    kv = dict(kw, vocab=509)
+    vp = {}
+    for split in (False, True):
+        e = TrainEngine(fused_comm=True, vocab_parallel=split, **kv)
+        idx, tgt = Rng(6).batch(e.tokens_per_step, 509)
+        ls = []
+        for _ in range(5):
+            e.train_step(idx, tgt)
+            ls.append(e.loss())
+        vp[split] = (ls, e.model.params.w.clone().cpu())
+    res["vp_losses"] = {k: v[0] for k, v in vp.items()}
+    res["vp_werr"] = ((vp[True][1] - vp[False][1]).norm() / vp[False][1].norm()).item()
     # ZeRO-1: fused reduce-scatter + AdamW + bf16 all-gather kernel vs the NCCL path, DP = world
     mesh_dp = Mesh(1, 1, world, timeout_s=120)
     kw["mesh"] = mesh_dp
@@ -132,6 +145,9 @@ def test_fused_tp_kernels_two_gpus():
         a, b = r["losses"][False], r["losses"][True]
         assert max(abs(x - y) for x, y in zip(a, b)) < 3e-2, (a, b)
         assert b[-1] < b[0]
+        va, vb = r["vp_losses"][False], r["vp_losses"][True]
+        assert max(abs(x - y) for x, y in zip(va, vb)) < 2e-2, (va, vb)
+        assert r["vp_werr"] < 2e-3, r["vp_werr"]
         za, zb = r["zero_losses"][False], r["zero_losses"][True]
         assert max(abs(x - y) for x, y in zip(za, zb)) < 2e-2, (za, zb)
         assert r["zero_werr"] < 1e-3, r["zero_werr"]

@@ -127,6 +127,46 @@ def test_layernorm_fwd_bwd():
         assert relerr(dx, dx2) < 5e-3 and relerr(dw, dw2) < 1e-3 and relerr(db, db2) < 1e-3
 
 
+def test_xent_vocab_slices_combine_to_full_softmax():
+    """Per-slice statistics + combined gradient equal the full-row cross-entropy."""
+    torch.manual_seed(6)
+    R, V, parts = 96, 1003, 2
+    vs = (V + parts - 1) // parts
+    ld = (vs + 63) // 64 * 64
+    full = _rand(R, V, scale=2.0)
+    tgt = torch.randint(0, V, (R,), device=DEV, dtype=torch.int32)
+    tgt[5] = -1
+    stats, bufs = [], []
+    for r in range(parts):
+        v0, v1 = r * vs, min(V, (r + 1) * vs)
+        lg = torch.full((R, ld), 77.0, device=DEV, dtype=torch.bfloat16)
+        lg[:, :v1 - v0] = full[:, v0:v1]
+        st = torch.empty(R, 3, device=DEV); st2 = torch.empty(R, 3, device=DEV)
+        ops.xent_stats(lg, v1 - v0, tgt, v0, st)
+        ref.xent_stats(lg, v1 - v0, tgt, v0, st2)
+        assert torch.equal(torch.isinf(st[:, 2]), torch.isinf(st2[:, 2]))
+        fin = ~torch.isinf(st2[:, 2])
+        assert relerr(st[:, :2], st2[:, :2]) < 1e-3 and relerr(st[fin, 2], st2[fin, 2]) < 1e-6
+        stats.append(st); bufs.append((lg, v0, v1))
+    sa = torch.stack(stats)
+    gm = sa[..., 0].max(0).values
+    gs = (sa[..., 1] * torch.exp(sa[..., 0] - gm)).sum(0)
+    loss = torch.where(tgt >= 0, torch.log(gs) + gm - sa[..., 2].max(0).values, torch.zeros_like(gm))
+    want = full.clone().float()
+    lp = torch.log_softmax(want, -1)
+    want_loss = torch.where(tgt >= 0, -lp.gather(1, tgt.clamp(min=0).long()[:, None]).squeeze(1), torch.zeros(R, device=DEV))
+    assert relerr(loss, want_loss) < 1e-3
+    grad = torch.softmax(want, -1)
+    grad[torch.arange(R, device=DEV), tgt.clamp(min=0).long()] -= 1.0
+    grad[tgt < 0] = 0
+    grad *= 0.25
+    for lg, v0, v1 in bufs:
+        ops.xent_grad(lg, v1 - v0, tgt, v0, gm, gs, uniform=0.25)
+        assert relerr(lg[:, :v1 - v0], grad[:, v0:v1]) < 1e-2
+        pad8 = (v1 - v0 + 7) // 8 * 8
+        assert lg[:, v1 - v0:pad8].abs().max().item() == 0 if pad8 > v1 - v0 else True
+
+
 def test_xent():
     torch.manual_seed(5)
     for R, V, ld in [(64, 256, 256), (130, 50257, 50304), (32, 1000, 1008)]:
