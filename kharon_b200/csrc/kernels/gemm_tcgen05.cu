@@ -304,10 +304,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       tile_coord(t, tm, tn);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
-      tc_fence_after();
       const int row = tm * TM + (int)crank * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
+      const bool use_bias = (p.epi == EPI_BIAS || p.epi == EPI_BIAS_GELU || p.epi == EPI_BIAS_RESID);
+      const bool use_aux = (p.epi == EPI_BIAS_RESID || p.epi == EPI_RESID || p.epi == EPI_DGELU);
+      // Operands of the epilogue are fetched one 32-column chunk ahead (the first chunk before the
+      // accumulator is even complete), so their DRAM latency is not paid once per chunk.
+      uint4 nb[4], nx[4];
+      auto fetch = [&](int c0) {
+        const int col = tn * BN + c0;
+        if (c0 >= BN || col + 32 > p.N) return;
+        if (use_bias) {
+          const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col);
+#pragma unroll
+          for (int j = 0; j < 4; j++) nb[j] = __ldg(bp + j);
+        }
+        if (use_aux && row_ok) {
+          const uint4* ap = reinterpret_cast<const uint4*>(p.aux + (size_t)row * p.ldaux + col);
+#pragma unroll
+          for (int j = 0; j < 4; j++) nx[j] = ap[j];
+        }
+      };
+      if (use_aux && row_ok) {
+        const char* ap = reinterpret_cast<const char*>(p.aux + (size_t)row * p.ldaux + tn * BN);
+        const int nbytes = min(BN, p.N - tn * BN) * 2;
+        for (int b = 128; b < nbytes; b += 128) prefetch_l2(ap + b);
+      }
+      fetch(0);
+      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
+      tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -315,17 +340,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         if (col >= p.N) break;                 // uniform across the warp
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
+        uint4 cb[4], cx[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) { cb[j] = nb[j]; cx[j] = nx[j]; }
+        fetch(c0 + 32);
         tmem_ld_wait();
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]) * p.alpha;
         const bool full = (col + 32 <= p.N);
-        if (p.epi == EPI_BIAS || p.epi == EPI_BIAS_GELU || p.epi == EPI_BIAS_RESID) {
+        if (use_bias) {
           if (full) {
-            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-              uint4 b = __ldg(bp + j);
+              uint4 b = cb[j];
               float2 f0 = unpack_bf16(b.x), f1 = unpack_bf16(b.y), f2 = unpack_bf16(b.z), f3 = unpack_bf16(b.w);
               v[8 * j + 0] += f0.x; v[8 * j + 1] += f0.y; v[8 * j + 2] += f1.x; v[8 * j + 3] += f1.y;
               v[8 * j + 4] += f2.x; v[8 * j + 5] += f2.y; v[8 * j + 6] += f3.x; v[8 * j + 7] += f3.y;
@@ -353,13 +381,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             // backward pass (which only sees the bf16 copy) differentiates the same function
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
-          } else if (p.epi == EPI_BIAS_RESID || p.epi == EPI_RESID || p.epi == EPI_DGELU) {
+          } else if (use_aux) {
             const bf16* ap = p.aux + (size_t)row * p.ldaux + col;
             float x[32];
             if (full) {
 #pragma unroll
               for (int j = 0; j < 4; j++) {
-                uint4 b = reinterpret_cast<const uint4*>(ap)[j];
+                uint4 b = cx[j];
                 float2 f0 = unpack_bf16(b.x), f1 = unpack_bf16(b.y), f2 = unpack_bf16(b.z), f3 = unpack_bf16(b.w);
                 x[8 * j + 0] = f0.x; x[8 * j + 1] = f0.y; x[8 * j + 2] = f1.x; x[8 * j + 3] = f1.y;
                 x[8 * j + 4] = f2.x; x[8 * j + 5] = f2.y; x[8 * j + 6] = f3.x; x[8 * j + 7] = f3.y;
@@ -379,14 +407,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col;
             if (full) {
+              if (p.accumulate) {
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                if (p.accumulate) {
-                  float4 old = reinterpret_cast<float4*>(cp)[j];
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                reinterpret_cast<float4*>(cp)[j] = o;
+                for (int j = 0; j < 8; j++) red_add_v4_f32(cp + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                  reinterpret_cast<float4*>(cp)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
               }
             } else {
               for (int i = 0; i < 32; i++)
