@@ -25,7 +25,9 @@
 // rank -> all ranks hold bit-identical results, run to run.
 // Flow control: arrival counters only grow (4 per call and tile); staging is double-buffered
 // by call parity, which is sufficient because a rank cannot be two calls ahead of a peer it
-// needs partials from.  Every wait is bounded; on expiry the error word gets code 5 and all
+// needs partials from.  The call number lives in device memory (a word per buffer set that the
+// last CTA of a launch advances), so a launch takes the same arguments every time and can be
+// replayed from a CUDA graph or a recorded launch plan.  Every wait is bounded; on expiry the error word gets code 5 and all
 // roles of the CTA unwind.  No TMA load here uses cluster multicast; peer memory is only
 // touched by st.global / red (push) and, in gather mode, by non-multicast TMA loads.
 #include "../kernels/common.cuh"
@@ -55,16 +57,18 @@ struct CommParams {
   bf16* out; int ldo;          // AR: [M, N]; RS: [M/tp, N]
   const bf16* bias;            // [N] or null, added by the reducer
   const bf16* resid; int ldr;  // residual rows aligned with `out`, or null
-  bf16* stage[MAX_TP];         // stage[r]: rank r's staging base (tp slots of M*N), parity applied by host
+  bf16* stage[MAX_TP];         // stage[r]: rank r's staging base for parity 0 (tp slots of M*N); parity 1 follows
+  size_t slot_elems;           // tp * M * N
+  uint32_t* epoch;             // local: [0] calls completed on this buffer set, [1] CTAs finished; null: host counts
   uint32_t* flags[MAX_TP];     // flags[r]: rank r's arrival counters [tp][num_tiles]
   uint32_t* ready[MAX_TP];     // gather mode: ready[r]: rank r's "shard published" counters [tp]
-  uint32_t target;             // counter value that means "this call's partial has arrived"
+  uint32_t call_no;            // 1-based call number when the host counts
   uint32_t ready_target;
   int* err;
 };
 
 // out: the local output; st[r]: slot `rank` of rank r's staging (where this rank's partial goes)
-struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap st[MAX_TP]; };
+struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap st[2][MAX_TP]; };
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -155,6 +159,12 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // this launch's call number: every CTA reads it before any CTA can have finished, and only the
+  // CTA that finishes last advances it
+  const uint32_t call = p.epoch ? *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1u : p.call_no;
+  const uint32_t target = 4u * call;           // counter value that means "this call's partial has arrived"
+  const int par = (int)(call & 1u);
+  const bf16* my_stage = p.stage[p.rank] + (size_t)par * p.slot_elems;
 
   // Tiles are visited M-band by M-band starting with this rank's own rows, so that in gather mode
   // local shards are consumed while the peers' shards are still being published.
@@ -306,7 +316,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
           if (mine) tma_store_2d(&maps.out, sbuf, col, out_row0);
           for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
             if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
-            tma_store_2d(&maps.st[pr], sbuf, col, tm * BM);
+            tma_store_2d(&maps.st[par][pr], sbuf, col, tm * BM);
           }
           tma_store_commit();
           if (chunk_no == 0 && pend_t >= 0) {
@@ -337,7 +347,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
         if (good && (owner < 0 || owner == p.rank)) {
           for (int pr = 0; pr < p.tp && good; pr++) {
             if (pr == p.rank) continue;
-            good = wait_counter(p.flags[p.rank] + (size_t)pr * num_tiles + t, p.target, abort_flag, p.err) ? 1 : 0;
+            good = wait_counter(p.flags[p.rank] + (size_t)pr * num_tiles + t, target, abort_flag, p.err) ? 1 : 0;
           }
         }
       }
@@ -372,7 +382,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
             const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
             const uint4* src = (r == p.rank)
                                    ? reinterpret_cast<const uint4*>(p.out + (size_t)out_row * p.ldo + col)
-                                   : reinterpret_cast<const uint4*>(p.stage[p.rank] + ((size_t)r * p.M + row) * p.N + col);
+                                   : reinterpret_cast<const uint4*>(my_stage + ((size_t)r * p.M + row) * p.N + col);
             v[i] = row < row_end ? __ldcg(src) : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
@@ -414,6 +424,14 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if (p.epoch && threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.epoch + 1, 1u) == gridDim.x - 1) {
+      p.epoch[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.epoch) = call;
+    }
+  }
 }
 
 int g_sms = 0;
@@ -433,13 +451,16 @@ int num_sms() {
 // to the per-rank row shards [M/tp, K] (or [K, M/tp] when a_mn) mapped into this process.
 // `stage_ptrs`, `flag_ptrs`, `ready_ptrs`: tp entries each, index r = rank r's buffer as seen from
 // this process (own entry = local buffer).  Staging holds tp slots of M*N bf16; flags hold
-// tp * ceil(M/128) * ceil(N/256) counters; ready holds tp counters.  `call_no` is this buffer set's
-// 1-based call count (identical on all ranks).  Returns 0 or -1.
+// tp * ceil(M/128) * ceil(N/256) counters; ready holds tp counters.  Staging is two parities of
+// tp * M * N bf16 each; `stage_ptrs` are the parity-0 bases.  The call count of the buffer set
+// (identical on all ranks) is either kept by the kernel in the two zero-initialised words at
+// `epoch_ptr` (local device memory) or, when that is 0, passed as the 1-based `call_no`.
+// Returns 0 or -1.
 extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn, const void* B, int ldb, int b_mn,
                             void* out, int ldo, int M, int N, int K, int mode, int gather, int tp, int rank,
                             const unsigned long long* stage_ptrs, const unsigned long long* flag_ptrs,
                             const unsigned long long* ready_ptrs, unsigned call_no, unsigned gather_no,
-                            const void* bias, const void* resid, int ldr, int max_ctas, void* stream) {
+                            unsigned long long epoch_ptr, const void* bias, const void* resid, int ldr, int max_ctas, void* stream) {
   if (tp < 2 || tp > MAX_TP || rank < 0 || rank >= tp) { kh_set_error("gemm_comm: bad tp/rank %d/%d", rank, tp); return -1; }
   if ((mode == MODE_RS || gather) && M % (tp * BM)) { kh_set_error("gemm_comm: M=%d must be a multiple of tp*128 for row-sharded modes", M); return -1; }
   if (M < 1) { kh_set_error("gemm_comm: empty problem"); return -1; }
@@ -459,12 +480,14 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   const CUtensorMap* to = kh_tmap_2d_bf16(out, out_rows, N, ldo, BM, 64);
   if (!to) return -1;
   maps.out = *to;
-  for (int r = 0; r < tp; r++) {
-    if (r == rank || mode == MODE_LOCAL) continue;
-    const CUtensorMap* ts = kh_tmap_2d_bf16((const bf16*)stage_ptrs[r] + (size_t)rank * M * N, M, N, N, BM, 64);
-    if (!ts) return -1;
-    maps.st[r] = *ts;
-  }
+  const size_t slot_elems = (size_t)tp * M * N;
+  for (int par = 0; par < 2; par++)
+    for (int r = 0; r < tp; r++) {
+      if (r == rank || mode == MODE_LOCAL) continue;
+      const CUtensorMap* ts = kh_tmap_2d_bf16((const bf16*)stage_ptrs[r] + par * slot_elems + (size_t)rank * M * N, M, N, N, BM, 64);
+      if (!ts) return -1;
+      maps.st[par][r] = *ts;
+    }
   CommParams p = {};
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.tp = tp; p.rank = rank; p.gather = gather;
   p.out = (bf16*)out; p.ldo = ldo; p.bias = (const bf16*)bias; p.resid = (const bf16*)resid; p.ldr = ldr;
@@ -473,7 +496,9 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
     p.flags[r] = (uint32_t*)flag_ptrs[r];
     p.ready[r] = ready_ptrs ? (uint32_t*)ready_ptrs[r] : nullptr;
   }
-  p.target = 4u * call_no;
+  p.call_no = call_no;
+  p.slot_elems = slot_elems;
+  p.epoch = (uint32_t*)epoch_ptr;
   p.ready_target = gather_no;
   p.err = kh_error_word_dev();
   static bool attr = false;

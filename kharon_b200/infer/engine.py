@@ -84,7 +84,10 @@ class InferEngine:
             n = max(ops.gemm_skinny_scratch_elems(ops.SKINNY_MAX_ROWS, N, K) for N, K in shapes)
             self.skinny = torch.zeros(n, dtype=torch.float32, **z)
         self.temperature, self.seed, self.step_no = 0.0, 0, 0
-        self.use_graphs = bool(use_graphs and self.dev.type == "cuda" and self.tp == 1)
+        # under TP the captured step contains the fused GEMM + all-reduce kernels (their call counter
+        # is a device word); the NCCL seam is left to eager launches
+        self.use_graphs = bool(use_graphs and self.dev.type == "cuda"
+                               and (self.tp == 1 or getattr(model, "fused_tp", None) is not None))
         self.graphs = {}
         self._warm = set()
         self.d_step = None

@@ -11,8 +11,10 @@
                that live in symmetric memory and are read tile by tile with TMA.
 
 Buffers come from ``torch.distributed._symmetric_memory`` (allocation and address exchange
-only); all data movement is issued from inside the kernel.  Call counters are kept on the host
-and are identical on all ranks because every rank issues the same sequence of calls.
+only); all data movement is issued from inside the kernel.  The call counter of a buffer set
+is a device word that the kernel advances itself (identical on all ranks because every rank
+issues the same sequence of calls), so a fused product is an ordinary native call: it can be
+recorded in a launch plan and captured in a CUDA graph.
 """
 from __future__ import annotations
 
@@ -48,14 +50,13 @@ class _Ctx:
         torch.cuda.synchronize(device)
         self.h.barrier()
         base = [int(p) for p in self.h.buffer_ptrs]
-        self.stage = [[b + par * self.slot_bytes for b in base] for par in (0, 1)]
         self.flags = [b + 2 * self.slot_bytes for b in base]
         self.ready = [b + 2 * self.slot_bytes + self.flag_bytes for b in base]
         U = C.c_uint64 * tp
-        self.c_stage = [U(*self.stage[0]), U(*self.stage[1])]
+        self.c_stage = U(*base)                  # parity-0 bases; parity 1 follows at slot_bytes
         self.c_flags = U(*self.flags)
         self.c_ready = U(*self.ready)
-        self.calls = 0
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)    # [calls completed, CTAs finished]
         self.gathers = 0
 
 
@@ -79,28 +80,18 @@ class FusedTP:
         t, h = _symm_alloc(rows * cols * 2, self.device, self.group)
         return t.view(dtype).view(rows, cols), [int(p) for p in h.buffer_ptrs], h
 
-    def _launch(self, a_ptrs, lda, a_mn, b, b_mn, out, M, N, K, mode, gather, bias, resid):
-        c = self._get(M, N, mode)
-        c.calls += 1
-        if gather:
-            c.gathers += 1
-        lib = _native.cuda()
-        rc = lib.kh_gemm_comm(a_ptrs, lda, int(a_mn), b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(),
-                              out.stride(0), M, N, K, mode, int(gather), self.tp, self.rank, c.c_stage[c.calls & 1],
-                              c.c_flags, c.c_ready, c.calls, c.gathers, ops._p(bias), ops._p(resid),
-                              resid.stride(0) if resid is not None else 0, self.max_ctas,
-                              torch.cuda.current_stream().cuda_stream)
-        ops._chk(rc)
-
     def _gemm(self, a, b, out, a_mn, b_mn, mode, bias, resid):
         if a_mn:
             K, M = a.shape
         else:
             M, K = a.shape
         N = b.shape[1] if b_mn else b.shape[0]
+        c = self._get(M, N, mode)
         ptr = (C.c_uint64 * 1)(a.data_ptr())
-        # a host callable, so that a recorded launch plan re-evaluates the call counter
-        ops.plan_call(self._launch, ptr, a.stride(0), a_mn, b, b_mn, out, M, N, K, mode, 0, bias, resid)
+        ops._call(_native.cuda().kh_gemm_comm, 1, ptr, a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+                  out.data_ptr(), out.stride(0), M, N, K, mode, 0, self.tp, self.rank, c.c_stage, c.c_flags,
+                  c.c_ready, 0, 0, c.epoch.data_ptr(), ops._p(bias), ops._p(resid),
+                  resid.stride(0) if resid is not None else 0, self.max_ctas, ops._stream())
         return out
 
     def gemm_ar(self, a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None):
@@ -124,14 +115,14 @@ class FusedTP:
     def _launch_ag(self, ptrs, lda, b, b_mn, out, M, N, K):
         # gather mode uses a context of its own: its "reduction" is local-only (tp slots unused)
         c = self._get(M, N, 2)
-        c.calls += 1
         c.gathers += 1
         lib = _native.cuda()
         rc = lib.kh_gemm_comm(ptrs, lda, 0, b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0),
-                              M, N, K, 2, 1, self.tp, self.rank, c.c_stage[c.calls & 1], c.c_flags, c.c_ready,
-                              c.calls, c.gathers, None, None, 0, self.max_ctas,
+                              M, N, K, 2, 1, self.tp, self.rank, c.c_stage, c.c_flags, c.c_ready,
+                              0, c.gathers, c.epoch.data_ptr(), None, None, 0, self.max_ctas,
                               torch.cuda.current_stream().cuda_stream)
         ops._chk(rc)
+        ops.launch_count += 1
 
 
 def install(model, mesh):

