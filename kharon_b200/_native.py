@@ -69,6 +69,7 @@ def rt():
         _sig(lib, "kh_grpo_coef", None, vp, vp, vp, i32, i32, i32, i32, f32, vp)
         _sig(lib, "kh_pp_schedule", i32, i32, i32, i32, vp, i32)
         _sig(lib, "kh_pp_num_slots", i32, i32, i32, i32)
+        _sig(lib, "kh_pp_schedule_deferred", i32, i32, i32, i32, i32, i32, vp, i32)
         _sig(lib, "kh_eng_create", vp, i32, i32, i32, i32)
         _sig(lib, "kh_eng_free", None, vp)
         _sig(lib, "kh_eng_reset", None, vp)

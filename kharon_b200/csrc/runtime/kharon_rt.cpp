@@ -335,6 +335,45 @@ extern "C" int kh_pp_schedule(int32_t s, int32_t P, int32_t M, int32_t* out, int
   return n;
 }
 
+// Schedule for stages whose sends never wait for the receiver (mailbox transport) and whose
+// weight gradients are deferred: every micro-batch owns an activation slot (a1 == a0), a stage
+// other than the last runs `extra` more forwards ahead than 1F1B would, and uses that slack to
+// form the weight gradients of the first half of the micro-batches in the middle of the step
+// (`mid` != 0) instead of all of them at its end.
+extern "C" int kh_pp_schedule_deferred(int32_t s, int32_t P, int32_t M, int32_t extra, int32_t mid, int32_t* out,
+                                       int32_t max_ops) {
+  if (P < 1 || s < 0 || s >= P || M < 1 || extra < 0) return fail(KH_E_ARG, "pp_schedule_deferred: bad stage %d/%d M=%d", s, P, M);
+  const bool first = s == 0, last = s == P - 1;
+  const int warm = std::min(M, P - 1 - s + (last ? 0 : extra));
+  const int flush_at = (!last && mid && M >= 4) ? M / 2 - 1 : -1;
+  int n = 0;
+  bool over = false;
+  auto emit = [&](int op, int a0, int a1) {
+    if (n >= max_ops) { over = true; return; }
+    out[3 * n] = op; out[3 * n + 1] = a0; out[3 * n + 2] = a1;
+    n++;
+  };
+  int ff = 0, bb = 0, flushed = 0;
+  auto fwd = [&]() {
+    if (!first) emit(KH_PP_RECV_ACT, ff, ff);
+    emit(KH_PP_FWD, ff, ff);
+    if (!last) emit(KH_PP_SEND_ACT, ff, ff);
+    ff++;
+  };
+  for (int i = 0; i < warm; i++) fwd();
+  while (bb < M) {
+    if (ff < M) fwd();
+    if (!last) emit(KH_PP_RECV_GRAD, bb, bb);
+    emit(KH_PP_BWD, bb, bb);
+    if (!first) emit(KH_PP_SEND_GRAD, bb, bb);
+    if (bb == flush_at) { emit(KH_PP_FLUSH_DW, flushed, bb + 1); flushed = bb + 1; }
+    bb++;
+  }
+  emit(KH_PP_FLUSH_DW, flushed, M);
+  if (over) return fail(KH_E_ARG, "pp_schedule_deferred: more than %d ops", max_ops);
+  return n;
+}
+
 // ------------------------------------------------------------------- paged-KV scheduler
 namespace {
 enum SeqState { S_FREE = 0, S_WAIT, S_RUN, S_HOLD, S_DONE };

@@ -92,12 +92,18 @@ enum {
   KH_PP_FWD = 4,        // forward of micro-batch a0 using activation slot a1
   KH_PP_BWD = 5,        // backward of micro-batch a0 using activation slot a1
   KH_PP_SEND_ACT_RECV_GRAD = 6,   // one fused exchange with the next stage
-  KH_PP_SEND_GRAD_RECV_ACT = 7    // one fused exchange with the previous stage
+  KH_PP_SEND_GRAD_RECV_ACT = 7,   // one fused exchange with the previous stage
+  KH_PP_FLUSH_DW = 8              // weight gradients of micro-batch slots [a0, a1) (deferred mode)
 };
 // Writes triples (op, a0, a1) into out[3 * max_ops]; returns the op count or negative error.
 int kh_pp_schedule(int32_t stage, int32_t n_stages, int32_t n_micro, int32_t* out,
                    int32_t max_ops);
 int kh_pp_num_slots(int32_t stage, int32_t n_stages, int32_t n_micro);
+// Schedule for non-blocking sends and deferred weight gradients (one slot per micro-batch):
+// `extra` additional warm-up forwards on every stage but the last, `mid` != 0 adds a weight-gradient
+// pass over the first half of the micro-batches in the middle of the step.
+int kh_pp_schedule_deferred(int32_t stage, int32_t n_stages, int32_t n_micro, int32_t extra, int32_t mid,
+                            int32_t* out, int32_t max_ops);
 
 // ---- paged-KV block pool and continuous-batching scheduler ------------------------------
 typedef struct KhEngine KhEngine;

@@ -34,7 +34,7 @@ from . import _native, ops
 from .models import GPT, Config
 from .parallel.mesh import Mesh
 
-PP_RECV_ACT, PP_SEND_ACT, PP_RECV_GRAD, PP_SEND_GRAD, PP_FWD, PP_BWD, PP_SEND_ACT_RECV_GRAD, PP_SEND_GRAD_RECV_ACT = range(8)
+PP_RECV_ACT, PP_SEND_ACT, PP_RECV_GRAD, PP_SEND_GRAD, PP_FWD, PP_BWD, PP_SEND_ACT_RECV_GRAD, PP_SEND_GRAD_RECV_ACT, PP_FLUSH_DW = range(9)
 
 
 def pp_schedule(stage: int, n_stages: int, n_micro: int):
@@ -42,6 +42,14 @@ def pp_schedule(stage: int, n_stages: int, n_micro: int):
     cap = 8 * (n_micro + n_stages) + 16
     buf = (C.c_int32 * (3 * cap))()
     n = _native.rt_check(_native.rt().kh_pp_schedule(stage, n_stages, n_micro, buf, cap))
+    return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
+
+
+def pp_schedule_deferred(stage: int, n_stages: int, n_micro: int, extra: int = 1, mid: bool = True):
+    """Op list for non-blocking sends with deferred weight gradients (see kh_pp_schedule_deferred)."""
+    cap = 8 * (n_micro + n_stages) + 16
+    buf = (C.c_int32 * (3 * cap))()
+    n = _native.rt_check(_native.rt().kh_pp_schedule_deferred(stage, n_stages, n_micro, extra, int(mid), buf, cap))
     return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
 
 
@@ -78,7 +86,8 @@ def stage_split(layers: int, pp: int, d_model: int, vocab: int, spec=None):
 class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
-                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None, vocab_parallel=True):
+                 fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None, vocab_parallel=True,
+                 defer_dw=None, eager_p2p=None):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
         self.tracer = Tracer(enabled=bool(trace))     # per-phase CUDA-event timeline (forward / backward / p2p / optimizer)
@@ -97,13 +106,19 @@ class TrainEngine:
         layer0 = sum(self.stage_layers[:c.stage])
         self.cfg = Config(nl, d_model, heads, vocab, seq, mbatch)
         self.n_slots = pp_num_slots(c.stage, c.pp, n_micro)
+        # Deferred weight gradients (default under pipeline parallelism): every micro-batch keeps its
+        # own activation slot, backward stores the layers' output gradients, and one pass after the
+        # schedule forms all weight/bias gradients over M x R rows.
+        self.defer_dw = bool(c.pp > 1 and n_micro > 1) if defer_dw is None else bool(defer_dw and not self.fused_mb)
+        if self.defer_dw:
+            self.n_slots = n_micro
         self.zero_fused = None
         if c.dp > 1 and fused_comm and self.device.type == "cuda":
             from .parallel.zero_fused import ZeroFused
             self.zero_fused = ZeroFused(self.mesh, self.device)
         self.model = GPT(self.cfg, self.device, dtype, tp=c.tp, tp_rank=c.tp_rank, first=c.first, last=c.last,
                          untied_head=untied_head, n_slots=self.n_slots, dp=c.dp,
-                         alloc=self.zero_fused.alloc if self.zero_fused else None)
+                         alloc=self.zero_fused.alloc if self.zero_fused else None, defer_dw=self.defer_dw)
         if init == "device":
             self.model.init_weights_device(seed)
         else:
@@ -111,6 +126,21 @@ class TrainEngine:
         self.schedule = pp_schedule(c.stage, c.pp, n_micro)
         R = mbatch * seq
         dev = self.device
+        # Message transport between stages.  With deferred weight gradients and a transport whose
+        # sends do not wait for the receiver (mailboxes in peer memory on GPUs, gloo isend on CPU
+        # ranks) the stage runs the deeper-warm-up schedule that hides half of the weight-gradient
+        # pass; blocking NCCL send/recv keeps the 1F1B order and appends one pass at the end.
+        self.box = None
+        if self.defer_dw and c.pp > 1 and eager_p2p is not False:
+            from .parallel import p2p
+            if self.device.type == "cuda" and fused_comm:
+                self.box = p2p.Mailbox(self.mesh, dev, n_micro, R, d_model, dtype)
+            elif dist.get_backend() == "gloo":
+                self.box = p2p.DistMailbox(self.mesh, dev, n_micro, R, d_model, dtype)
+        if self.box is not None:
+            self.schedule = pp_schedule_deferred(c.stage, c.pp, n_micro)
+        elif self.defer_dw:
+            self.schedule = self.schedule + [(PP_FLUSH_DW, 0, n_micro)]
         self.tok_dev = torch.zeros(n_micro * R, dtype=torch.int32, device=dev)
         self.tgt_dev = torch.zeros(n_micro * R, dtype=torch.int32, device=dev)
         if c.pp > 1:
@@ -223,7 +253,28 @@ class TrainEngine:
         out_act = {}
         in_grad = {}
         n_loss = 0
+        box = self.box
         for op, a0, a1 in self.schedule:
+            if self.defer_dw and op in (PP_FWD, PP_BWD):
+                a1 = a0                 # one slot per micro-batch
+            if op == PP_FLUSH_DW:
+                with tr.range("weight gradients"):
+                    self._compute(("W", a0, a1), lambda: m.flush_dw(a0, a1))
+                continue
+            if box is not None and op not in (PP_FWD, PP_BWD):
+                with tr.range("pipeline p2p"):
+                    if op == PP_RECV_ACT:
+                        self._compute(("RA", a0), lambda: box.wait_act(a0))
+                    elif op == PP_SEND_ACT:
+                        self._compute(("SA", a0), lambda: box.send_act(a0, out_act.pop(a0)))
+                    elif op == PP_RECV_GRAD:
+                        self._compute(("RG", a0), lambda: box.wait_grad(a0))
+                    elif op == PP_SEND_GRAD:
+                        self._compute(("SG", a0), lambda: box.send_grad(a0, in_grad.pop(a0)))
+                continue
+            if box is not None:
+                cur_act = None if c.first else box.act_in(a0)
+                cur_grad = None if c.last else box.grad_in(a0)
             if op == PP_FWD:
                 with tr.range("forward"):
                     out_act[a0] = self._compute(("F", a0, a1), lambda: (
@@ -256,6 +307,8 @@ class TrainEngine:
                     cur_act = self.recv_act[a1 & 1]
                     self._p2p([dist.P2POp(dist.isend, in_grad.pop(a0), c.prev_rank),
                                dist.P2POp(dist.irecv, cur_act, c.prev_rank)])
+        if box is not None:
+            box.finish()
         with tr.range("optimizer"):
             m.sync_head_grad()
             self._tie_embedding_grads()

@@ -55,20 +55,47 @@ def _buf(shape, dtype, dev):
     return torch.empty(*shape, dtype=dtype, device=dev)
 
 
+class _SlotGroup:
+    """Buffers that the deferred weight-gradient pass reads across ALL micro-batches of a step: per
+    layer the four GEMM inputs (ln1, att, ln2, act) and the four output gradients (d_out, d_pre,
+    d_mid, d_qkv), each one [n_slots * R, width] tensor of which slot i owns rows [i*R, (i+1)*R).
+    One product over n_slots * R rows then replaces n_slots products over R rows."""
+    WIDTHS = ("ln1", "att", "ln2", "act", "d_out", "d_pre", "d_mid", "d_qkv")
+
+    def __init__(self, cfg: Config, tp, dev, dt, n):
+        R, d = cfg.batch * cfg.seq, cfg.d_model
+        dl, fo = d // tp, 4 * d // tp
+        w = dict(ln1=d, att=dl, ln2=d, act=fo, d_out=d, d_pre=fo, d_mid=d, d_qkv=3 * dl)
+        self.n, self.R = n, R
+        self.layers = [{k: _buf((n * R, w[k]), dt, dev) for k in self.WIDTHS} for _ in range(cfg.n_layer)]
+
+    def view(self, l, name, i):
+        return self.layers[l][name][i * self.R:(i + 1) * self.R]
+
+    def rows(self, l, name, lo, hi):
+        return self.layers[l][name][lo * self.R:hi * self.R]
+
+
 class _Slot:
     """Activation stash of one in-flight micro-batch."""
 
-    def __init__(self, cfg: Config, tp, dev, dt, first, last, Vp):
+    def __init__(self, cfg: Config, tp, dev, dt, first, last, Vp, group=None, index=0):
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo, Hl = d // tp, 4 * d // tp, cfg.n_head // tp
         e = lambda *s: _buf(s, dt, dev)
         f = lambda *s: _buf(s, torch.float32, dev)
         self.x = [e(R, d) for _ in range(cfg.n_layer + 1)]   # residual stream: x[l] enters layer l
         self.layers = []
-        for _ in range(cfg.n_layer):
-            self.layers.append(dict(
-                ln1=e(R, d), mean1=f(R), rstd1=f(R), qkv=e(R, 3 * dl), att=e(R, dl), lse=f(cfg.batch, Hl, cfg.seq),
-                xmid=e(R, d), ln2=e(R, d), mean2=f(R), rstd2=f(R), pre=e(R, fo), act=e(R, fo)))
+        for l in range(cfg.n_layer):
+            g = (lambda name, *shp: group.view(l, name, index)) if group is not None else (lambda name, *shp: e(*shp))
+            a = dict(
+                ln1=g("ln1", R, d), mean1=f(R), rstd1=f(R), qkv=e(R, 3 * dl), att=g("att", R, dl),
+                lse=f(cfg.batch, Hl, cfg.seq), xmid=e(R, d), ln2=g("ln2", R, d), mean2=f(R), rstd2=f(R),
+                pre=e(R, fo), act=g("act", R, fo))
+            if group is not None:
+                for k in ("d_out", "d_pre", "d_mid", "d_qkv"):
+                    a[k] = group.view(l, k, index)
+            self.layers.append(a)
         self.tok = torch.zeros(R, dtype=torch.int32, device=dev)
         self.tgt = torch.zeros(R, dtype=torch.int32, device=dev)
         if last:
@@ -84,7 +111,7 @@ class _Slot:
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype=torch.bfloat16, tp=1, tp_rank=0, first=True, last=True,
-                 untied_head=False, n_slots=1, dp=1, alloc=None):
+                 untied_head=False, n_slots=1, dp=1, alloc=None, defer_dw=False):
         assert cfg.d_model % cfg.n_head == 0 and cfg.n_head % tp == 0
         self.cfg, self.tp, self.tp_rank = cfg, tp, tp_rank
         self.first, self.last = first, last
@@ -97,7 +124,10 @@ class GPT:
         self.params.alloc_moments()
         self.step = 0
         self.Vp = _pad64(cfg.vocab)
-        self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp) for _ in range(n_slots)]
+        # deferred weight gradients: backward only stores each layer's output gradients; flush_dw()
+        # forms all weight and bias gradients of the step in one pass over every micro-batch
+        self.group = _SlotGroup(cfg, tp, self.device, dtype, n_slots) if defer_dw else None
+        self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp, self.group, i) for i in range(n_slots)]
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo = d // tp, 4 * d // tp
         e = lambda *s: _buf(s, dtype, self.device)
@@ -111,7 +141,8 @@ class GPT:
         self.s_lnpart = torch.zeros(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
                                     dtype=torch.float32, device=self.device)
         cuda = self.device.type == "cuda"
-        ncs = max(ops.colsum_scratch_elems(R, n) for n in (d, fo, 3 * dl)) if cuda else 1
+        Rc = R * (n_slots if defer_dw else 1)
+        ncs = max(ops.colsum_scratch_elems(Rc, n) for n in (d, fo, 3 * dl)) if cuda else 1
         self.s_colsum = torch.zeros(ncs, dtype=torch.float32, device=self.device)
         self.s_table = torch.empty(2 * cfg.vocab, dtype=torch.int32, device=self.device)
         self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -346,6 +377,9 @@ class GPT:
         B, T, Hl, hd = cfg.batch, cfg.seq, cfg.n_head // tp, cfg.head_dim
         P, Gd = self.params.c, self.params.grad
         dx, other = self.s_dx
+        defer = self.group is not None
+        if defer:       # the gradient w.r.t. the stage output lands in the top layer's stash
+            dx = s.layers[cfg.n_layer - 1]["d_out"]
         if self.last:
             want_loss = loss_scale is not None and not self.skip_loss
             if self.vp_group is None:
@@ -368,6 +402,24 @@ class GPT:
                               Gd["lnf_b"], self.s_lnpart)
         else:
             ops.plan_call(dx.copy_, dx_out)
+        if defer:
+            for l in reversed(range(cfg.n_layer)):
+                a = s.layers[l]
+                nxt = s.layers[l - 1]["d_out"] if l > 0 else self.s_dx[0]
+                ops.gemm(a["d_out"], self.L(l, "fcproj_w"), a["d_pre"], b_mn=True, epi=ops.EPI_DGELU, aux=a["pre"])
+                self._row_parallel(a["d_pre"], self.L(l, "fc_w"), self.s_dln, b_mn=True)
+                ops.layernorm_bwd(self.s_dln, a["xmid"], self.L(l, "ln2_w"), a["mean2"], a["rstd2"], a["d_out"],
+                                  a["d_mid"], self.G(l, "ln2_w"), self.G(l, "ln2_b"), self.s_lnpart)
+                ops.gemm(a["d_mid"], self.L(l, "proj_w"), self.s_datt, b_mn=True)
+                ops.flash_bwd(a["qkv"], a["att"], self.s_datt, a["lse"], a["d_qkv"], self.s_delta, B, T, Hl, hd)
+                self._row_parallel(a["d_qkv"], self.L(l, "qkv_w"), self.s_dln, b_mn=True)
+                ops.layernorm_bwd(self.s_dln, s.x[l], self.L(l, "ln1_w"), a["mean1"], a["rstd1"], a["d_mid"], nxt,
+                                  self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
+            dx = self.s_dx[0]
+            if self.first:
+                ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T, table=self.s_table)
+                return None
+            return dx
         for l in reversed(range(cfg.n_layer)):
             a = s.layers[l]
             # x[l+1] = xmid + act @ Wfp^T + b
@@ -395,6 +447,22 @@ class GPT:
             ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T, table=self.s_table)
             return None
         return dx
+
+    def flush_dw(self, lo=0, hi=None):
+        """Weight and bias gradients of all layers from the stashed output gradients of micro-batch
+        slots [lo, hi): one product over (hi - lo) * R rows per weight instead of one per
+        micro-batch (the reference forms them inside every micro-batch's backward,
+        src/core/gpt.c:726-761)."""
+        g = self.group
+        hi = g.n if hi is None else hi
+        if hi <= lo:
+            return
+        pairs = (("d_out", "act", "fcproj"), ("d_pre", "ln2", "fc"), ("d_mid", "att", "proj"), ("d_qkv", "ln1", "qkv"))
+        for l in reversed(range(self.cfg.n_layer)):
+            for dy, x, name in pairs:
+                dyr, xr = g.rows(l, dy, lo, hi), g.rows(l, x, lo, hi)
+                ops.colsum(dyr, self.G(l, name + "_b"), scratch=self.s_colsum)
+                ops.gemm(dyr, xr, self.G(l, name + "_w"), a_mn=True, b_mn=True, accumulate=True)
 
     def gather_prob(self, slot=0):
         """p(target) per row from the logits of the last forward (src/core/kernels.cu:372-378)."""

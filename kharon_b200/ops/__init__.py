@@ -399,6 +399,20 @@ def wait_probe(flag, target: int, limit_ms: int, status):
     _call(_lib().kh_wait_probe, 1, flag.data_ptr(), int(target), int(limit_ms), status.data_ptr(), _stream())
 
 
+def p2p_put(src, dst_ptr: int, flag_ptr: int, state):
+    """Push ``src`` (contiguous) to device address ``dst_ptr`` (normally a peer's mailbox slot) and then
+    store-release the next sequence number to ``flag_ptr``; ``state`` = two zero-initialised int32
+    device words of this slot (csrc/comm/p2p_mailbox.cu)."""
+    _call(_lib().kh_p2p_put, 1, src.data_ptr(), int(dst_ptr), src.numel() * src.element_size(), int(flag_ptr),
+          state.data_ptr(), _stream())
+
+
+def p2p_wait(flag_ptr: int, expected, limit_ms: int):
+    """Stream-ordered bounded wait until the counter at ``flag_ptr`` reaches the next expected value
+    (``expected`` = one int32 device word, advanced on success); code 7 in the error word on time-out."""
+    _call(_lib().kh_p2p_wait, 1, int(flag_ptr), expected.data_ptr(), int(limit_ms), _stream())
+
+
 # ------------------------------------------------------------------------------ paged KV
 def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
     """Scatter k, v of each new token into its block: pool layout [n_blocks, bs, H, hd]."""

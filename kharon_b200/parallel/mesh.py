@@ -8,6 +8,8 @@ innermost, so a TP group is a run of adjacent GPUs.  Process groups:
 * ``dp_group``   ranks that share (stage, tp_rank)
 * ``tie_group``  first and last stage of one pipeline (same dp_rank, tp_rank); carries the
                  gradient exchange that keeps the embedding and the head tied
+* ``pp_group``   all stages of one pipeline (same dp_rank, tp_rank), group rank = stage; used to
+  exchange the addresses of the stage mailboxes
 * pipeline neighbours are ``rank -/+ tp`` on the world group (src/pp_train.c:27)
 
 One process per GPU; bootstrap is the TCP store of ``torchrun`` (the reference used MPI only
@@ -76,7 +78,7 @@ class Mesh:
         if tp * pp * dp != self.world:
             raise ValueError("mesh %dx%dx%d does not cover %d ranks" % (tp, pp, dp, self.world))
         self.c = Coord(self.rank, self.world, tp, pp, dp)
-        self.tp_group = self.dp_group = self.tie_group = None
+        self.tp_group = self.dp_group = self.tie_group = self.pp_group = None
         to = datetime.timedelta(seconds=timeout_s)
         # every rank must create every group, in the same order
         for d in range(dp):
@@ -98,13 +100,19 @@ class Mesh:
                     g = dist.new_group(ranks, timeout=to)
                     if self.rank in ranks:
                         self.tie_group = g
+            for d in range(dp):         # all stages of one pipeline, group rank = stage
+                for t in range(tp):
+                    ranks = [rank_of(d, s, t, tp, pp) for s in range(pp)]
+                    g = dist.new_group(ranks, timeout=to)
+                    if self.rank in ranks:
+                        self.pp_group = g
 
     @classmethod
     def single(cls):
         m = cls.__new__(cls)
         m.world, m.rank = 1, 0
         m.c = Coord(0, 1, 1, 1, 1)
-        m.tp_group = m.dp_group = m.tie_group = None
+        m.tp_group = m.dp_group = m.tie_group = m.pp_group = None
         return m
 
     def describe(self):

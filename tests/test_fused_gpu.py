@@ -110,6 +110,21 @@ def _worker(rank, world, port, out_dir):
         vp[split] = (ls, e.model.params.w.clone().cpu())
     res["vp_losses"] = {k: v[0] for k, v in vp.items()}
     res["vp_werr"] = ((vp[True][1] - vp[False][1]).norm() / vp[False][1].norm()).item()
+    # pipeline (PP = world): mailbox transport + deferred weight gradients vs blocking NCCL 1F1B
+    mesh_pp = Mesh(1, world, 1, timeout_s=120)
+    kp = dict(kw, mesh=mesh_pp, n_micro=4)
+    pl = {}
+    for name, opt in (("mailbox", dict(fused_comm=True)), ("nccl_deferred", dict(fused_comm=False)),
+                      ("nccl_1f1b", dict(fused_comm=False, defer_dw=False))):
+        e = TrainEngine(**opt, **kp)
+        idx, tgt = Rng(7).batch(e.tokens_per_step, 512)
+        ls = []
+        for _ in range(5):
+            e.train_step(idx, tgt)
+            ls.append(e.loss() if mesh_pp.c.last else 0.0)
+        pl[name] = ls
+    res["pp_losses"] = pl
+    res["word_pp"] = ops.error_word()
     # ZeRO-1: fused reduce-scatter + AdamW + bf16 all-gather kernel vs the NCCL path, DP = world
     mesh_dp = Mesh(1, 1, world, timeout_s=120)
     kw["mesh"] = mesh_dp
@@ -148,6 +163,10 @@ def test_fused_tp_kernels_two_gpus():
         va, vb = r["vp_losses"][False], r["vp_losses"][True]
         assert max(abs(x - y) for x, y in zip(va, vb)) < 2e-2, (va, vb)
         assert r["vp_werr"] < 1e-2, r["vp_werr"]      # Adam turns bf16-level gradient noise into sign flips
+        assert r["word_pp"] == 0
+        for name in ("nccl_deferred", "nccl_1f1b"):
+            pa, pb = r["pp_losses"]["mailbox"], r["pp_losses"][name]
+            assert max(abs(x - y) for x, y in zip(pa, pb)) < 2e-2, (name, pa, pb)
         za, zb = r["zero_losses"][False], r["zero_losses"][True]
         assert max(abs(x - y) for x, y in zip(za, zb)) < 2e-2, (za, zb)
         assert r["zero_werr"] < 1e-3, r["zero_werr"]

@@ -299,6 +299,28 @@ def test_bounded_wait_runs_out_and_reports_status():
     assert torch.ones(4, device=DEV).sum().item() == 4.0     # the context still works
 
 
+def test_mailbox_put_then_wait_and_wait_that_runs_out():
+    """The pipeline mailbox primitives on one device (the slot is local memory here): a put delivers
+    the bytes and raises the slot counter, the wait queued behind it passes and advances its expected
+    count; a wait for a message nobody sends gives up after its limit with code 7."""
+    src = _rand(300, 64)
+    dst = torch.zeros_like(src)
+    flag = torch.zeros(1, device=DEV, dtype=torch.int32)
+    state = torch.zeros(2, device=DEV, dtype=torch.int32)
+    expected = torch.zeros(1, device=DEV, dtype=torch.int32)
+    for k in range(1, 4):
+        src.add_(1.0)
+        ops.p2p_put(src, dst.data_ptr(), flag.data_ptr(), state)
+        ops.p2p_wait(flag.data_ptr(), expected, 500)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, src) and flag.item() == k and expected.item() == k
+        assert state.tolist() == [k, 0] and ops.error_word() == 0
+    ops.p2p_wait(flag.data_ptr(), expected, 50)          # message 4 never comes
+    torch.cuda.synchronize()
+    assert ops.error_word() == 7 and expected.item() == 3
+    assert ops.error_word() == 0
+
+
 def test_guard_bands_stay_intact_through_training_steps():
     from kharon_b200.engine import TrainEngine
     from kharon_b200.models import gpt

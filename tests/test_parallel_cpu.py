@@ -57,7 +57,12 @@ def _worker(rank, world, port, tp, pp, dp, steps, out_dir, mode):
     from kharon_b200.engine import TrainEngine
     from kharon_b200.parallel.mesh import Mesh
     mesh = Mesh(tp, pp, dp, timeout_s=60)
-    e = TrainEngine(mesh=mesh, pp_split="3,1" if mode == "uneven" else None, **KW)
+    extra = {}
+    if mode == "classic_deferred":      # blocking 1F1B order + one weight-gradient pass at the end
+        extra = dict(defer_dw=True, eager_p2p=False)
+    elif mode == "not_deferred":
+        extra = dict(defer_dw=False)
+    e = TrainEngine(mesh=mesh, pp_split="3,1" if mode == "uneven" else None, **extra, **KW)
     data = _batches(mesh.c.dp_rank, steps, e.tokens_per_step, KW["vocab"])
     losses = []
     prefix = os.path.join(out_dir, "ck")
@@ -124,6 +129,33 @@ def test_mesh_matches_single_process(tp, pp, dp):
             assert torch.allclose(_view(r, "wte"), P["wte"], rtol=1e-4, atol=2e-5)
         if stage == pp - 1 and pp > 1:      # tied copy on the last stage stays equal to the embedding
             assert torch.allclose(_view(r, "head_w"), P["wte"], rtol=1e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("mode", ["classic_deferred", "not_deferred"])
+def test_pipeline_variants_match_single_process(mode):
+    """The default pipeline path defers the weight gradients and sends without waiting; the 1F1B
+    order with a final weight-gradient pass and the per-micro-batch form give the same training."""
+    steps = 3
+    _, ref_losses = _single(steps, 1)
+    with tempfile.TemporaryDirectory() as d:
+        res = _launch(1, 2, 1, steps, d, mode)
+    last = [r for r in res if r["coord"][1] == 1][0]
+    assert max(abs(a - b) for a, b in zip(last["losses"], ref_losses)) < 2e-5
+
+
+def test_deferred_weight_gradients_single_process():
+    from kharon_b200.engine import TrainEngine
+    out = {}
+    for defer in (False, True):
+        e = TrainEngine(defer_dw=defer, **KW)
+        assert e.defer_dw == defer
+        losses = []
+        for idx, tgt in _batches(0, 3, e.tokens_per_step, KW["vocab"]):
+            e.train_step(idx, tgt)
+            losses.append(e.loss())
+        out[defer] = (losses, e.model.params.w.clone())
+    assert max(abs(a - b) for a, b in zip(out[True][0], out[False][0])) < 2e-5
+    assert torch.allclose(out[True][1], out[False][1], rtol=1e-4, atol=2e-5)
 
 
 def test_uneven_pipeline_split_matches_single_process():

@@ -188,3 +188,35 @@ def test_1f1b_schedule_is_consistent(P, M):
             break
         assert progressed, "pipeline schedule deadlocks"
     assert all(not v for v in chan.values())
+
+
+def test_deferred_pipeline_schedule_is_consistent():
+    """Every micro-batch: receive -> forward -> send, receive grad -> backward -> send grad, each
+    once and in that order; the weight-gradient passes cover [0, M) once, only over finished
+    micro-batches; stages agree on the order of the messages they exchange."""
+    from kharon_b200.engine import (pp_schedule_deferred, PP_FWD, PP_BWD, PP_FLUSH_DW, PP_RECV_ACT, PP_SEND_ACT,
+                                    PP_RECV_GRAD, PP_SEND_GRAD)
+    for P, M in [(1, 4), (2, 8), (4, 8), (3, 5), (2, 2), (4, 2)]:
+        scheds = [pp_schedule_deferred(s, P, M) for s in range(P)]
+        for s, sc in enumerate(scheds):
+            f = [a for op, a, _ in sc if op == PP_FWD]
+            b = [a for op, a, _ in sc if op == PP_BWD]
+            assert f == list(range(M)) and b == list(range(M))
+            done_b, covered = set(), []
+            pos = {}
+            for k, (op, a0, a1) in enumerate(sc):
+                pos[(op, a0)] = k
+                if op == PP_BWD:
+                    assert (PP_FWD, a0) in pos
+                    done_b.add(a0)
+                if op == PP_FLUSH_DW:
+                    assert all(i in done_b for i in range(a0, a1))
+                    covered += list(range(a0, a1))
+            assert covered == list(range(M))
+            for i in range(M):
+                if s > 0:
+                    assert pos[(PP_RECV_ACT, i)] < pos[(PP_FWD, i)] and pos[(PP_BWD, i)] < pos[(PP_SEND_GRAD, i)]
+                if s < P - 1:
+                    assert pos[(PP_FWD, i)] < pos[(PP_SEND_ACT, i)] and pos[(PP_RECV_GRAD, i)] < pos[(PP_BWD, i)]
+            # in-flight forwards never exceed the micro-batch slots
+            assert len(sc) < 8 * (M + P) + 16
