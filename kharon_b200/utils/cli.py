@@ -2,6 +2,11 @@
 
 Same conventions as the reference binaries (src/train.c:29-41): flags are scanned linearly,
 unknown flags are ignored, a bare flag is a boolean.  ``--help`` prints the known flags.
+
+Every flag can also be written ``--kh-<name>``.  That spelling is for launches under
+``python -m torch.distributed.run``, whose argument parser rejects the whole command line when a
+script flag is an abbreviation of one of its own options (``--d`` of ``--duplicate-...``, ``--log``
+of ``--log-dir``): ``... -m kharon_b200.pp_train --kh-d 2048 --kh-log 10``.
 """
 from __future__ import annotations
 
@@ -15,9 +20,9 @@ class Flags:
         self.known = []
 
     def _find(self, name):
-        key = "--" + name
+        keys = ("--" + name, "--kh-" + name)
         for i, a in enumerate(self.argv):
-            if a == key:
+            if a in keys:
                 return i
         return -1
 

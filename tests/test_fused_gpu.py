@@ -111,6 +111,8 @@ def _worker(rank, world, port, out_dir):
     res["vp_losses"] = {k: v[0] for k, v in vp.items()}
     res["vp_werr"] = ((vp[True][1] - vp[False][1]).norm() / vp[False][1].norm()).item()
     # pipeline (PP = world): mailbox transport + deferred weight gradients vs blocking NCCL 1F1B
+    from kharon_b200.parallel import p2p
+    p2p.WAIT_LIMIT_MS = 4000
     mesh_pp = Mesh(1, world, 1, timeout_s=120)
     kp = dict(kw, mesh=mesh_pp, n_micro=4)
     pl = {}
