@@ -1,5 +1,6 @@
 """Tracing / metrics plumbing: per-phase timers, roofline fractions, JSONL metrics."""
 import json
+import os
 
 import torch
 
@@ -28,3 +29,12 @@ def test_jsonl_metrics(tmp_path):
                 "--jsonl", str(out)])
     rows = [json.loads(l) for l in open(out)]
     assert [r["step"] for r in rows] == [2, 4] and all("loss" in r and "tok_s" in r for r in rows)
+
+
+def test_plot_writes_charts_without_a_display(tmp_path):
+    """bench/plot.py renders the committed results file headlessly (SVG writer when matplotlib is absent)."""
+    from kharon_b200.bench import plot
+    made = plot.main([os.path.join(os.path.dirname(plot.__file__), "results.json"), str(tmp_path)])
+    assert len(made) == 3
+    for m in made:
+        assert os.path.getsize(m) > 500
