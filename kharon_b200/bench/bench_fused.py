@@ -1,6 +1,7 @@
 """``python -m kharon_b200.bench.bench_fused ROWS N`` (default 8192 2048, reference bench/bench_fused.c:30-31):
 memory-bound kernels as achieved HBM bandwidth: LayerNorm fwd/bwd, column sum, cross-entropy
-(fwd+bwd in place), AdamW."""
+(fwd+bwd in place; and the vocabulary-sliced statistics / gradient pair of the TP head), the embedding
+gather and its deterministic backward, the pipeline mailbox put (looped back to local memory), AdamW."""
 import json
 import sys
 
@@ -33,6 +34,28 @@ def main(argv=None):
     rl = torch.empty(Rv, device=dev)
     t = time_ms(lambda: ops.xent(lg, V, tgt, uniform=1.0 / Rv, rowloss=rl), flush=fl)
     res["xent_fwd_bwd_GBs"] = 3 * Rv * ld * 2 / t / 1e6
+    st = torch.empty(Rv, 3, device=dev); gm = torch.zeros(Rv, device=dev); gs = torch.ones(Rv, device=dev)
+    Vs = (V + 1) // 2
+    t = time_ms(lambda: ops.xent_stats(lg, Vs, tgt, 0, st), flush=fl)
+    res["xent_stats_GBs"] = Rv * Vs * 2 / t / 1e6
+    t = time_ms(lambda: ops.xent_grad(lg, Vs, tgt, 0, gm, gs, uniform=1.0 / Rv), flush=fl)
+    res["xent_grad_GBs"] = 2 * Rv * Vs * 2 / t / 1e6
+    # embedding: R rows of width N gathered from a [V, N] table (+ positions), and the backward into fp32
+    T = 512
+    tok = torch.randint(0, V, (R,), device=dev, dtype=torch.int32)
+    wte = torch.randn(V, N, device=dev).bfloat16(); wpe = torch.randn(T, N, device=dev).bfloat16()
+    pos = (torch.arange(R, device=dev, dtype=torch.int32) % T)
+    t = time_ms(lambda: ops.embed_fwd(tok, pos, wte, wpe, y, T), flush=fl)
+    res["embed_fwd_GBs"] = 3 * R * N * 2 / t / 1e6
+    gwte = torch.zeros(V, N, device=dev); gwpe = torch.zeros(T, N, device=dev)
+    table = torch.empty(2 * V, dtype=torch.int32, device=dev)
+    t = time_ms(lambda: ops.embed_bwd(tok, dy, gwte, gwpe, R // T, T, table=table), flush=fl)
+    res["embed_bwd_ms"] = t
+    # pipeline mailbox put of one [2048, N] message (8 MB at N = 2048), local loop-back
+    msg = torch.randn(2048, N, device=dev).bfloat16(); box = torch.empty_like(msg)
+    flag = torch.zeros(1, device=dev, dtype=torch.int32); state = torch.zeros(2, device=dev, dtype=torch.int32)
+    t = time_ms(lambda: ops.p2p_put(msg, box.data_ptr(), flag.data_ptr(), state), flush=fl)
+    res["p2p_put_local_GBs"] = 2 * msg.numel() * 2 / t / 1e6
     n = 64 << 20
     p = torch.randn(n, device=dev); g = torch.randn(n, device=dev); m = torch.zeros(n, device=dev); v = torch.zeros(n, device=dev)
     pb = torch.empty(n, device=dev, dtype=torch.bfloat16)

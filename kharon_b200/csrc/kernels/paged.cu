@@ -47,24 +47,34 @@ extern "C" int kh_append_kv(const void* qkv, int ld, void* kc, void* vc, const v
 // ------------------------------------------------------------------------------- attention
 // CTA = (token, head), 128 threads.  Phase 1: thread j scores keys j, j+128, ... (whole dot
 // product in registers, 16-byte K loads, q broadcast from shared memory).  Phase 2: block
-// max / sum.  Phase 3: thread e accumulates out[e] = sum_j p_j V[j][e] with coalesced V reads
-// (threads split the keys 128/hd ways when hd < 128 and combine in shared memory in a fixed
-// order).  Context = positions 0..pos of the token's own sequence (the new token's K/V was
-// appended before this kernel).
+// max / sum.  Phase 3: HD/8 threads share one value row (16-byte loads), 128/(HD/8) rows are in
+// flight per iteration, and the row groups are combined in shared memory in a fixed order.
+// Context = positions 0..pos of the token's own sequence.  With `append` != 0 (decode steps: one
+// new token per sequence) the CTA first copies its token's k and v for this head from the qkv row
+// into the cache, which replaces the separate append launch; otherwise the new tokens' K/V must
+// already be in the cache (prefill: several tokens of one sequence attend to each other).
 template <int HD>
 __global__ void __launch_bounds__(128)
-paged_attn_k(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+paged_attn_k(const bf16* __restrict__ qkv, int ld, bf16* __restrict__ kc, bf16* __restrict__ vc,
              bf16* __restrict__ out, const int* __restrict__ pos, const int* __restrict__ slot,
-             const int* __restrict__ btab, int max_lb, int bs, int H, float scale, int max_ctx) {
+             const int* __restrict__ btab, int max_lb, int bs, int H, float scale, int max_ctx, int append) {
   extern __shared__ float sm[];
+  constexpr int TPR = HD / 8;               // threads per value row
+  constexpr int GROUPS = 128 / TPR;         // value rows in flight
   float* s_q = sm;                // HD
   float* s_p = sm + HD;           // max_ctx scores / probabilities
-  float* s_red = s_p + max_ctx;   // 128 floats of reduction scratch (+ HD * (128/HD) partial outputs)
+  float* s_red = s_p + max_ctx;   // GROUPS * HD partial outputs (>= 128 floats of reduction scratch)
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int d = H * HD;
   const int ctx = pos[t] + 1;
   const int* bt = btab + (size_t)slot[t] * max_lb;
   for (int e = tid; e < HD; e += 128) s_q[e] = __bfloat162float(qkv[(size_t)t * ld + h * HD + e]) * scale;
+  if (append && tid < 2 * TPR) {
+    const int p = ctx - 1, which = tid / TPR, c = (tid % TPR) * 8;
+    const size_t dst = ((size_t)bt[p / bs] * bs + (p % bs)) * d + h * HD + c;
+    const uint4 v = *reinterpret_cast<const uint4*>(qkv + (size_t)t * ld + (which + 1) * d + h * HD + c);
+    *reinterpret_cast<uint4*>((which ? vc : kc) + dst) = v;
+  }
   __syncthreads();
   float lmax = -INFINITY;
   for (int j = tid; j < ctx; j += 128) {
@@ -104,27 +114,30 @@ paged_attn_k(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ kc, 
   const float inv = 1.f / s_red[0];
   __syncthreads();
   // phase 3
-  constexpr int SPLIT = 128 / HD;          // key splits handled by different thread groups
-  const int e = tid % HD, part = tid / HD;
-  float acc = 0.f;
-  for (int j = part; j < ctx; j += SPLIT) {
-    const bf16* vp = vc + ((size_t)bt[j / bs] * bs + (j % bs)) * d + h * HD;
-    acc += s_p[j] * __bfloat162float(vp[e]);
-  }
-  if (SPLIT > 1) {
-    s_red[tid] = acc;
-    __syncthreads();
-    if (part == 0) {
+  const int c8 = (tid % TPR) * 8, grp = tid / TPR;
+  float acc[8];
 #pragma unroll
-      for (int k = 1; k < SPLIT; k++) acc += s_red[k * HD + e];
-    }
+  for (int k = 0; k < 8; k++) acc[k] = 0.f;
+  for (int j = grp; j < ctx; j += GROUPS) {
+    const uint4 v = *reinterpret_cast<const uint4*>(vc + ((size_t)bt[j / bs] * bs + (j % bs)) * d + h * HD + c8);
+    const float p = s_p[j];
+    float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), e = unpack_bf16(v.w);
+    acc[0] += p * a.x; acc[1] += p * a.y; acc[2] += p * b.x; acc[3] += p * b.y;
+    acc[4] += p * cc.x; acc[5] += p * cc.y; acc[6] += p * e.x; acc[7] += p * e.y;
   }
-  if (part == 0) out[(size_t)t * d + h * HD + e] = __float2bfloat16(acc * inv);
+#pragma unroll
+  for (int k = 0; k < 8; k++) s_red[grp * HD + c8 + k] = acc[k];
+  __syncthreads();
+  if (tid < HD) {
+    float o = 0.f;
+    for (int g = 0; g < GROUPS; g++) o += s_red[g * HD + tid];
+    out[(size_t)t * d + h * HD + tid] = __float2bfloat16(o * inv);
+  }
 }
-extern "C" int kh_paged_attn(const void* qkv, int ld, const void* kc, const void* vc, void* out, const void* pos,
+extern "C" int kh_paged_attn(const void* qkv, int ld, void* kc, void* vc, void* out, const void* pos,
                              const void* slot, const void* btab, int max_lb, int bs, int H, int hd, float scale,
-                             int ntok, int max_ctx, void* stream) {
-  const size_t smem = (size_t)(hd + max_ctx + 128 + 8) * sizeof(float);
+                             int ntok, int max_ctx, int append, void* stream) {
+  const size_t smem = (size_t)(hd + max_ctx + 1024 + 8) * sizeof(float);
   if (smem > 200 * 1024) { kh_set_error("paged_attn: context %d does not fit in shared memory", max_ctx); return -1; }
   dim3 grid(ntok, H);
   cudaStream_t st = (cudaStream_t)stream;
@@ -132,9 +145,9 @@ extern "C" int kh_paged_attn(const void* qkv, int ld, const void* kc, const void
   {                                                                                                                  \
     static size_t attr = 48 * 1024;                                                                                  \
     if (smem > attr) { cudaFuncSetAttribute(paged_attn_k<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; } \
-    paged_attn_k<HD><<<grid, 128, smem, st>>>((const bf16*)qkv, ld, (const bf16*)kc, (const bf16*)vc, (bf16*)out,     \
+    paged_attn_k<HD><<<grid, 128, smem, st>>>((const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (bf16*)out,                 \
                                               (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, H,    \
-                                              scale, max_ctx);                                                       \
+                                              scale, max_ctx, append);                                               \
   }
   if (hd == 128) LAUNCH(128)
   else if (hd == 64) LAUNCH(64)

@@ -124,9 +124,11 @@ class InferEngine:
             ln, qkv, att, xmid = self.ln[:ntok], self.qkv[:ntok], self.att[:ntok], self.xmid[:ntok]
             ops.layernorm_fwd(xs, m.L(l, "ln1_w"), m.L(l, "ln1_b"), ln)
             self._lin(ln, m.L(l, "qkv_w"), qkv, ops.EPI_BIAS, m.L(l, "qkv_b"))
-            ops.append_kv(qkv, self.kc[l], self.vc[l], pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok)
+            decode = ntok == nseq        # one new token per sequence: the attention kernel appends k, v itself
+            if not decode:
+                ops.append_kv(qkv, self.kc[l], self.vc[l], pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok)
             ops.paged_attn(qkv, self.kc[l], self.vc[l], att, pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok,
-                           cfg.seq)
+                           cfg.seq, append=decode)
             # row-parallel products: one GEMM, or under TP the fused GEMM + all-reduce kernel / NCCL seam
             self._row(att, m.L(l, "proj_w"), xmid, m.L(l, "proj_b"), xs)
             ops.layernorm_fwd(xmid, m.L(l, "ln2_w"), m.L(l, "ln2_b"), ln)

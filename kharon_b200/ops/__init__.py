@@ -422,14 +422,18 @@ def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
                              slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd, ntok, _stream())
 
 
-def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx):
+def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx, append=False):
     """Causal attention of each listed token over positions 0..pos of its own sequence, K/V read
-    through the block table."""
+    through the block table.  ``append``: the kernel itself stores each token's k, v into the cache
+    first (valid when no two listed tokens belong to one sequence, i.e. decode steps); otherwise
+    ``append_kv`` must have run."""
     if not qkv.is_cuda:
+        if append:
+            ref.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
         return ref.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok)
     _call(_lib().kh_paged_attn, 1, qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
                               pos.data_ptr(), slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd,
-                              1.0 / math.sqrt(hd), ntok, max_ctx, _stream())
+                              1.0 / math.sqrt(hd), ntok, max_ctx, int(append), _stream())
 
 
 def gather_rows(x, rows, out, nseq):

@@ -30,10 +30,13 @@ def test_paged_kernels(hd, H):
         slot = torch.tensor(tok_slot, device="cuda", dtype=torch.int32)
         qkv = torch.randn(ntok, 3 * d, device="cuda").bfloat16()
         out = torch.empty(ntok, d, device="cuda", dtype=torch.bfloat16); out2 = torch.empty_like(out)
-        ops.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
+        if phase == 0:
+            ops.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
         ref.append_kv(qkv, kc2, vc2, pos, slot, btab, bs, H, hd, ntok)
+        # decode step: the attention kernel stores the new k, v itself
+        ops.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, 64, append=phase == 1)
+        torch.cuda.synchronize()
         assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
-        ops.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, 64)
         ref.paged_attn(qkv, kc2, vc2, out2, pos, slot, btab, bs, H, hd, ntok)
         err = ((out.float() - out2.float()).norm() / out2.float().norm()).item()
         assert err < 1e-2, err
