@@ -13,6 +13,10 @@
 //   independent of arrival order, so decoding is reproducible.
 //
 // Epilogues as in the big GEMM: bias, bias+GELU (pre-activation kept), bias+residual.
+// Optional LayerNorm prologue (up to 16 rows): instead of loading x tiles with TMA, the CTA computes
+// each row's mean / rstd over the full K, normalises its own K slice in registers and writes it
+// into the B-operand tiles in the 128-byte-swizzled layout the MMA descriptor expects, so a decode
+// layer needs no separate LayerNorm launch and the normalised rows never touch global memory.
 // The reference used the same cuBLAS call for M = 1..32 as for training (src/core/infer.c:152-180).
 // Waits are bounded (error word code 1/3).
 #include "common.cuh"
@@ -35,6 +39,8 @@ struct SkinnyParams {
   int epi;
   const bf16* bias;
   bf16* aux; int ldaux;
+  const bf16* x; int ldx;            // raw activation rows (LayerNorm prologue only)
+  const bf16* ln_w; const bf16* ln_b;  // non-null: y = LayerNorm(x) * ln_w + ln_b feeds the product
   int* counters;        // [n_tiles], zero between launches
   float* partials;      // [split][MP][N]
   int* err;
@@ -75,13 +81,62 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const uint32_t tmem = *tmem_slot;
 
   bool ok = true;
+  const bool fuse_ln = (MP == 16) && p.ln_w != nullptr;
   if (tid == 0) {
     for (int i = 0; i < nkb; i++) {
       const uint32_t sw = base + i * STAGE, sx = sw + W_BYTES;
-      mbar_expect_tx(bar_full + 8 * i, STAGE);
+      mbar_expect_tx(bar_full + 8 * i, fuse_ln ? W_BYTES : STAGE);
       tma_load_2d(sw, &map_w, bar_full + 8 * i, (kb0 + i) * BK, nt * TN);
-      tma_load_2d(sx, &map_x, bar_full + 8 * i, (kb0 + i) * BK, 0);
+      if (!fuse_ln) tma_load_2d(sx, &map_x, bar_full + 8 * i, (kb0 + i) * BK, 0);
     }
+  }
+  if (fuse_ln) {
+    // 8 threads per row: statistics over the whole row (two passes, fp32), then this CTA's K slice
+    const int r = tid >> 3, sub = tid & 7;
+    const bool live = r < p.M;
+    const bf16* xr = p.x + (size_t)r * p.ldx;
+    const int nchunk = p.K >> 3;                     // 16-byte chunks per row (K % 8 == 0)
+    float sum = 0.f;
+    if (live)
+      for (int c = sub; c < nchunk; c += 8) {
+        const uint4 u = *reinterpret_cast<const uint4*>(xr + c * 8);
+        float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), e = unpack_bf16(u.w);
+        sum += (a.x + a.y) + (b.x + b.y) + (cc.x + cc.y) + (e.x + e.y);
+      }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1); sum += __shfl_xor_sync(0xffffffffu, sum, 2); sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    const float mean = sum / (float)p.K;
+    float sq = 0.f;
+    if (live)
+      for (int c = sub; c < nchunk; c += 8) {
+        const uint4 u = *reinterpret_cast<const uint4*>(xr + c * 8);
+        float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), e = unpack_bf16(u.w);
+        float d0 = a.x - mean, d1 = a.y - mean, d2 = b.x - mean, d3 = b.y - mean, d4 = cc.x - mean, d5 = cc.y - mean,
+              d6 = e.x - mean, d7 = e.y - mean;
+        sq += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3 + d4 * d4 + d5 * d5 + d6 * d6 + d7 * d7;
+      }
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1); sq += __shfl_xor_sync(0xffffffffu, sq, 2); sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+    const float rstd = rsqrtf(sq / (float)p.K + 1e-5f);
+    for (int i = 0; i < nkb; i++) {
+      const int col = (kb0 + i) * BK + sub * 8;
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (live && col < p.K) {
+        const uint4 u = *reinterpret_cast<const uint4*>(xr + col);
+        const uint4 gw = __ldg(reinterpret_cast<const uint4*>(p.ln_w + col)), gb = __ldg(reinterpret_cast<const uint4*>(p.ln_b + col));
+        const uint32_t* ui = &u.x; const uint32_t* wi = &gw.x; const uint32_t* bi = &gb.x; uint32_t* oi = &o.x;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const float2 xv = unpack_bf16(ui[k]), wv = unpack_bf16(wi[k]), bv = unpack_bf16(bi[k]);
+          oi[k] = pack_bf16((xv.x - mean) * rstd * wv.x + bv.x, (xv.y - mean) * rstd * wv.y + bv.y);
+        }
+      }
+      const uint32_t sx = base + i * STAGE + W_BYTES;
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sx + r * 128 + ((sub ^ (r & 7)) << 4)), "r"(o.x), "r"(o.y),
+                   "r"(o.z), "r"(o.w) : "memory");
+    }
+    fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's async proxy
+  }
+  __syncthreads();
+  if (tid == 0) {
     constexpr uint32_t idesc = umma_idesc_bf16(TN, MP, 0, 0);
     for (int i = 0; i < nkb && ok; i++) {
       if (!mbar_wait(bar_full + 8 * i, 0, abort_flag, 1, p.err)) { ok = false; break; }
@@ -205,8 +260,14 @@ extern "C" long kh_gemm_skinny_scratch_elems(int M, int N, int K) {
   return COUNTER_SLOTS + (long)pick_split(N, K) * pad_rows(M) * N;
 }
 extern "C" int kh_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
-                              int epi, const void* bias, void* aux, int ldaux, void* scratch, void* stream) {
+                              int epi, const void* bias, void* aux, int ldaux, void* scratch, const void* ln_w,
+                              const void* ln_b, void* stream) {
   if (M < 1 || M > 64) { kh_set_error("gemm_skinny: M=%d outside [1, 64]", M); return -1; }
+  if ((ln_w != nullptr) != (ln_b != nullptr)) { kh_set_error("gemm_skinny: LayerNorm needs both weight and bias"); return -1; }
+  if (ln_w && (M > 16 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15))) {
+    kh_set_error("gemm_skinny: fused LayerNorm needs M <= 16, K %% 8 == 0 and 16-byte aligned rows (M=%d K=%d)", M, K);
+    return -1;
+  }
   const int n_tiles = (N + TN - 1) / TN;
   if (n_tiles > COUNTER_SLOTS) { kh_set_error("gemm_skinny: N=%d exceeds %d column tiles", N, COUNTER_SLOTS * TN); return -1; }
   if (epi != EPI_NONE && !bias) { kh_set_error("gemm_skinny: bias missing"); return -1; }
@@ -221,6 +282,7 @@ extern "C" int kh_gemm_skinny(const void* x, int ldx, const void* W, int ldw, vo
   const int split = pick_split(N, K);
   p.kb_per_cta = (p.num_kb + split - 1) / split;
   p.out = (bf16*)out; p.ldo = ldo; p.epi = epi; p.bias = (const bf16*)bias; p.aux = (bf16*)aux; p.ldaux = ldaux;
+  p.x = (const bf16*)x; p.ldx = ldx; p.ln_w = (const bf16*)ln_w; p.ln_b = (const bf16*)ln_b;
   p.counters = (int*)scratch; p.partials = (float*)scratch + COUNTER_SLOTS;
   p.err = kh_error_word_dev();
   cudaStream_t st = (cudaStream_t)stream;

@@ -122,8 +122,7 @@ class InferEngine:
         ops.embed_fwd(tok, pos, P["wte"], P["wpe"], xs, cfg.seq)
         for l in range(cfg.n_layer):
             ln, qkv, att, xmid = self.ln[:ntok], self.qkv[:ntok], self.att[:ntok], self.xmid[:ntok]
-            ops.layernorm_fwd(xs, m.L(l, "ln1_w"), m.L(l, "ln1_b"), ln)
-            self._lin(ln, m.L(l, "qkv_w"), qkv, ops.EPI_BIAS, m.L(l, "qkv_b"))
+            self._ln_lin(xs, m.L(l, "ln1_w"), m.L(l, "ln1_b"), ln, m.L(l, "qkv_w"), qkv, ops.EPI_BIAS, m.L(l, "qkv_b"))
             decode = ntok == nseq        # one new token per sequence: the attention kernel appends k, v itself
             if not decode:
                 ops.append_kv(qkv, self.kc[l], self.vc[l], pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok)
@@ -131,15 +130,15 @@ class InferEngine:
                            cfg.seq, append=decode)
             # row-parallel products: one GEMM, or under TP the fused GEMM + all-reduce kernel / NCCL seam
             self._row(att, m.L(l, "proj_w"), xmid, m.L(l, "proj_b"), xs)
-            ops.layernorm_fwd(xmid, m.L(l, "ln2_w"), m.L(l, "ln2_b"), ln)
-            self._lin(ln, m.L(l, "fc_w"), self.act[:ntok], ops.EPI_BIAS_GELU, m.L(l, "fc_b"), self.pre[:ntok])
+            self._ln_lin(xmid, m.L(l, "ln2_w"), m.L(l, "ln2_b"), ln, m.L(l, "fc_w"), self.act[:ntok], ops.EPI_BIAS_GELU,
+                         m.L(l, "fc_b"), self.pre[:ntok])
             ys = nxt[:ntok]
             self._row(self.act[:ntok], m.L(l, "fcproj_w"), ys, m.L(l, "fcproj_b"), xmid)
             x, nxt = nxt, x
             xs = ys
         ops.gather_rows(xs, self.d_rows, self.last, nseq)
-        ops.layernorm_fwd(self.last[:nseq], P["lnf_w"], P["lnf_b"], self.lnf[:nseq])
-        self._lin(self.lnf[:nseq], m.head_weight(), self.logits[:nseq, :cfg.vocab])
+        self._ln_lin(self.last[:nseq], P["lnf_w"], P["lnf_b"], self.lnf[:nseq], m.head_weight(),
+                     self.logits[:nseq, :cfg.vocab])
         ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq)
 
     def _lin(self, x, w, out, epi=ops.EPI_NONE, bias=None, aux=None):
@@ -148,6 +147,15 @@ class InferEngine:
             ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux)
         else:
             ops.gemm(x, w, out, epi=epi, bias=bias, aux=aux)
+
+    def _ln_lin(self, x, ln_w, ln_b, ln_out, w, out, epi=ops.EPI_NONE, bias=None, aux=None):
+        """LayerNorm followed by a linear layer: for decode-sized inputs the skinny kernel normalises
+        the rows itself (no LayerNorm launch, ``ln_out`` stays unused)."""
+        if self.skinny is not None and x.shape[0] <= ops.SKINNY_BEST_ROWS and x.shape[1] % 8 == 0:
+            ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux, ln_w=ln_w, ln_b=ln_b)
+        else:
+            ops.layernorm_fwd(x, ln_w, ln_b, ln_out)
+            self._lin(ln_out, w, out, epi, bias, aux)
 
     def _row(self, x, w, out, bias, resid):
         """Row-parallel linear layer (+ bias + residual); summed over the TP group when there is one."""

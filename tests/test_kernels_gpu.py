@@ -279,6 +279,31 @@ def test_gemm_skinny(M, N, K):
     assert ops.error_word() == 0
 
 
+@pytest.mark.parametrize("M", [1, 5, 16])
+@pytest.mark.parametrize("N,K", [(3072, 1024), (4096, 1024), (50257, 1024), (200, 192)])
+def test_gemm_skinny_with_layernorm_prologue(M, N, K):
+    """LayerNorm folded into the weight-streaming GEMM equals LayerNorm followed by the GEMM."""
+    torch.manual_seed(10)
+    x = _rand(M, K, scale=2.0) + 0.5
+    w = _rand(N, K, scale=0.1)
+    bias = _rand(N)
+    lw, lb = (1.0 + 0.1 * torch.randn(K, device=DEV)).bfloat16(), (0.1 * torch.randn(K, device=DEV)).bfloat16()
+    ld = (N + 63) // 64 * 64
+    scratch = torch.zeros(ops.gemm_skinny_scratch_elems(M, N, K), device=DEV)
+    y = torch.empty_like(x)
+    ref.layernorm_fwd(x, lw, lb, y, None, None)
+    for epi in (ops.EPI_NONE, ops.EPI_BIAS, ops.EPI_BIAS_GELU):
+        aux = torch.zeros(M, ld, device=DEV, dtype=torch.bfloat16)[:, :N]
+        aux_ref = aux.clone()
+        out = torch.zeros(M, ld, device=DEV, dtype=torch.bfloat16)[:, :N]
+        want = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_skinny(x, w, out, scratch, epi=epi, bias=bias, aux=aux, ln_w=lw, ln_b=lb)
+        ref.gemm(y, w, want, False, False, False, epi, bias, aux_ref, 1.0)
+        assert relerr(out, want) < 1e-2, (epi, relerr(out, want))
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+
+
 def test_bounded_wait_status_word_is_clean():
     assert ops.error_word() == 0
 
