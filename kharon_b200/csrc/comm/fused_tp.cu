@@ -3,8 +3,11 @@
 //   gemm_comm, mode AR : out[M,N]      = sum_r A_r * op(B_r)   on every rank      (GEMM -> all-reduce)
 //   gemm_comm, mode RS : out[M/tp,N]   = rows [rank*M/tp, ...) of that sum         (GEMM -> reduce-scatter)
 //   optional gather    : A is the row-wise concatenation of per-rank shards that live in
-//                        peer memory (all-gather -> GEMM), read tile by tile with plain
-//                        (non-multicast) TMA loads through per-rank tensor maps.
+//                        peer memory (all-gather -> GEMM).  A few CTAs of the same launch act as
+//                        copiers: they pull the peers' shards over NVLink once, 32 KB at a time
+//                        with non-multicast bulk copies (peer -> shared memory -> local gather
+//                        buffer), and publish every 128-row block through a counter; the GEMM CTAs
+//                        start on the local rows and read remote rows from the local copy.
 //
 // These replace the reference's cuBLAS GEMM followed by a blocking bf16 ncclAllReduce on the
 // same stream (src/core/gpt.c:686-687, 692-693, 745-746, 760-761; src/parallel/comms.cu:97-99).
@@ -62,13 +65,27 @@ struct CommParams {
   uint32_t* epoch;             // local: [0] calls completed on this buffer set, [1] CTAs finished; null: host counts
   uint32_t* flags[MAX_TP];     // flags[r]: rank r's arrival counters [tp][num_tiles]
   uint32_t* ready[MAX_TP];     // gather mode: ready[r]: rank r's "shard published" counters [tp]
+  const bf16* shard[MAX_TP];   // gather mode: rank r's row shard [M/tp, K], contiguous, as mapped here
+  bf16* gbuf;                  // gather mode: local [M, K] buffer that receives the remote rows
+  uint32_t* blk_ready;         // gather mode: per 128-row block, calls for which the block has been delivered
+  int n_copy;                  // gather mode: CTAs at the end of the grid that copy instead of multiplying
   uint32_t call_no;            // 1-based call number when the host counts
   uint32_t ready_target;
   int* err;
 };
 
 // out: the local output; st[r]: slot `rank` of rank r's staging (where this rank's partial goes)
-struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap st[2][MAX_TP]; };
+struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap st[2][MAX_TP]; CUtensorMap g; };
+
+constexpr int COPY_CHUNK = 32 * 1024, COPY_SLOTS = 4;
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -165,6 +182,10 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   const uint32_t target = 4u * call;           // counter value that means "this call's partial has arrived"
   const int par = (int)(call & 1u);
   const bf16* my_stage = p.stage[p.rank] + (size_t)par * p.slot_elems;
+  // gather mode: the last n_copy CTAs of the grid pull the peers' shards, the others multiply
+  const int n_workers = (int)gridDim.x - (p.gather ? p.n_copy : 0);
+  const int worker = (int)blockIdx.x;
+  const bool copier = worker >= n_workers;
 
   // Tiles are visited M-band by M-band starting with this rank's own rows, so that in gather mode
   // local shards are consumed while the peers' shards are still being published.
@@ -192,17 +213,73 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       }
       int it = 0;
       bool ok = true;
-      uint32_t seen = 1u << p.rank;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      if (copier) {
+        // ---- copier CTA: peers' shards -> local gather buffer.  Remote 128-row blocks are dealt
+        // round-robin to the copiers in the order the multiplying CTAs reach them; a copier moves
+        // its block in 32 KB pieces with up to four bulk loads in flight, then publishes the block
+        const int cid = worker - n_workers;
+        for (int r = 0; r < p.tp && ok; r++)
+          if (r != p.rank && !wait_counter(p.ready[p.rank] + r, p.ready_target, abort_flag, p.err)) ok = false;
+        asm volatile("fence.proxy.async;" ::: "memory");     // the acquire above orders generic accesses; bulk copies are async-proxy
+        const size_t blk_bytes = (size_t)BM * p.K * 2;
+        const int pieces = (int)((blk_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
+        const int shift = p.rank * (rows_per_rank / BM);
+        uint32_t uses[COPY_SLOTS] = {0, 0, 0, 0};
+        int remote_no = 0;
+        for (int i = 0; i < tiles_m && ok; i++) {
+          const int tm = (i + shift) % tiles_m;
+          const int src = owner_of(tm);
+          if (src == p.rank) continue;
+          if ((remote_no++) % p.n_copy != cid) continue;
+          const char* sbase = reinterpret_cast<const char*>(p.shard[src]) + (size_t)(tm * BM - src * rows_per_rank) * p.K * 2;
+          char* dbase = reinterpret_cast<char*>(p.gbuf) + (size_t)tm * blk_bytes;
+          for (int q0 = 0; q0 < pieces && ok; q0 += COPY_SLOTS) {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // slots no longer read by earlier stores
+            int nb = 0;
+            for (int j = 0; j < COPY_SLOTS; j++, nb++) {
+              const int q = q0 + j;
+              if (q >= pieces) break;
+              const size_t off = (size_t)q * COPY_CHUNK;
+              const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, blk_bytes - off);
+              mbar_expect_tx(bar_full + 8 * j, bytes);
+              bulk_load_1d(smem_base + j * COPY_CHUNK, sbase + off, bytes, bar_full + 8 * j);
+            }
+            for (int j = 0; j < nb; j++) {
+              if (!mbar_wait(bar_full + 8 * j, uses[j] & 1, abort_flag, 6, p.err)) { ok = false; break; }
+              uses[j]++;
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              const size_t off = (size_t)(q0 + j) * COPY_CHUNK;
+              const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, blk_bytes - off);
+              bulk_store_1d(dbase + off, smem_base + j * COPY_CHUNK, bytes);
+            }
+            tma_store_commit();
+          }
+          // block tm is complete in local memory: publish it
+          tma_store_wait_all();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          atomicAdd(p.blk_ready + tm, 1u);
+        }
+        tma_store_wait_all();
+      }
+      int ready_tm = -1;
+      for (int t = worker; !copier && ok && t < num_tiles; t += n_workers) {
         int tm, tn;
         tile_coord(t, tm, tn);
-        int src = 0, row_in_src = tm * BM;
+        const CUtensorMap* amap = &maps.a[0];
+        int row_in_src = tm * BM;
         if (p.gather) {
-          src = owner_of(tm);
-          row_in_src = tm * BM - src * rows_per_rank;
-          if (!(seen & (1u << src))) {
-            if (!wait_counter(p.ready[p.rank] + src, p.ready_target, abort_flag, p.err)) { ok = false; break; }
-            seen |= 1u << src;
+          const int src = owner_of(tm);
+          if (src == p.rank) {
+            amap = &maps.a[p.rank];
+            row_in_src = tm * BM - src * rows_per_rank;
+          } else {
+            amap = &maps.g;
+            if (ready_tm != tm) {      // the block's copier has delivered it (one increment per call)
+              if (!wait_counter(p.blk_ready + tm, call, abort_flag, p.err)) { ok = false; break; }
+              asm volatile("fence.proxy.async;" ::: "memory");
+              ready_tm = tm;
+            }
           }
         }
         for (int kb = 0; kb < num_kb; kb++, it++) {
@@ -211,9 +288,9 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
           mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-          if (!p.a_mn) tma_load_2d(sa, &maps.a[src], bar_full + 8 * s, kb * BK, row_in_src);
+          if (!p.a_mn) tma_load_2d(sa, amap, bar_full + 8 * s, kb * BK, row_in_src);
           else
-            for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), &maps.a[src], bar_full + 8 * s, row_in_src + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), amap, bar_full + 8 * s, row_in_src + j * 64, kb * BK);
           if (!p.b_mn) tma_load_2d(sb, &maps.b, bar_full + 8 * s, kb * BK, tn * BN);
           else
             for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * (BK * 128), &maps.b, bar_full + 8 * s, tn * BN + j * 64, kb * BK);
@@ -228,7 +305,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       const uint32_t b_kstep = p.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
       int it = 0, tcount = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+      for (int t = worker; !copier && ok && t < num_tiles; t += n_workers, tcount++) {
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
         if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1, abort_flag, 4, p.err)) { ok = false; break; }
@@ -267,7 +344,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       }
       atomicAdd(const_cast<int*>(s_pub), 4);
     };
-    for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, tcount++) {
+    for (int t = worker; !copier && ok && t < num_tiles; t += n_workers, tcount++) {
       int tm, tn;
       tile_coord(t, tm, tn);
       const int acc = tcount & 1;
@@ -337,7 +414,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
     const int rw = warp - 6;
     int tcount = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && p.mode != MODE_LOCAL && t < num_tiles; t += gridDim.x, tcount++) {
+    for (int t = worker; !copier && ok && p.mode != MODE_LOCAL && t < num_tiles; t += n_workers, tcount++) {
       int tm, tn;
       tile_coord(t, tm, tn);
       const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
@@ -460,18 +537,28 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
                             void* out, int ldo, int M, int N, int K, int mode, int gather, int tp, int rank,
                             const unsigned long long* stage_ptrs, const unsigned long long* flag_ptrs,
                             const unsigned long long* ready_ptrs, unsigned call_no, unsigned gather_no,
-                            unsigned long long epoch_ptr, const void* bias, const void* resid, int ldr, int max_ctas, void* stream) {
+                            unsigned long long epoch_ptr, void* gather_buf, void* blk_ready, const void* bias, const void* resid, int ldr, int max_ctas, void* stream) {
   if (tp < 2 || tp > MAX_TP || rank < 0 || rank >= tp) { kh_set_error("gemm_comm: bad tp/rank %d/%d", rank, tp); return -1; }
   if ((mode == MODE_RS || gather) && M % (tp * BM)) { kh_set_error("gemm_comm: M=%d must be a multiple of tp*128 for row-sharded modes", M); return -1; }
   if (M < 1) { kh_set_error("gemm_comm: empty problem"); return -1; }
   if (N % 8 || ldo % 8 || ((uintptr_t)out & 15)) { kh_set_error("gemm_comm: N and the output pitch must be multiples of 8"); return -1; }
+  if (gather && (a_mn || lda != K || !gather_buf || !blk_ready || !epoch_ptr)) {
+    kh_set_error("gemm_comm: gather mode needs row-major contiguous shards (lda == K), a gather buffer, block counters and an epoch word");
+    return -1;
+  }
   Maps maps;
   const int rows_a = gather ? M / tp : M;
-  for (int r = 0; r < (gather ? tp : 1); r++) {
+  {   // the local operand: the whole A, or in gather mode this rank's own shard
+    const int r = gather ? rank : 0;
     const void* A = (const void*)a_ptrs[r];
     const CUtensorMap* ta = a_mn ? kh_tmap_2d_bf16(A, K, rows_a, lda, BK, 64) : kh_tmap_2d_bf16(A, rows_a, K, lda, BM, BK);
     if (!ta) return -1;
     maps.a[r] = *ta;
+  }
+  if (gather) {
+    const CUtensorMap* tg = kh_tmap_2d_bf16(gather_buf, M, K, K, BM, BK);
+    if (!tg) return -1;
+    maps.g = *tg;
   }
   const CUtensorMap* tb = b_mn ? kh_tmap_2d_bf16(B, K, N, ldb, BK, 64) : kh_tmap_2d_bf16(B, N, K, ldb, BN, BK);
   if (!tb) return -1;
@@ -496,6 +583,14 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
     p.flags[r] = (uint32_t*)flag_ptrs[r];
     p.ready[r] = ready_ptrs ? (uint32_t*)ready_ptrs[r] : nullptr;
   }
+  int n_copy = 0;
+  if (gather) {
+    for (int r = 0; r < tp; r++) p.shard[r] = (const bf16*)a_ptrs[r];
+    p.gbuf = (bf16*)gather_buf;
+    p.blk_ready = (uint32_t*)blk_ready;
+    n_copy = 12;
+  }
+  p.n_copy = n_copy;
   p.call_no = call_no;
   p.slot_elems = slot_elems;
   p.epoch = (uint32_t*)epoch_ptr;
@@ -508,8 +603,10 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
     attr = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int grid = tiles < num_sms() ? tiles : num_sms();
-  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  int grid = tiles < num_sms() - n_copy ? tiles : num_sms() - n_copy;
+  if (max_ctas > 0 && grid > max_ctas - n_copy) grid = max_ctas - n_copy;
+  if (grid < 1) grid = 1;
+  grid += n_copy;
   gemm_comm_kernel<<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(maps, p);
   KH_LAUNCH_CHECK("gemm_comm");
   return 0;

@@ -13,9 +13,9 @@
 //            loads, sums them in rank order, scales by 1/dp, updates master / moments, and
 //            PUSHES the bf16 value into the compute copy of every rank (8-byte stores, a warp
 //            covers 256 contiguous bytes);
-//   phase 2  every CTA announces completion to every peer and waits until all CTAs of all peers
-//            have done so: all peers have finished reading this rank's gradients and writing
-//            this rank's compute copy;
+//   phase 2  every CTA announces completion to every rank (its own included) and waits until all
+//            CTAs of all ranks have done so: everybody, the other CTAs of this launch too, has
+//            finished reading this rank's gradients and writing this rank's compute copy;
 //   phase 3  the local gradient arena is cleared for the next accumulation.
 //
 // Only 2 bytes per parameter travel in the gather direction (the reference gathers 4), and the
@@ -119,11 +119,12 @@ zero1_step_kernel(const ZeroParams p) {
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
-    for (int r = 0; r < p.dp; r++)
-      if (r != p.rank) red_release_sys_add(p.ctr[r] + p.dp + p.rank, 1);
+    // the local counter is part of the barrier: phase 3 of one CTA overwrites gradients that a
+    // slower CTA of the same launch may still have to read in phase 1
+    for (int r = 0; r < p.dp; r++) red_release_sys_add(p.ctr[r] + p.dp + p.rank, 1);
     int ok = 1;
     for (int r = 0; r < p.dp && ok; r++)
-      if (r != p.rank) ok = wait_counter(p.ctr[p.rank] + p.dp + r, p.epoch * gridDim.x, p.err) ? 1 : 0;
+      ok = wait_counter(p.ctr[p.rank] + p.dp + r, p.epoch * gridDim.x, p.err) ? 1 : 0;
     s_ok = ok;
   }
   __syncthreads();

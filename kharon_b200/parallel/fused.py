@@ -90,7 +90,7 @@ class FusedTP:
         ptr = (C.c_uint64 * 1)(a.data_ptr())
         ops._call(_native.cuda().kh_gemm_comm, 1, ptr, a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                   out.data_ptr(), out.stride(0), M, N, K, mode, 0, self.tp, self.rank, c.c_stage, c.c_flags,
-                  c.c_ready, 0, 0, c.epoch.data_ptr(), ops._p(bias), ops._p(resid),
+                  c.c_ready, 0, 0, c.epoch.data_ptr(), None, None, ops._p(bias), ops._p(resid),
                   resid.stride(0) if resid is not None else 0, self.max_ctas, ops._stream())
         return out
 
@@ -116,10 +116,16 @@ class FusedTP:
         # gather mode uses a context of its own: its "reduction" is local-only (tp slots unused)
         c = self._get(M, N, 2)
         c.gathers += 1
+        if getattr(c, "gbuf_k", None) != K:      # local landing buffer for the remote rows + per-block counters
+            c.gbuf = torch.empty(M, K, dtype=torch.bfloat16, device=self.device)
+            c.blk_ready = torch.zeros((M + 127) // 128, dtype=torch.int32, device=self.device)
+            c.epoch.zero_()
+            c.gbuf_k = K
         lib = _native.cuda()
         rc = lib.kh_gemm_comm(ptrs, lda, 0, b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0),
                               M, N, K, 2, 1, self.tp, self.rank, c.c_stage, c.c_flags, c.c_ready,
-                              0, c.gathers, c.epoch.data_ptr(), None, None, 0, self.max_ctas,
+                              0, c.gathers, c.epoch.data_ptr(), c.gbuf.data_ptr(), c.blk_ready.data_ptr(), None, None, 0,
+                              self.max_ctas,
                               torch.cuda.current_stream().cuda_stream)
         ops._chk(rc)
         ops.launch_count += 1

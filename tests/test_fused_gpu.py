@@ -21,7 +21,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, part):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
@@ -44,8 +44,8 @@ def _worker(rank, world, port, out_dir):
             part = part + bias.float() + resid.float()
         return part
 
-    errs, same = [], []
-    for it in range(5):                      # repeated calls exercise the staging parity
+    errs, errs_rs, errs_ag, same = [], [], [], []
+    for it in range(5 if part == "kernels" else 0):                      # repeated calls exercise the staging parity
         for b_mn in (False, True):
             a = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
             b = (torch.randn(K, N, device=dev) if b_mn else torch.randn(N, K, device=dev)).mul(0.1).bfloat16()
@@ -64,11 +64,12 @@ def _worker(rank, world, port, out_dir):
             shard = torch.zeros(M // world, N, device=dev, dtype=torch.bfloat16)
             rs = resid[rank * M // world:(rank + 1) * M // world] if use_b else None
             f.gemm_rs(a, b, shard, b_mn=b_mn, bias=bias if use_b else None, resid=rs)
-            errs.append(rel(shard, want[rank * M // world:(rank + 1) * M // world]))
+            errs_rs.append(rel(shard, want[rank * M // world:(rank + 1) * M // world]))
     # all-gather -> GEMM: A = concat of per-rank shards in symmetric memory
     rows = 512
-    sh, ptrs, h = f.symmetric_rows(rows, K)
-    for it in range(3):
+    if part == "kernels":
+        sh, ptrs, h = f.symmetric_rows(rows, K)
+    for it in range(3 if part == "kernels" else 0):
         sh.copy_((torch.randn(rows, K, device=dev) * 0.5).bfloat16())
         w = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
         out = torch.zeros(rows * world, N, device=dev, dtype=torch.bfloat16)
@@ -76,103 +77,131 @@ def _worker(rank, world, port, out_dir):
         full = [torch.empty_like(sh) for _ in range(world)]
         dist.all_gather(full, sh.contiguous())
         want = torch.cat(full, 0).float() @ w.float().t()
-        errs.append(rel(out, want))
+        errs_ag.append(rel(out, want))
         torch.cuda.synchronize()
         dist.barrier()          # the shard is rewritten next iteration
     torch.cuda.synchronize()
-    res["errs"], res["same"], res["word"] = errs, same, ops.error_word()
+    res["errs"], res["errs_rs"], res["errs_ag"], res["same"], res["word"] = errs, errs_rs, errs_ag, same, ops.error_word()
 
-    # engine: fused path vs NCCL baseline path, TP = world
     from kharon_b200.engine import TrainEngine
     from kharon_b200.utils.rng import Rng
     kw = dict(layers=2, d_model=256, heads=4, vocab=512, seq=128, mbatch=4, n_micro=2, device=dev, lr=1e-3, wd=0.0,
               mesh=mesh)
-    losses = {}
-    for fused in (False, True):
-        e = TrainEngine(fused_comm=fused, **kw)
-        idx, tgt = Rng(5).batch(e.tokens_per_step, 512)
-        ls = []
-        for _ in range(6):
-            e.train_step(idx, tgt)
-            ls.append(e.loss())
-        losses[fused] = ls
-    res["losses"] = losses
-    # vocabulary-parallel head (the default) against the replicated head, odd vocabulary
-    kv = dict(kw, vocab=509)
-    vp = {}
-    for split in (False, True):
-        e = TrainEngine(fused_comm=True, vocab_parallel=split, **kv)
-        idx, tgt = Rng(6).batch(e.tokens_per_step, 509)
-        ls = []
-        for _ in range(5):
-            e.train_step(idx, tgt)
-            ls.append(e.loss())
-        vp[split] = (ls, e.model.params.w.clone().cpu())
-    res["vp_losses"] = {k: v[0] for k, v in vp.items()}
-    res["vp_werr"] = ((vp[True][1] - vp[False][1]).norm() / vp[False][1].norm()).item()
-    # pipeline (PP = world): mailbox transport + deferred weight gradients vs blocking NCCL 1F1B
-    from kharon_b200.parallel import p2p
-    p2p.WAIT_LIMIT_MS = 4000
-    mesh_pp = Mesh(1, world, 1, timeout_s=120)
-    kp = dict(kw, mesh=mesh_pp, n_micro=4)
-    pl = {}
-    for name, opt in (("mailbox", dict(fused_comm=True)), ("nccl_deferred", dict(fused_comm=False)),
-                      ("nccl_1f1b", dict(fused_comm=False, defer_dw=False))):
-        e = TrainEngine(**opt, **kp)
-        idx, tgt = Rng(7).batch(e.tokens_per_step, 512)
-        ls = []
-        for _ in range(5):
-            e.train_step(idx, tgt)
-            ls.append(e.loss() if mesh_pp.c.last else 0.0)
-        pl[name] = ls
-    res["pp_losses"] = pl
-    res["word_pp"] = ops.error_word()
-    # ZeRO-1: fused reduce-scatter + AdamW + bf16 all-gather kernel vs the NCCL path, DP = world
-    mesh_dp = Mesh(1, 1, world, timeout_s=120)
-    kw["mesh"] = mesh_dp
-    zl, zw = {}, {}
-    for fused in (False, True):
-        e = TrainEngine(fused_comm=fused, **kw)
-        idx, tgt = Rng(50 + mesh_dp.c.dp_rank).batch(e.tokens_per_step, 512)
-        ls = []
-        for _ in range(6):
-            e.train_step(idx, tgt)
-            ls.append(e.loss())
-        e.gather_master()
-        zl[fused], zw[fused] = ls, e.model.params.w.clone().cpu()
-        assert e.model.params.g.abs().max().item() == 0
-    res["zero_losses"] = zl
-    res["zero_werr"] = ((zw[True] - zw[False]).norm() / zw[False].norm()).item()
+    if part == "tp":
+        # engine: fused path vs NCCL baseline path, TP = world
+        losses = {}
+        for fused in (False, True):
+            e = TrainEngine(fused_comm=fused, **kw)
+            idx, tgt = Rng(5).batch(e.tokens_per_step, 512)
+            ls = []
+            for _ in range(6):
+                e.train_step(idx, tgt)
+                ls.append(e.loss())
+            losses[fused] = ls
+        res["losses"] = losses
+        # vocabulary-parallel head (the default) against the replicated head, odd vocabulary
+        kv = dict(kw, vocab=509)
+        vp = {}
+        for split in (False, True):
+            e = TrainEngine(fused_comm=True, vocab_parallel=split, **kv)
+            idx, tgt = Rng(6).batch(e.tokens_per_step, 509)
+            ls = []
+            for _ in range(5):
+                e.train_step(idx, tgt)
+                ls.append(e.loss())
+            vp[split] = (ls, e.model.params.w.clone().cpu())
+        res["vp_losses"] = {k: v[0] for k, v in vp.items()}
+        res["vp_werr"] = ((vp[True][1] - vp[False][1]).norm() / vp[False][1].norm()).item()
+    if part == "pp":
+        # pipeline (PP = world): mailbox transport + deferred weight gradients vs blocking NCCL 1F1B
+        from kharon_b200.parallel import p2p
+        p2p.WAIT_LIMIT_MS = 4000
+        mesh_pp = Mesh(1, world, 1, timeout_s=120)
+        kp = dict(kw, mesh=mesh_pp, n_micro=4)
+        pl = {}
+        for name, opt in (("mailbox", dict(fused_comm=True)), ("nccl_deferred", dict(fused_comm=False)),
+                          ("nccl_1f1b", dict(fused_comm=False, defer_dw=False)), ("mailbox_again", dict(fused_comm=True))):
+            e = TrainEngine(**opt, **kp)
+            idx, tgt = Rng(7).batch(e.tokens_per_step, 512)
+            ls = []
+            for _ in range(5):
+                e.train_step(idx, tgt)
+                ls.append(e.loss() if mesh_pp.c.last else 0.0)
+            pl[name] = ls
+        res["pp_losses"] = pl
+    if part == "zero":
+        # ZeRO-1: fused reduce-scatter + AdamW + bf16 all-gather kernel vs the NCCL path, DP = world
+        mesh_dp = Mesh(1, 1, world, timeout_s=120)
+        kw["mesh"] = mesh_dp
+        zl, zw = {}, {}
+        for fused in (False, True):
+            e = TrainEngine(fused_comm=fused, **kw)
+            idx, tgt = Rng(50 + mesh_dp.c.dp_rank).batch(e.tokens_per_step, 512)
+            ls = []
+            for _ in range(6):
+                e.train_step(idx, tgt)
+                ls.append(e.loss())
+            e.gather_master()
+            zl[fused], zw[fused] = ls, e.model.params.w.clone().cpu()
+            assert e.model.params.g.abs().max().item() == 0
+        res["zero_losses"] = zl
+        res["zero_werr"] = ((zw[True] - zw[False]).norm() / zw[False].norm()).item()
+    torch.cuda.synchronize()
     res["word2"] = ops.error_word()
     torch.save(res, os.path.join(out_dir, "r%d.pt" % rank))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_tp_kernels_two_gpus():
+def _run(part):
     import torch.multiprocessing as mp
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_worker, args=(2, _free_port(), d), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, _free_port(), d, part), nprocs=2, join=True)
         res = [torch.load(os.path.join(d, "r%d.pt" % r), weights_only=False) for r in range(2)]
     for r in res:
         assert r["word"] == 0 and r["word2"] == 0
-        assert max(r["errs"]) < 1e-2, r["errs"]
+    return res
+
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+@needs2
+def test_fused_tp_kernels_two_gpus():
+    for r in _run("kernels"):
+        assert max(r["errs"]) < 1e-2, ("gemm_ar", r["errs"])
+        assert max(r["errs_rs"]) < 1e-2, ("gemm_rs", r["errs_rs"])
+        assert max(r["errs_ag"]) < 1e-2, ("ag_gemm", r["errs_ag"])
         assert all(r["same"])
+
+
+@needs2
+def test_tp_engine_fused_matches_nccl_two_gpus():
+    res = _run("tp")
+    for r in res:
         a, b = r["losses"][False], r["losses"][True]
         assert max(abs(x - y) for x, y in zip(a, b)) < 3e-2, (a, b)
         assert b[-1] < b[0]
         va, vb = r["vp_losses"][False], r["vp_losses"][True]
         assert max(abs(x - y) for x, y in zip(va, vb)) < 2e-2, (va, vb)
         assert r["vp_werr"] < 1e-2, r["vp_werr"]      # Adam turns bf16-level gradient noise into sign flips
-        assert r["word_pp"] == 0
-        for name in ("nccl_deferred", "nccl_1f1b"):
+    assert res[0]["losses"][True] == res[1]["losses"][True]
+
+
+@needs2
+def test_pipeline_mailbox_matches_nccl_two_gpus():
+    for r in _run("pp"):
+        for name in ("nccl_deferred", "nccl_1f1b", "mailbox_again"):
             pa, pb = r["pp_losses"]["mailbox"], r["pp_losses"][name]
             assert max(abs(x - y) for x, y in zip(pa, pb)) < 2e-2, (name, pa, pb)
+
+
+@needs2
+def test_zero1_fused_matches_nccl_two_gpus():
+    for r in _run("zero"):
         za, zb = r["zero_losses"][False], r["zero_losses"][True]
         assert max(abs(x - y) for x, y in zip(za, zb)) < 2e-2, (za, zb)
         assert r["zero_werr"] < 1e-3, r["zero_werr"]
-    assert res[0]["losses"][True] == res[1]["losses"][True]
 
 
 def _decode_worker(rank, world, port, out_dir):
