@@ -96,6 +96,16 @@ struct TmapHash {
     return (size_t)h;
   }
 };
+static size_t g_tmap_limit = 1u << 16;
+// Test hook: number of cached descriptors after which the index is dropped (returns the old limit).
+extern "C" long kh_tmap_cache_limit(long n) {
+  const long old = (long)g_tmap_limit;
+  if (n > 0) g_tmap_limit = (size_t)n;
+  return old;
+}
+
+// Returns a descriptor that stays valid for the life of the process: callers hold the pointer
+// across further look-ups (a launch fetches the A, B and output maps one after the other).
 const CUtensorMap* kh_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                    uint32_t box_rows, uint32_t box_cols) {
   static std::unordered_map<TmapKey, CUtensorMap*, TmapHash> cache;
@@ -127,8 +137,11 @@ const CUtensorMap* kh_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t col
                  (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_rows, box_cols);
     return nullptr;
   }
-  if (cache.size() > 4096) {   // buffers come from long-lived arenas; this only bounds pathological churn
-    for (auto& kv : cache) delete kv.second;
+  if (cache.size() >= g_tmap_limit) {
+    // Buffers come from long-lived arenas, so this only bounds pathological churn.  The index is
+    // dropped but the descriptors themselves are deliberately NOT freed (128 bytes each): pointers
+    // handed out earlier, possibly a moment ago to the caller that triggered this insertion, must
+    // not dangle.
     cache.clear();
   }
   cache[key] = m;

@@ -304,6 +304,29 @@ def test_gemm_skinny_with_layernorm_prologue(M, N, K):
     assert ops.error_word() == 0
 
 
+def test_tensor_map_cache_overflow_keeps_descriptors_valid():
+    """The descriptor cache drops its index when full; descriptors handed out before (the A map of
+    the very launch whose B map caused the overflow) must stay valid, so results stay right."""
+    from kharon_b200 import _native
+    lib = _native.cuda()
+    old = lib.kh_tmap_cache_limit(7)
+    try:
+        torch.manual_seed(11)
+        big_a = _rand(128 + 400, 192, scale=0.5)
+        big_b = _rand(256 + 400, 192, scale=0.2)
+        out = torch.empty(128, 256, device=DEV, dtype=torch.bfloat16)
+        want = torch.empty_like(out)
+        for i in range(0, 400, 3):          # every launch sees operands at new addresses
+            a, b = big_a[i:i + 128], big_b[i + 1:i + 257]
+            ops.gemm(a, b, out)
+            ref.gemm(a, b, want, False, False, False, ops.EPI_NONE, None, None, 1.0)
+            assert relerr(out, want) < 8e-3, i
+    finally:
+        lib.kh_tmap_cache_limit(old)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+
+
 def test_bounded_wait_status_word_is_clean():
     assert ops.error_word() == 0
 
