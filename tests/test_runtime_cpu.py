@@ -220,3 +220,21 @@ def test_deferred_pipeline_schedule_is_consistent():
                     assert pos[(PP_FWD, i)] < pos[(PP_SEND_ACT, i)] and pos[(PP_RECV_GRAD, i)] < pos[(PP_BWD, i)]
             # in-flight forwards never exceed the micro-batch slots
             assert len(sc) < 8 * (M + P) + 16
+
+
+def test_cli_flags_accept_the_torchrun_safe_spelling():
+    from kharon_b200.utils.cli import Flags
+    f = Flags(["--layers", "3", "--kh-d", "96", "--kh-log", "7", "--synthetic", "--lr", "1e-3"])
+    assert f.int("layers", 8) == 3 and f.int("d", 512) == 96 and f.int("log", 50) == 7
+    assert f.has("synthetic") and not f.has("resume") and f.float("lr", 3e-4) == 1e-3
+    assert f.int("heads", 8) == 8
+
+
+def test_milestone_script_parses():
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sh = os.path.join(root, "kharon_b200", "bench", "milestones.sh")
+    assert subprocess.run(["bash", "-n", sh]).returncode == 0
+    out = subprocess.run(["bash", sh, "nosuchjob"], capture_output=True, text=True)
+    assert out.returncode == 2 and "usage" in out.stdout
