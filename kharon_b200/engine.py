@@ -347,8 +347,14 @@ class TrainEngine:
         dist.all_gather_into_tensor(tgt_full, tgt_full[lo:hi], group=grp)
 
     def loss(self) -> float:
-        """Mean loss of the last step (valid on the last pipeline stage)."""
-        return float(self.model.loss_acc.item())
+        """Mean loss of the last step (valid on the last pipeline stage).  Reading it synchronises
+        with the device, so this is also where a bounded wait that ran out during the step (a peer
+        that never delivered a partial tile, a mailbox message or its gradients) turns into an
+        exception instead of a silently wrong step."""
+        v = float(self.model.loss_acc.item())
+        if self.device.type == "cuda":
+            ops.check_device_status()
+        return v
 
     # ------------------------------------------------------------------ checkpoint
     def gather_master(self):
