@@ -97,7 +97,7 @@ def _view(res, name):
     return res["w"][o:o + n].view(shp)
 
 
-@pytest.mark.parametrize("tp,pp,dp", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (1, 2, 2)])
+@pytest.mark.parametrize("tp,pp,dp", [(2, 1, 1), (1, 2, 1), (1, 1, 2), (2, 2, 1), (1, 2, 2), (1, 4, 1)])
 def test_mesh_matches_single_process(tp, pp, dp):
     steps = 3
     ref_e, ref_losses = _single(steps, dp)
