@@ -295,11 +295,65 @@ __global__ void layernorm_fwd_k(const bf16* __restrict__ x, const bf16* __restri
     yp[i] = o;
   }
 }
+// Same arithmetic for d = NPL * 256: the warp reads its row once (NPL independent 16-byte loads per
+// lane, all in flight together) and keeps it in registers for the three sweeps.
+template <int NPL>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_reg_k(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
+                    bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows) {
+  constexpr int d = NPL * 256;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+  uint4 v[NPL];
+#pragma unroll
+  for (int j = 0; j < NPL; j++) v[j] = xp[lane + 32 * j];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < NPL; j++) {
+    float2 a = unpack_bf16(v[j].x), bb = unpack_bf16(v[j].y), c = unpack_bf16(v[j].z), e = unpack_bf16(v[j].w);
+    s += (a.x + a.y) + (bb.x + bb.y) + (c.x + c.y) + (e.x + e.y);
+  }
+  const float mu = warp_sum(s) / d;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < NPL; j++) {
+    float2 a = unpack_bf16(v[j].x), bb = unpack_bf16(v[j].y), c = unpack_bf16(v[j].z), e = unpack_bf16(v[j].w);
+    float t;
+    t = a.x - mu; q += t * t; t = a.y - mu; q += t * t; t = bb.x - mu; q += t * t; t = bb.y - mu; q += t * t;
+    t = c.x - mu; q += t * t; t = c.y - mu; q += t * t; t = e.x - mu; q += t * t; t = e.y - mu; q += t * t;
+  }
+  const float rs = rsqrtf(warp_sum(q) / d + 1e-5f);
+  if (lane == 0) { if (mean) mean[row] = mu; if (rstd) rstd[row] = rs; }
+  const uint4* wp = reinterpret_cast<const uint4*>(w);
+  const uint4* bp = reinterpret_cast<const uint4*>(b);
+  uint4* yp = reinterpret_cast<uint4*>(y + (size_t)row * d);
+#pragma unroll
+  for (int j = 0; j < NPL; j++) {
+    const int i = lane + 32 * j;
+    uint4 wv = __ldg(wp + i), bv = __ldg(bp + i), o;
+    const uint32_t* vi = &v[j].x; const uint32_t* wi = &wv.x; const uint32_t* bi = &bv.x; uint32_t* oi = &o.x;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      float2 xv = unpack_bf16(vi[k]), ww = unpack_bf16(wi[k]), bb = unpack_bf16(bi[k]);
+      oi[k] = pack_bf16((xv.x - mu) * rs * ww.x + bb.x, (xv.y - mu) * rs * ww.y + bb.y);
+    }
+    yp[i] = o;
+  }
+}
 extern "C" int kh_layernorm_fwd(const void* x, const void* w, const void* b, void* y, void* mean, void* rstd, int rows,
                                 int d, void* stream) {
   if (d % 8) { kh_set_error("layernorm: d must be a multiple of 8"); return -1; }
-  layernorm_fwd_k<<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
-                                                                    (bf16*)y, (float*)mean, (float*)rstd, rows, d);
+  if (d == 2048)
+    layernorm_fwd_reg_k<8><<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+                                                                           (bf16*)y, (float*)mean, (float*)rstd, rows);
+  else if (d == 1024)
+    layernorm_fwd_reg_k<4><<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+                                                                           (bf16*)y, (float*)mean, (float*)rstd, rows);
+  else
+    layernorm_fwd_k<<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+                                                                      (bf16*)y, (float*)mean, (float*)rstd, rows, d);
   KH_LAUNCH_CHECK("layernorm_fwd");
   return 0;
 }
@@ -351,6 +405,58 @@ __global__ void layernorm_bwd_dx_k(const bf16* __restrict__ dy, const bf16* __re
       oi[k] = pack_bf16(rs * (g.x * ww.x - s1 - xh0 * s2) + rr.x, rs * (g.y * ww.y - s1 - xh1 * s2) + rr.y);
     }
     op[i] = o;
+  }
+}
+template <int NPL>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_dx_reg_k(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                       const float* __restrict__ mean, const float* __restrict__ rstd,
+                       const bf16* __restrict__ dres, bf16* __restrict__ dx, int rows) {
+  constexpr int d = NPL * 256;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* dyp = reinterpret_cast<const uint4*>(dy + (size_t)row * d);
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+  const uint4* wp = reinterpret_cast<const uint4*>(w);
+  const uint4* rp = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * d) : nullptr;
+  const float mu = mean[row], rs = rstd[row];
+  uint4 gv[NPL], xv[NPL], rv[NPL];
+#pragma unroll
+  for (int j = 0; j < NPL; j++) {
+    gv[j] = dyp[lane + 32 * j];
+    xv[j] = xp[lane + 32 * j];
+    rv[j] = rp ? rp[lane + 32 * j] : make_uint4(0, 0, 0, 0);
+  }
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NPL; j++) {
+    const uint4 wv = __ldg(wp + lane + 32 * j);
+    const uint32_t* gi = &gv[j].x; const uint32_t* xi = &xv[j].x; const uint32_t* wi = &wv.x;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      float2 g = unpack_bf16(gi[k]), xx = unpack_bf16(xi[k]), ww = unpack_bf16(wi[k]);
+      float g0 = g.x * ww.x, g1 = g.y * ww.y;
+      s1 += g0 + g1;
+      s2 += g0 * ((xx.x - mu) * rs) + g1 * ((xx.y - mu) * rs);
+    }
+  }
+  s1 = warp_sum(s1) / d;
+  s2 = warp_sum(s2) / d;
+  uint4* op = reinterpret_cast<uint4*>(dx + (size_t)row * d);
+#pragma unroll
+  for (int j = 0; j < NPL; j++) {
+    const uint4 wv = __ldg(wp + lane + 32 * j);
+    uint4 o;
+    const uint32_t* gi = &gv[j].x; const uint32_t* xi = &xv[j].x; const uint32_t* wi = &wv.x; const uint32_t* ri = &rv[j].x;
+    uint32_t* oi = &o.x;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      float2 g = unpack_bf16(gi[k]), xx = unpack_bf16(xi[k]), ww = unpack_bf16(wi[k]), rr = unpack_bf16(ri[k]);
+      float xh0 = (xx.x - mu) * rs, xh1 = (xx.y - mu) * rs;
+      oi[k] = pack_bf16(rs * (g.x * ww.x - s1 - xh0 * s2) + rr.x, rs * (g.y * ww.y - s1 - xh1 * s2) + rr.y);
+    }
+    op[lane + 32 * j] = o;
   }
 }
 __global__ void layernorm_bwd_dwdb_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
@@ -423,7 +529,14 @@ extern "C" int kh_layernorm_bwd(const void* dy, const void* x, const void* w, co
   cudaStream_t st = (cudaStream_t)stream;
   const int parts = kh_layernorm_bwd_parts(rows, d);
   const int rps = (rows + parts - 1) / parts;
-  layernorm_bwd_dx_k<<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+  if (d == 2048)
+    layernorm_bwd_dx_reg_k<8><<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+                                                            (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows);
+  else if (d == 1024)
+    layernorm_bwd_dx_reg_k<4><<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+                                                            (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows);
+  else
+    layernorm_bwd_dx_k<<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
                                                      (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows, d);
   dim3 grid(cdiv(d, 64), parts);
   layernorm_bwd_dwdb_k<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd,
