@@ -161,11 +161,21 @@ __global__ void colsum_k(const bf16* __restrict__ x, int ld, float* __restrict__
 #pragma unroll
   for (int k = 0; k < 8; k++) acc[k] = 0.f;
   if (col + 8 <= N) {
-    for (int r = r0 + rg; r < r1; r += 32) {
-      uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)r * ld + col);
+    auto add = [&](const uint4& v) {
       float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), e = unpack_bf16(v.w);
       acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+    };
+    int r = r0 + rg;
+    // four rows per trip: four independent 16-byte loads in flight per thread, added in row order
+    for (; r + 96 < r1; r += 128) {
+      const bf16* p0 = x + (size_t)r * ld + col;
+      const uint4 v0 = *reinterpret_cast<const uint4*>(p0);
+      const uint4 v1 = *reinterpret_cast<const uint4*>(p0 + (size_t)32 * ld);
+      const uint4 v2 = *reinterpret_cast<const uint4*>(p0 + (size_t)64 * ld);
+      const uint4 v3 = *reinterpret_cast<const uint4*>(p0 + (size_t)96 * ld);
+      add(v0); add(v1); add(v2); add(v3);
     }
+    for (; r < r1; r += 32) add(*reinterpret_cast<const uint4*>(x + (size_t)r * ld + col));
   } else {
     for (int r = r0 + rg; r < r1; r += 32)
       for (int k = 0; k < 8; k++) if (col + k < N) acc[k] += __bfloat162float(x[(size_t)r * ld + col + k]);
