@@ -53,7 +53,10 @@ def _symm_alloc(nbytes, device, group):
     torch.cuda.synchronize(device)
     h.barrier()
     for r in range(h.world_size):
-        got = int(h.get_buffer(r, (1,), torch.int64).item())
+        try:
+            got = int(h.get_buffer(r, (1,), torch.int64).item())
+        except (AttributeError, TypeError, NotImplementedError):
+            break           # this build exposes no typed view of a peer buffer: keep the drain + barrier only
         if got != stamp(r):
             raise RuntimeError("symmetric allocation #%d (%d bytes, group %s): the address mapped for rank %d holds stamp "
                                "%#x, expected %#x" % (_alloc_seq, nbytes, name, r, got, stamp(r)))
