@@ -28,7 +28,7 @@ from .. import _native, ops
 MODE_AR, MODE_RS = 0, 1
 
 
-_alloc_seq = 0
+_alloc_seq = {}      # per process group: allocations rendezvoused on it so far (identical on its ranks)
 
 
 def _symm_alloc(nbytes, device, group):
@@ -42,13 +42,12 @@ def _symm_alloc(nbytes, device, group):
     one run in four of such a sequence trained on corrupted weights or gradients; with it none of
     eleven did.  The stamps turn a handle that pairs the buffer with anything but the peers'
     buffers of the same allocation into an error."""
-    global _alloc_seq
     import torch.distributed._symmetric_memory as symm_mem
     t = symm_mem.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
     name = group.group_name if hasattr(group, "group_name") else group
     h = symm_mem.rendezvous(t, name)
-    _alloc_seq += 1
-    stamp = lambda r: (_alloc_seq << 8) + r + 1
+    seq = _alloc_seq[name] = _alloc_seq.get(name, 0) + 1
+    stamp = lambda r: (seq << 40) + (int(nbytes) << 8) + r + 1
     t[:8].view(torch.int64).fill_(stamp(h.rank))
     torch.cuda.synchronize(device)
     h.barrier()
@@ -59,7 +58,7 @@ def _symm_alloc(nbytes, device, group):
             break           # this build exposes no typed view of a peer buffer: keep the drain + barrier only
         if got != stamp(r):
             raise RuntimeError("symmetric allocation #%d (%d bytes, group %s): the address mapped for rank %d holds stamp "
-                               "%#x, expected %#x" % (_alloc_seq, nbytes, name, r, got, stamp(r)))
+                               "%#x, expected %#x" % (seq, nbytes, name, r, got, stamp(r)))
     torch.cuda.synchronize(device)
     h.barrier()
     t[:8].zero_()
