@@ -15,6 +15,16 @@ maximum over ranks:
   value   inputs already resident on the device (kernel-only figure)
   e2e     TrainEngine.train_step fed from pinned host memory every step and the loss read
           back to the host every step (what a user of the API sees)
+
+Further keys of the line:
+  fused_check         (N > 1) every in-kernel collective the mesh uses, run on small problems on
+                      these ranks before the timed region and compared with NCCL / PyTorch
+                      (kharon_b200/parallel/selfcheck.py); a failure makes the exit code non-zero
+  at_reference_shape  the same engine and mesh with the shape the reference binary hard-codes
+                      (vocab 256, untied head, src/pp_train.c:77), for a like-for-like ratio
+  decode              paged-KV decode tok/s of the 24-layer d1024 model at G = 1 / 8 / 32 on one GPU
+                      (rank 0; BASELINE's second metric), KV bytes paged vs full-sequence
+Skip the extras with --no-extras.
 """
 from __future__ import annotations
 
@@ -108,6 +118,13 @@ def run_ours():
     fuse = "--no-fuse" not in sys.argv
     fused_comm = "--no-fused-comm" not in sys.argv     # in-kernel NVLink collectives (product path) vs NCCL baseline
     mesh = Mesh(tp, pp, dp) if world > 1 else Mesh.single()
+    extras = "--no-extras" not in sys.argv
+    fused_check = None
+    if world > 1 and fused_comm and device.type == "cuda" and extras:
+        import gc
+        from kharon_b200.parallel import selfcheck
+        fused_check = selfcheck.fused_check(mesh, device)
+        gc.collect()
     eng = TrainEngine(L, d, H, V, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                       init=arg("init", "device", str), fused_comm=fused_comm, pp_split=arg("pp-split", "auto", str))
     ntok = M * mb * S                                    # per replica and step
@@ -173,6 +190,42 @@ def run_ours():
         t = torch.tensor([final_loss if mesh.c.last else 0.0], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         final_loss = float(t.item())
+    # ---- extras: none of them touches the numbers above
+    ref_shape = decode = None
+    if extras and device.type == "cuda":
+        import gc
+        stage_layers = eng.stage_layers
+        fused_mb = bool(eng.fused_mb)
+        del eng
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            Kr = min(K, 10)
+            e2 = TrainEngine(L, d, H, 256, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
+                             init=arg("init", "device", str), fused_comm=fused_comm, untied_head=True,
+                             pp_split=arg("pp-split", "auto", str))
+            data.batch_into(host_idx[0], host_tgt[0], 256)
+            dev_idx.copy_(host_idx[0]); dev_tgt.copy_(host_tgt[0])
+            for _ in range(W):
+                e2.train_step(dev_idx, dev_tgt)
+            ms_r = timed(lambda i: e2.train_step(dev_idx, dev_tgt), Kr)
+            ops.check_device_status()
+            ref_shape = {"value": round(ntok * dp * Kr / (ms_r / 1e3), 1), "unit": "tok/s", "ms_per_step": round(ms_r / Kr, 3),
+                         "steps": Kr, "model": "GPT L%d d%d H%d V256 untied head" % (L, d, H),
+                         "layers_per_stage": e2.stage_layers}
+            del e2
+            gc.collect()
+            torch.cuda.empty_cache()
+        except Exception as ex:       # the headline numbers stand on their own
+            ref_shape = {"error": "%s: %s" % (type(ex).__name__, str(ex)[:200])}
+        if rank == 0:
+            try:
+                decode = decode_numbers(device)
+            except Exception as ex:
+                decode = {"error": "%s: %s" % (type(ex).__name__, str(ex)[:200])}
+        barrier()
+    else:
+        stage_layers, fused_mb = eng.stage_layers, bool(eng.fused_mb)
     if rank == 0:
         tokens = ntok * dp * K
         value = tokens / (ms_dev / 1e3)
@@ -194,19 +247,55 @@ def run_ours():
             "mfu_peak_tflops_per_gpu": round(peak / 1e12, 1),
             "config": {"model": "GPT L%d d%d H%d V%d tied" % (L, d, H, V), "global_batch": mb * M * dp, "seq_len": S,
                        "micro_batch": mb, "micro_batches": M, "parallelism": "tp%d pp%d dp%d(zero1)" % (tp, pp, dp),
-                       "microbatches_fused_on_single_stage": bool(eng.fused_mb), "fused_comm": fused_comm,
-                       "layers_per_stage": eng.stage_layers,
+                       "microbatches_fused_on_single_stage": fused_mb, "fused_comm": fused_comm,
+                       "layers_per_stage": stage_layers,
                        "l2": "inputs larger than L2 (step working set > 20 GB)", "loss_last_step": round(final_loss, 4)},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "ms_per_step": round(ms_e2e / K, 3),
                     "h2d_bytes_per_step": 2 * ntok * 4, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
         }
+        if fused_check is not None:
+            out["fused_check"] = fused_check
+        if ref_shape is not None:
+            out["at_reference_shape"] = ref_shape
+        if decode is not None:
+            out["decode"] = decode
         print(json.dumps(out), flush=True)
+    rc = 0
+    if fused_check is not None:
+        from kharon_b200.parallel import selfcheck
+        rc = 0 if selfcheck.passed(fused_check) else 3
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    return 0
+    return rc
+
+
+def decode_numbers(device):
+    """Paged-KV decode of BASELINE's inference configuration on one GPU: L24 d1024 H16 V50257, prompt
+    128, 256 new greedy tokens, block 16, G identical prompts through continuous batching
+    (bench/bench_infer.c:43-58 of the reference; tok/s = tokens_decoded / wall time, prefill included)."""
+    import torch
+    from kharon_b200.infer import InferEngine
+    from kharon_b200.models import GPT, Config
+    L, d, H, V, seq, plen, n_new, bs = 24, 1024, 16, 50257, 1024, 128, 256, 16
+    m = GPT(Config(L, d, H, V, seq, 1), device, torch.bfloat16)
+    m.init_weights_device(1234)
+    prompt = [(i * 131 + 7) % V for i in range(plen)]
+    max_lb = (seq + bs - 1) // bs
+    out = {}
+    for G in (1, 8, 32):
+        eng = InferEngine(m, bs, G * max_lb + 16, max(G, plen) + G * plen + 64, G + 1)
+        best = None
+        for _ in range(2):              # the first pass captures the CUDA graphs
+            _, st, ms = eng.generate([prompt] * G, n_new, max_active=G)
+            best = ms if best is None else min(best, ms)
+        out["G%d_tok_s" % G] = round(st["tokens_decoded"] * 1000.0 / best, 1)
+        out["kv_ratio"] = round(G * seq / (st["blocks_peak"] * bs), 2)
+        eng.close()
+    out["config"] = "L24 d1024 H16 V50257 prompt 128 new 256 block 16 bf16, 1 GPU, CUDA-graph decode steps, device sampler"
+    return out
 
 
 class Config_like:
@@ -215,8 +304,8 @@ class Config_like:
 
 
 def run_reference():
-    from baseline import reference_arm
-    return reference_arm.main(sys.argv[1:])
+    from baseline import reference_run
+    return reference_run.main(sys.argv[1:])
 
 
 if __name__ == "__main__":

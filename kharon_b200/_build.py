@@ -25,8 +25,13 @@ OBJ = LIB / "obj"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
 ]
+# --use_fast_math (approximate division / sqrt / tanh, flush-to-zero) only where exponentials and
+# tanh sit in a hot loop: GEMM epilogues (GELU), attention, the decode kernels.  The optimizer
+# (fp32 master weights, Adam moments), LayerNorm statistics, the loss and the ZeRO step are
+# compiled with IEEE division and square root; their softmax exponentials call __expf explicitly.
+FAST_MATH_FILES = {"gemm_tcgen05.cu", "gemm_skinny.cu", "flash_tcgen05.cu", "paged.cu", "fused_tp.cu"}
 
 
 def _newer(srcs, target: Path) -> bool:
@@ -81,7 +86,8 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
         obj = OBJ / (src.stem + ".o")
         objs.append(obj)
         if force or _newer([src] + headers, obj):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+            fast = ["--use_fast_math"] if src.name in FAST_MATH_FILES else []
+            cmd = [nvcc] + NVCC_FLAGS + fast + (["-Xptxas", "-v"] if verbose else []) + [
                 "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             jobs.append(cmd)
     if jobs:

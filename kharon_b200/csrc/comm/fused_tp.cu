@@ -71,6 +71,7 @@ struct CommParams {
   int n_copy;                  // gather mode: CTAs at the end of the grid that copy instead of multiplying
   uint32_t call_no;            // 1-based call number when the host counts
   uint32_t ready_target;
+  uint64_t wait_ns;            // limit of every wait in this kernel (all of them can be stalled by a peer)
   int* err;
 };
 
@@ -108,7 +109,8 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // bounded spin until *p has reached `target` (counters only grow; compare with wrap-around)
-__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, volatile int* abort_flag, int* err) {
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, volatile int* abort_flag, int* err,
+                                             uint64_t limit_ns) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
@@ -116,7 +118,7 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
       if (*abort_flag) return false;
       const uint64_t now = kh_globaltimer();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > KH_WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 5;
         atomicCAS(err, 0, 5);
         return false;
@@ -125,7 +127,8 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
     }
   }
 }
-__device__ __forceinline__ bool wait_smem_count(volatile int* p, int target, volatile int* abort_flag, int* err) {
+__device__ __forceinline__ bool wait_smem_count(volatile int* p, int target, volatile int* abort_flag, int* err,
+                                                uint64_t limit_ns) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (*p >= target) return true;
@@ -133,7 +136,7 @@ __device__ __forceinline__ bool wait_smem_count(volatile int* p, int target, vol
       if (*abort_flag) return false;
       const uint64_t now = kh_globaltimer();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > KH_WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 5;
         atomicCAS(err, 0, 5);
         return false;
@@ -219,7 +222,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
         // its block in 32 KB pieces with up to four bulk loads in flight, then publishes the block
         const int cid = worker - n_workers;
         for (int r = 0; r < p.tp && ok; r++)
-          if (r != p.rank && !wait_counter(p.ready[p.rank] + r, p.ready_target, abort_flag, p.err)) ok = false;
+          if (r != p.rank && !wait_counter(p.ready[p.rank] + r, p.ready_target, abort_flag, p.err, p.wait_ns)) ok = false;
         asm volatile("fence.proxy.async;" ::: "memory");     // the acquire above orders generic accesses; bulk copies are async-proxy
         const size_t blk_bytes = (size_t)BM * p.K * 2;
         const int pieces = (int)((blk_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
@@ -245,7 +248,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
               bulk_load_1d(smem_base + j * COPY_CHUNK, sbase + off, bytes, bar_full + 8 * j);
             }
             for (int j = 0; j < nb; j++) {
-              if (!mbar_wait(bar_full + 8 * j, uses[j] & 1, abort_flag, 6, p.err)) { ok = false; break; }
+              if (!mbar_wait(bar_full + 8 * j, uses[j] & 1, abort_flag, 6, p.err, p.wait_ns)) { ok = false; break; }
               uses[j]++;
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               const size_t off = (size_t)(q0 + j) * COPY_CHUNK;
@@ -276,7 +279,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
           } else {
             amap = &maps.g;
             if (ready_tm != tm) {      // the block's copier has delivered it (one increment per call)
-              if (!wait_counter(p.blk_ready + tm, call, abort_flag, p.err)) { ok = false; break; }
+              if (!wait_counter(p.blk_ready + tm, call, abort_flag, p.err, p.wait_ns)) { ok = false; break; }
               asm volatile("fence.proxy.async;" ::: "memory");
               ready_tm = tm;
             }
@@ -285,7 +288,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
         for (int kb = 0; kb < num_kb; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err, p.wait_ns)) { ok = false; break; }
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
           mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
           if (!p.a_mn) tma_load_2d(sa, amap, bar_full + 8 * s, kb * BK, row_in_src);
@@ -308,13 +311,13 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       for (int t = worker; !copier && ok && t < num_tiles; t += n_workers, tcount++) {
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
-        if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1, abort_flag, 4, p.err)) { ok = false; break; }
+        if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1, abort_flag, 4, p.err, p.wait_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, 1, p.err)) { ok = false; break; }
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, 1, p.err, p.wait_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
           const uint64_t adesc = umma_desc_sw128(sa, a_lbo, 1024), bdesc = umma_desc_sw128(sb, b_lbo, 1024);
@@ -349,7 +352,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       tile_coord(t, tm, tn);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err)) { ok = false; break; }
+      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err, p.wait_ns)) { ok = false; break; }
       tc_fence_after();
       const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
       const bool mine = owner < 0 || owner == p.rank;
@@ -420,11 +423,11 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
       int good = 1;
       if (lane == 0) {
-        good = wait_smem_count(s_pub, 4 * (tcount + 1), abort_flag, p.err) ? 1 : 0;
+        good = wait_smem_count(s_pub, 4 * (tcount + 1), abort_flag, p.err, p.wait_ns) ? 1 : 0;
         if (good && (owner < 0 || owner == p.rank)) {
           for (int pr = 0; pr < p.tp && good; pr++) {
             if (pr == p.rank) continue;
-            good = wait_counter(p.flags[p.rank] + (size_t)pr * num_tiles + t, target, abort_flag, p.err) ? 1 : 0;
+            good = wait_counter(p.flags[p.rank] + (size_t)pr * num_tiles + t, target, abort_flag, p.err, p.wait_ns) ? 1 : 0;
           }
         }
       }
@@ -541,6 +544,12 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   if (tp < 2 || tp > MAX_TP || rank < 0 || rank >= tp) { kh_set_error("gemm_comm: bad tp/rank %d/%d", rank, tp); return -1; }
   if ((mode == MODE_RS || gather) && M % (tp * BM)) { kh_set_error("gemm_comm: M=%d must be a multiple of tp*128 for row-sharded modes", M); return -1; }
   if (M < 1) { kh_set_error("gemm_comm: empty problem"); return -1; }
+  if (gather && mode != MODE_LOCAL) {
+    // the gather form rotates the tile order by rank, so tile index t names different tiles on different
+    // ranks and the per-tile arrival counters of a reduction would not line up
+    kh_set_error("gemm_comm: the all-gather form has no reduction (mode must be 2)");
+    return -1;
+  }
   if (N % 8 || ldo % 8 || ((uintptr_t)out & 15)) { kh_set_error("gemm_comm: N and the output pitch must be multiples of 8"); return -1; }
   if (gather && (a_mn || lda != K || !gather_buf || !blk_ready || !epoch_ptr)) {
     kh_set_error("gemm_comm: gather mode needs row-major contiguous shards (lda == K), a gather buffer, block counters and an epoch word");
@@ -595,6 +604,7 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   p.slot_elems = slot_elems;
   p.epoch = (uint32_t*)epoch_ptr;
   p.ready_target = gather_no;
+  p.wait_ns = kh_peer_wait_limit_ns();
   p.err = kh_error_word_dev();
   static bool attr = false;
   if (!attr) {

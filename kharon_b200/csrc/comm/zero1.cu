@@ -43,6 +43,7 @@ struct ZeroParams {
   float* w; float* m; float* v;   // local master (full arena), local moment shards
   float lr, b1, b2, eps, wd, bc1, bc2, inv_dp;
   uint32_t epoch;
+  uint64_t wait_ns;            // limit of the waits on the other ranks
   int* err;
 };
 
@@ -54,7 +55,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, int* err) {
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, int* err, uint64_t limit_ns) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
@@ -62,7 +63,7 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
       if (*(volatile int*)err) return false;
       const uint64_t now = kh_globaltimer();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > KH_WAIT_LIMIT_NS) { atomicCAS(err, 0, 5); return false; }
+      else if (now - t0 > limit_ns) { atomicCAS(err, 0, 5); return false; }
       __nanosleep(128);
     }
   }
@@ -81,7 +82,7 @@ zero1_step_kernel(const ZeroParams p) {
     }
     int ok = 1;
     for (int r = 0; r < p.dp && ok; r++)
-      if (r != p.rank) ok = wait_counter(p.ctr[p.rank] + r, p.epoch, p.err) ? 1 : 0;
+      if (r != p.rank) ok = wait_counter(p.ctr[p.rank] + r, p.epoch, p.err, p.wait_ns) ? 1 : 0;
     s_ok = ok;
   }
   __syncthreads();
@@ -124,7 +125,7 @@ zero1_step_kernel(const ZeroParams p) {
     for (int r = 0; r < p.dp; r++) red_release_sys_add(p.ctr[r] + p.dp + p.rank, 1);
     int ok = 1;
     for (int r = 0; r < p.dp && ok; r++)
-      ok = wait_counter(p.ctr[p.rank] + p.dp + r, p.epoch * gridDim.x, p.err) ? 1 : 0;
+      ok = wait_counter(p.ctr[p.rank] + p.dp + r, p.epoch * gridDim.x, p.err, p.wait_ns) ? 1 : 0;
     s_ok = ok;
   }
   __syncthreads();
@@ -157,6 +158,7 @@ extern "C" int kh_zero1_step(const unsigned long long* g_ptrs, const unsigned lo
   p.w = (float*)w; p.m = (float*)m; p.v = (float*)v;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.inv_dp = 1.f / dp;
   p.epoch = epoch;
+  p.wait_ns = kh_peer_wait_limit_ns();
   p.err = kh_error_word_dev();
   zero1_step_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   KH_LAUNCH_CHECK("zero1_step");

@@ -16,7 +16,15 @@ typedef __nv_bfloat16 bf16;
 // The word lives in one translation unit; kernels receive its device address as a parameter.
 int* kh_error_word_dev();   // host: device address of the error word of the current device
 
-#define KH_WAIT_LIMIT_NS 2000000000ull   // 2 s
+#define KH_WAIT_LIMIT_NS 2000000000ull   // 2 s: waits that only depend on this GPU
+// Waits that depend on another rank (peer flags, and every wait of a kernel whose pipeline a peer can
+// stall) take their limit as a kernel argument: ranks of a healthy job can be seconds apart (plan
+// recording in the first step, a checkpoint write or an evaluation on one rank).  Default 30 s,
+// changed with kh_set_peer_wait_limit_ms or the environment variable KHARON_PEER_WAIT_MS.  After a
+// wait on a peer has run out (error word 5) the counters of that buffer set no longer agree between
+// the ranks: the buffers must be rebuilt (new FusedTP / ZeroFused / Mailbox objects) before they are
+// used again.
+unsigned long long kh_peer_wait_limit_ns();   // host
 
 __device__ __forceinline__ uint64_t kh_globaltimer() {
   uint64_t t;
@@ -64,7 +72,8 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the wait ran out or another role of this CTA already
 // gave up (abort flag in shared memory); the caller then unwinds to the kernel's teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* err_word) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* err_word,
+                                          uint64_t limit_ns = KH_WAIT_LIMIT_NS) {
   if (mbar_try(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -73,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = kh_globaltimer();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > KH_WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = code;
         atomicCAS(err_word, 0, code);
         return false;

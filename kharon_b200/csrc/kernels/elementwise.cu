@@ -6,6 +6,8 @@
 // Reference counterparts (src/core/kernels.cu): embed_k :125, layernorm_fwd_k :145,
 // ce_fwd_k/ce_bwd_k :310-353, grpo_dlogits_k :358, gather_prob_k :372, layernorm_bwd_* :380-414,
 // colsum_k :511, embed_bwd_* :526-563, adamw_k :566, f2b_k :583; model_sync_bf16 gpt.c:377.
+#include <atomic>
+
 #include "common.cuh"
 
 static inline int cdiv(long a, long b) { return (int)((a + b - 1) / b); }
@@ -234,7 +236,7 @@ static __device__ __align__(256) float g_colsum_static_scratch[KH_COUNTER_SLOTS 
 // runtime, not a device address, so the address is looked up once per device with
 // cudaGetSymbolAddress (with that device current) and cached.
 extern "C" int kh_colsum_noalloc(const void* x, int ld, void* out, int rows, int N, int accumulate, void* stream) {
-  static float* dev_ptr[64] = {nullptr};
+  static std::atomic<float*> dev_ptr[64];     // zero-initialised; threads may race to fill an entry with the same value
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { kh_set_error("colsum_noalloc: no current device"); return -1; }
   if (rows <= 0 || N <= 0) { kh_set_error("colsum_noalloc: empty problem %d x %d", rows, N); return -1; }
@@ -245,13 +247,13 @@ extern "C" int kh_colsum_noalloc(const void* x, int ld, void* out, int rows, int
                  rows, N, (long)splits * N, KH_NOALLOC_PARTIAL_FLOATS);
     return -1;
   }
-  if (!dev_ptr[dev]) {   // first call on this device: resolve the array's device address
+  if (!dev_ptr[dev].load(std::memory_order_acquire)) {   // first call on this device: resolve the array's device address
     float* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_colsum_static_scratch);
     if (e != cudaSuccess || !ptr) { kh_set_error("colsum_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return -1; }
-    dev_ptr[dev] = ptr;
+    dev_ptr[dev].store(ptr, std::memory_order_release);
   }
-  float* scratch = dev_ptr[dev];
+  float* scratch = dev_ptr[dev].load(std::memory_order_acquire);
   cudaStream_t st = (cudaStream_t)stream;
   // the array keeps whatever the previous call left; the ticket counters must start at zero
   cudaError_t e = cudaMemsetAsync(scratch, 0, KH_COUNTER_SLOTS * sizeof(int), st);

@@ -20,10 +20,17 @@
 // (add_bias_k kernels.cu:174, bias_gelu_k :292, bias_residual_k :274, gelu_bwd_k :431,
 // add_k :262) and the beta=1 weight-gradient accumulation.
 //
+// Bias gradients: with `colsum` set (weight-gradient products, A = dY in M-major form) four more
+// warps add up the columns of the A tiles while they sit in shared memory and the CTAs that own
+// the first column of output tiles add the sums into colsum[M] -- the reference's separate
+// colsum_k pass over dY (kernels.cu:511-524) disappears.  A stage is handed back to the TMA
+// producer only after both the MMAs and these warps are done with it.
+//
 // Every mbarrier wait is bounded: on expiry the CTA stores a code in the library error word,
 // all roles unwind, TMEM is released and the kernel returns.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -46,6 +53,24 @@ int* kh_error_word_dev() {
 }
 
 // ------------------------------------------------------------------------------- host util
+static unsigned long long g_peer_wait_ns = 0;
+unsigned long long kh_peer_wait_limit_ns() {
+  if (g_peer_wait_ns == 0) {
+    unsigned long long ms = 30000;
+    if (const char* e = getenv("KHARON_PEER_WAIT_MS")) {
+      const long v = atol(e);
+      if (v > 0) ms = (unsigned long long)v;
+    }
+    g_peer_wait_ns = ms * 1000000ull;
+  }
+  return g_peer_wait_ns;
+}
+// Limit of every in-kernel wait on another rank, in milliseconds; returns the previous value.
+extern "C" long kh_set_peer_wait_limit_ms(long ms) {
+  const long old = (long)(kh_peer_wait_limit_ns() / 1000000ull);
+  if (ms > 0) g_peer_wait_ns = (unsigned long long)ms * 1000000ull;
+  return old;
+}
 static thread_local std::string g_host_err;
 void kh_set_error(const char* fmt, ...) {
   char buf[512];
@@ -160,11 +185,13 @@ struct GemmParams {
   const bf16* bias;        // [N]
   bf16* aux; int ldaux;    // EPI_BIAS_GELU: pre-activation out; EPI_BIAS_RESID/EPI_RESID: residual in; EPI_DGELU: pre-activation in
   float alpha;             // scales the accumulator before the epilogue
+  float* colsum;           // [M] fp32 or null: colsum[m] (+)= sum_k op(A)[m, k]  (needs a_mn; launch with CSUM_THREADS)
   int* err;                // library error word
 };
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int CSUM_THREADS = 320;          // + four column-sum warps
 
 // PAIR: two CTAs of a cluster form one 256 x BN tile (tcgen05 cta_group::2).  Each CTA stages its
 // own 128 rows of A and its own half of B, so a pair moves and re-reads 2/3 of the shared-memory
@@ -180,7 +207,7 @@ template <int BN, bool PAIR = false> struct GemmCfg {
 };
 
 template <int BN, bool PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(CSUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
   using Cfg = GemmCfg<BN, PAIR>;
   constexpr int TM = PAIR ? 2 * BM : BM;                       // rows of one scheduled tile
@@ -191,13 +218,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + Cfg::STAGES * Cfg::STAGE_BYTES);
-  // bars: full[STAGES], empty[STAGES], tfull[2], tempty[2], then tmem base word + abort flag
+  // bars: full[STAGES], empty[STAGES], tfull[2], tempty[2], free[STAGES], then tmem base word + abort flag
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * Cfg::STAGES;
   const uint32_t bar_tfull = bar_empty + 8 * Cfg::STAGES;
   const uint32_t bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 4);
+  const uint32_t bar_free = bar_tempty + 16;         // column-sum warps are done with the stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * Cfg::STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const bool csum = p.colsum != nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + TM - 1) / TM, tiles_n = (p.N + BN - 1) / BN;
@@ -205,7 +234,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int s = 0; s < Cfg::STAGES; s++) {
+      mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); mbar_init(bar_free + 8 * s, 4);
+    }
     // accumulator-free barrier: one arrival per epilogue warp of every CTA that reads the accumulator
     for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, PAIR ? 8 : 4); }
     *abort_flag = 0;
@@ -247,6 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
+          if (csum && !mbar_wait(bar_free + 8 * s, ph ^ 1, abort_flag, 2, p.err)) { ok = false; break; }
           const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
           if (!PAIR) {
             mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
@@ -305,6 +337,64 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           if (PAIR) umma_commit_pair(bar_empty + 8 * s, 3); else umma_commit(bar_empty + 8 * s);
         }
         if (ok) { if (PAIR) umma_commit_pair(bar_tfull + 8 * acc, 3); else umma_commit(bar_tfull + 8 * acc); }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ column sums of A (bias gradient)
+    // Present only in launches with CSUM_THREADS.  A stage is read after the MMAs that consume it
+    // have retired (its "empty" barrier, which also reaches the second CTA of a pair) and before the
+    // producer may refill it (the "free" barrier).  Warp cw owns columns [32 cw, 32 cw + 32) of the
+    // 128-column A tile: four 16-byte chunks of one 64-column slab.  Lane = 8 p + 4 h + c4 reads
+    // chunk c4 of rows 8 i + p + 4 h (i = 0..7): the two rows of a quarter-warp differ in bit 2, so
+    // the 128-byte swizzle puts them in different bank halves.  The warp needs no other warp's
+    // data, so there is no barrier between the four.
+    const int cw = warp - 6;
+    const int c4 = lane & 3, rsel = ((lane >> 3) & 3) + 4 * ((lane >> 2) & 1);
+    const uint32_t slab_off = (uint32_t)(cw >> 1) * (BK * 128);
+    const int chunk = (cw & 1) * 4 + c4;
+    int it = 0;
+    bool ok = true;
+    for (int t = worker; ok && t < num_tiles; t += n_workers) {
+      int tm, tn;
+      tile_coord(t, tm, tn);
+      const bool mine = (tn == 0);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] = 0.f;
+      for (int kb = 0; kb < num_kb; kb++, it++) {
+        const int s = it % Cfg::STAGES;
+        const uint32_t ph = (it / Cfg::STAGES) & 1;
+        if (!mbar_wait(bar_empty + 8 * s, ph, abort_flag, 2, p.err)) { ok = false; break; }
+        if (mine) {
+          const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES + slab_off;
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int r = 8 * i + rsel;
+            uint4 v;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(sa + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4)));
+            float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+            acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+            acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_free + 8 * s);
+      }
+      if (ok && mine) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 4);
+          acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 8);
+          acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 16);
+        }
+        if (lane < 4) {
+          const int m0 = tm * TM + (int)crank * BM + cw * 32 + c4 * 8;
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            if (m0 + j < p.M) p.colsum[m0 + j] = p.accumulate ? p.colsum[m0 + j] + acc[j] : acc[j];
+        }
       }
     }
   } else {
@@ -488,7 +578,7 @@ static int launch_gemm_pair(const CUtensorMap* ta, const CUtensorMap* tb, const 
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.blockDim = dim3(p.colsum ? CSUM_THREADS : GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
   if (g_pair_clusters < 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) { kh_set_error("gemm: cannot opt in to %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e)); return -1; }
@@ -521,7 +611,7 @@ static int launch_gemm(const CUtensorMap* ta, const CUtensorMap* tb, const GemmP
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_kernel<BN, false><<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(*ta, *tb, p);
+  gemm_kernel<BN, false><<<grid, p.colsum ? CSUM_THREADS : GEMM_THREADS, Cfg::SMEM, st>>>(*ta, *tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kh_set_error("gemm launch failed: %s", cudaGetErrorString(e)); return -1; }
   return 0;
@@ -531,10 +621,16 @@ static int launch_gemm(const CUtensorMap* ta, const CUtensorMap* tb, const GemmP
 // elements of the row-major buffers described at the top of this file.  block_n = 0 lets the
 // launcher pick the tile width; max_ctas > 0 caps the grid (used to leave SMs to a
 // concurrently running communication kernel).  Returns 0 or -1 (see kh_cuda_last_error).
-extern "C" int kh_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
-                            int M, int N, int K, int out_fp32, int accumulate, int epi, const void* bias, void* aux,
-                            int ldaux, float alpha, int block_n, int max_ctas, void* stream) {
+//
+// kh_gemm_bf16_colsum: same product with `colsum` [M] fp32 receiving colsum[m] (+)= sum_k op(A)[m, k]
+// (`+=` when `accumulate`), computed from the A tiles in shared memory by four extra warps.  A must
+// be in M-major form (a_mn), i.e. the call is a weight-gradient product dW = dY^T X and `colsum`
+// is the bias gradient.
+extern "C" int kh_gemm_bf16_colsum(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
+                                   int M, int N, int K, int out_fp32, int accumulate, int epi, const void* bias, void* aux,
+                                   int ldaux, float alpha, int block_n, int max_ctas, void* colsum, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) { kh_set_error("gemm: empty problem %dx%dx%d", M, N, K); return -1; }
+  if (colsum && !a_mn) { kh_set_error("gemm: column sums need the A operand in M-major form"); return -1; }
   if (accumulate && !out_fp32) { kh_set_error("gemm: accumulate needs an fp32 output"); return -1; }
   if ((ldc % (out_fp32 ? 4 : 8)) != 0 || ((uintptr_t)C & 15)) { kh_set_error("gemm: output pitch/base not 16-byte aligned (ldc %d)", ldc); return -1; }
   if ((epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_BIAS_RESID) && (!bias || ((uintptr_t)bias & 15))) { kh_set_error("gemm: bias missing or misaligned"); return -1; }
@@ -570,10 +666,18 @@ extern "C" int kh_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
   p.accumulate = accumulate; p.epi = epi; p.bias = (const bf16*)bias; p.aux = (bf16*)aux; p.ldaux = ldaux; p.alpha = alpha;
+  p.colsum = (float*)colsum;
   p.err = kh_error_word_dev();
   cudaStream_t st = (cudaStream_t)stream;
   if (pair) return launch_gemm_pair(ta, tb, p, max_ctas, st);
   if (bn == 256) return launch_gemm<256>(ta, tb, p, max_ctas, st);
   if (bn == 128) return launch_gemm<128>(ta, tb, p, max_ctas, st);
   return launch_gemm<64>(ta, tb, p, max_ctas, st);
+}
+
+extern "C" int kh_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
+                            int M, int N, int K, int out_fp32, int accumulate, int epi, const void* bias, void* aux,
+                            int ldaux, float alpha, int block_n, int max_ctas, void* stream) {
+  return kh_gemm_bf16_colsum(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, out_fp32, accumulate, epi, bias, aux, ldaux,
+                             alpha, block_n, max_ctas, nullptr, stream);
 }

@@ -90,6 +90,9 @@ class TrainEngine:
                  defer_dw=None, eager_p2p=None):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
+        # The in-kernel collectives move bf16 activations / weights; an fp32 model (the oracle
+        # configuration) takes the NCCL path, which also gathers fp32 parameters under ZeRO-1.
+        fused_comm = bool(fused_comm and dtype == torch.bfloat16)
         self.tracer = Tracer(enabled=bool(trace))     # per-phase CUDA-event timeline (forward / backward / p2p / optimizer)
         self.heartbeat = heartbeat                     # utils.watchdog.Heartbeat: peers are checked before every step
         c = self.mesh.c
@@ -168,7 +171,8 @@ class TrainEngine:
             if self.zero_fused:
                 self.zero_fused.finalize()
         self.plans = {}
-        self.use_plans = self.device.type == "cuda"
+        # launch plans replay native calls only; the fp32 oracle path also runs PyTorch operators
+        self.use_plans = self.device.type == "cuda" and dtype == torch.bfloat16
         # host -> device input staging (see _upload)
         self._par = 0
         if self.device.type == "cuda":

@@ -86,7 +86,7 @@ class InferEngine:
         self.temperature, self.seed, self.step_no = 0.0, 0, 0
         # under TP the captured step contains the fused GEMM + all-reduce kernels (their call counter
         # is a device word); the NCCL seam is left to eager launches
-        self.use_graphs = bool(use_graphs and self.dev.type == "cuda"
+        self.use_graphs = bool(use_graphs and self.dev.type == "cuda" and self.dt == torch.bfloat16
                                and (self.tp == 1 or getattr(model, "fused_tp", None) is not None))
         self.graphs = {}
         self._warm = set()

@@ -8,9 +8,10 @@ stage :665-772) but every elementwise step is folded into a GEMM epilogue or a f
 
   forward / layer   LN -> GEMM(+bias) -> flash attention -> GEMM(+bias+residual)
                     -> LN -> GEMM(+bias, GELU) -> GEMM(+bias+residual)
-  backward / layer  colsum, GEMM(dW+=), GEMM(dX * gelu'), colsum, GEMM(dW+=), GEMM(dX),
-                    LN-bwd(+residual grad), colsum, GEMM(dW+=), GEMM(dX), flash-bwd, colsum,
-                    GEMM(dW+=), GEMM(dX), LN-bwd(+residual grad)
+  backward / layer  GEMM(dW+=, db+=), GEMM(dX * gelu'), GEMM(dW+=, db+=), GEMM(dX),
+                    LN-bwd(+residual grad), GEMM(dW+=, db+=), GEMM(dX), flash-bwd,
+                    GEMM(dW+=, db+=), GEMM(dX), LN-bwd(+residual grad)
+                    (bias gradients are column sums taken inside the weight-gradient products)
 
 The same code runs in three modes: bf16 on a B200 (native kernels), bf16 on CPU (emulated,
 for the CPU test tier) and fp32 on CPU (the numerical oracle).
@@ -140,10 +141,6 @@ class GPT:
         self.s_delta = torch.empty(cfg.batch, cfg.n_head // tp, cfg.seq, dtype=torch.float32, device=self.device)
         self.s_lnpart = torch.zeros(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
                                     dtype=torch.float32, device=self.device)
-        cuda = self.device.type == "cuda"
-        Rc = R * (n_slots if defer_dw else 1)
-        ncs = max(ops.colsum_scratch_elems(Rc, n) for n in (d, fo, 3 * dl)) if cuda else 1
-        self.s_colsum = torch.zeros(ncs, dtype=torch.float32, device=self.device)
         self.s_table = torch.empty(2 * cfg.vocab, dtype=torch.int32, device=self.device)
         self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.tp_allreduce = None      # callable(tensor) summing in place over the TP group
@@ -423,22 +420,18 @@ class GPT:
         for l in reversed(range(cfg.n_layer)):
             a = s.layers[l]
             # x[l+1] = xmid + act @ Wfp^T + b
-            ops.colsum(dx, self.G(l, "fcproj_b"), scratch=self.s_colsum)
-            ops.gemm(dx, a["act"], self.G(l, "fcproj_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(dx, a["act"], self.G(l, "fcproj_w"), a_mn=True, b_mn=True, accumulate=True, colsum=self.G(l, "fcproj_b"))
             ops.gemm(dx, self.L(l, "fcproj_w"), self.s_dpre, b_mn=True, epi=ops.EPI_DGELU, aux=a["pre"])
-            ops.colsum(self.s_dpre, self.G(l, "fc_b"), scratch=self.s_colsum)
-            ops.gemm(self.s_dpre, a["ln2"], self.G(l, "fc_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(self.s_dpre, a["ln2"], self.G(l, "fc_w"), a_mn=True, b_mn=True, accumulate=True, colsum=self.G(l, "fc_b"))
             self._row_parallel(self.s_dpre, self.L(l, "fc_w"), self.s_dln, b_mn=True)
             ops.layernorm_bwd(self.s_dln, a["xmid"], self.L(l, "ln2_w"), a["mean2"], a["rstd2"], dx, other,
                               self.G(l, "ln2_w"), self.G(l, "ln2_b"), self.s_lnpart)
             dx, other = other, dx
             # xmid = x + att @ Wp^T + b
-            ops.colsum(dx, self.G(l, "proj_b"), scratch=self.s_colsum)
-            ops.gemm(dx, a["att"], self.G(l, "proj_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(dx, a["att"], self.G(l, "proj_w"), a_mn=True, b_mn=True, accumulate=True, colsum=self.G(l, "proj_b"))
             ops.gemm(dx, self.L(l, "proj_w"), self.s_datt, b_mn=True)
             ops.flash_bwd(a["qkv"], a["att"], self.s_datt, a["lse"], self.s_dqkv, self.s_delta, B, T, Hl, hd)
-            ops.colsum(self.s_dqkv, self.G(l, "qkv_b"), scratch=self.s_colsum)
-            ops.gemm(self.s_dqkv, a["ln1"], self.G(l, "qkv_w"), a_mn=True, b_mn=True, accumulate=True)
+            ops.gemm(self.s_dqkv, a["ln1"], self.G(l, "qkv_w"), a_mn=True, b_mn=True, accumulate=True, colsum=self.G(l, "qkv_b"))
             self._row_parallel(self.s_dqkv, self.L(l, "qkv_w"), self.s_dln, b_mn=True)
             ops.layernorm_bwd(self.s_dln, s.x[l], self.L(l, "ln1_w"), a["mean1"], a["rstd1"], dx, other,
                               self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
@@ -461,8 +454,8 @@ class GPT:
         for l in reversed(range(self.cfg.n_layer)):
             for dy, x, name in pairs:
                 dyr, xr = g.rows(l, dy, lo, hi), g.rows(l, x, lo, hi)
-                ops.colsum(dyr, self.G(l, name + "_b"), scratch=self.s_colsum)
-                ops.gemm(dyr, xr, self.G(l, name + "_w"), a_mn=True, b_mn=True, accumulate=True)
+                ops.gemm(dyr, xr, self.G(l, name + "_w"), a_mn=True, b_mn=True, accumulate=True,
+                         colsum=self.G(l, name + "_b"))
 
     def gather_prob(self, slot=0):
         """p(target) per row from the logits of the last forward (src/core/kernels.cu:372-378)."""

@@ -106,6 +106,13 @@ def _p(t):
     return 0 if t is None else t.data_ptr()
 
 
+def _use_reference(t):
+    """CPU tensors and fp32 activations on a GPU take the PyTorch fp32 evaluation of the operator
+    (``reference.py``; its matrix products run on the native fp32 kernel on a GPU).  fp32 storage is
+    the oracle configuration of the reference (src/core/gpt.c:332-371), not a throughput path."""
+    return (not t.is_cuda) or t.dtype == torch.float32
+
+
 def error_word(reset: bool = True) -> int:
     """Device-side status word: 0, or the code of the first bounded wait that ran out."""
     return int(_lib().kh_cuda_error_word(1 if reset else 0))
@@ -118,14 +125,30 @@ def check_device_status():
 
 
 # ----------------------------------------------------------------------------------- GEMM
+def _matmul_f32(A, B):
+    """A @ B for fp32 CUDA tensors (any strides) on the native CUDA-core kernel (csrc/kernels/gemm_f32.cu)."""
+    M, K = A.shape
+    N = B.shape[1]
+    out = torch.empty(M, N, dtype=torch.float32, device=A.device)
+    _call(_lib().kh_gemm_f32, 1, A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
+          out.data_ptr(), N, M, N, K, _stream())
+    return out
+
+
+ref.matmul_f32 = _matmul_f32
+
+
 def gemm(a, b, out, *, a_mn=False, b_mn=False, accumulate=False, epi=EPI_NONE, bias=None, aux=None,
-         alpha=1.0, block_n=0, max_ctas=0):
+         alpha=1.0, block_n=0, max_ctas=0, colsum=None):
     """out[M,N] (+)= alpha * op(a) @ op(b) with a fused epilogue.
 
     ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``); both
     bf16, row-major, last dim contiguous.  ``out`` is bf16 or fp32 (``accumulate`` only fp32).
     Epilogues: bias add; bias+GELU (``aux`` receives the pre-activation); bias+residual and
     residual (``aux`` is the residual); dGELU (``out = acc * gelu'(aux)``).
+    ``colsum`` (fp32 [M], needs ``a_mn``): also receives the column sums of ``a`` -- the bias gradient
+    of a weight-gradient product dW = dY^T X -- added to its content when ``accumulate``, formed from
+    the operand tiles the kernel already holds in shared memory.
     """
     if a_mn:
         K, M = a.shape
@@ -134,14 +157,17 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, accumulate=False, epi=EPI_NONE, b
     N = b.shape[1] if b_mn else b.shape[0]
     assert (b.shape[0] if b_mn else b.shape[1]) == K, "gemm: inner dimensions differ"
     assert out.shape[0] == M and out.shape[1] == N
-    if not a.is_cuda:
+    assert colsum is None or a_mn, "gemm: column sums need the M-major A of a weight-gradient product"
+    if _use_reference(a):
+        if colsum is not None:
+            ref.colsum(a, colsum, accumulate)
         return ref.gemm(a, b, out, a_mn, b_mn, accumulate, epi, bias, aux, alpha)
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
-    _call(_lib().kh_gemm_bf16, 1, a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+    _call(_lib().kh_gemm_bf16_colsum, 1, a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                              out.data_ptr(), out.stride(0), M, N, K, int(out.dtype == torch.float32),
                              int(accumulate), epi, _p(bias), _p(aux), aux.stride(0) if aux is not None else 0,
-                             float(alpha), block_n, max_ctas, _stream())
+                             float(alpha), block_n, max_ctas, _p(colsum), _stream())
     return out
 
 
@@ -161,7 +187,7 @@ def gemm_skinny(x, w, out, scratch, *, epi=EPI_NONE, bias=None, aux=None, ln_w=N
     taken of LayerNorm(x) * ln_w + ln_b, normalised inside the kernel."""
     M, K = x.shape
     N = w.shape[0]
-    if not x.is_cuda:
+    if _use_reference(x):
         if ln_w is not None:
             y = torch.empty_like(x)
             ref.layernorm_fwd(x, ln_w, ln_b, y, None, None)
@@ -175,7 +201,7 @@ def gemm_skinny(x, w, out, scratch, *, epi=EPI_NONE, bias=None, aux=None, ln_w=N
 
 # ------------------------------------------------------------------------------ embedding
 def embed_fwd(tok, pos, wte, wpe, out, T):
-    if not out.is_cuda:
+    if _use_reference(out):
         return ref.embed_fwd(tok, pos, wte, wpe, out, T)
     rows, d = out.shape
     _call(_lib().kh_embed_fwd, 1, tok.data_ptr(), _p(pos), wte.data_ptr(), wpe.data_ptr(), out.data_ptr(), rows, d,
@@ -200,7 +226,7 @@ def _scratch_buf(device, nbytes, tag="colsum"):
 def embed_bwd(tok, dx, dwte, dwpe, B, T, table=None):
     """dwte[tok[r]] += dx[r]; dwpe[t] += sum_b dx[b, t] (fp32 grads, deterministic).  ``table`` is
     int32 scratch of 2 * vocab entries."""
-    if not dx.is_cuda:
+    if _use_reference(dx):
         return ref.embed_bwd(tok, dx, dwte, dwpe, B, T)
     d = dx.shape[1]
     V = dwte.shape[0] if dwte is not None else 0
@@ -216,7 +242,7 @@ def colsum_scratch_elems(rows, N):
 def colsum(x, out, accumulate=True, scratch=None):
     """out[j] (+)= sum_r x[r, j]; ``scratch`` (colsum_scratch_elems fp32, zero-initialised once and
     left zeroed by every call) holds ticket counters and partial rows."""
-    if not x.is_cuda:
+    if _use_reference(x):
         return ref.colsum(x, out, accumulate)
     rows, N = x.shape
     if scratch is None:
@@ -227,7 +253,7 @@ def colsum(x, out, accumulate=True, scratch=None):
 
 # ------------------------------------------------------------------------------ LayerNorm
 def layernorm_fwd(x, w, b, y, mean=None, rstd=None):
-    if not x.is_cuda:
+    if _use_reference(x):
         return ref.layernorm_fwd(x, w, b, y, mean, rstd)
     rows, d = x.shape
     _call(_lib().kh_layernorm_fwd, 1, x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), _p(mean), _p(rstd), rows, d,
@@ -245,7 +271,7 @@ def layernorm_bwd_scratch_elems(rows, d):
 
 def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
     """dx = LN'(dy) (+ dres); dw += ..., db += ... (fp32, deterministic two-stage reduction)."""
-    if not x.is_cuda:
+    if _use_reference(x):
         return ref.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db)
     rows, d = x.shape
     assert partials.numel() >= layernorm_bwd_scratch_elems(rows, d)
@@ -258,7 +284,7 @@ def layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw, db, partials):
 def xent(logits, V, target, *, coef=None, uniform=1.0, rowloss=None, prob=None, write_grad=True):
     """Fused softmax-cross-entropy over bf16 logits [R, ld]; optionally overwrites the logits
     with ``scale_r * (softmax - onehot)`` (scale_r = coef[r] or ``uniform``)."""
-    if not logits.is_cuda:
+    if _use_reference(logits):
         return ref.xent(logits, V, target, coef, uniform, rowloss, prob, write_grad)
     _call(_lib().kh_xent, 1, logits.data_ptr(), logits.stride(0), V, target.data_ptr(), _p(coef), float(uniform),
                         _p(rowloss), _p(prob), int(write_grad), logits.shape[0], _stream())
@@ -267,7 +293,7 @@ def xent(logits, V, target, *, coef=None, uniform=1.0, rowloss=None, prob=None, 
 def xent_stats(logits, V, target, v0, stats):
     """Vocabulary-parallel cross-entropy, stage 1: per row (max, sum exp(x - max), target logit or -inf)
     over this rank's vocabulary slice [v0, v0 + V); ``stats`` is fp32 [R, 3]."""
-    if not logits.is_cuda:
+    if _use_reference(logits):
         return ref.xent_stats(logits, V, target, v0, stats)
     _call(_lib().kh_xent_stats, 1, logits.data_ptr(), logits.stride(0), V, target.data_ptr(), int(v0), stats.data_ptr(),
           logits.shape[0], _stream())
@@ -276,7 +302,7 @@ def xent_stats(logits, V, target, v0, stats):
 def xent_grad(logits, V, target, v0, gmax, gsum, *, coef=None, uniform=1.0):
     """Stage 2: overwrite the local logits with ``scale_r * (exp(x - gmax) / gsum - onehot)`` given the
     statistics combined over all vocabulary slices."""
-    if not logits.is_cuda:
+    if _use_reference(logits):
         return ref.xent_grad(logits, V, target, v0, gmax, gsum, coef, uniform)
     _call(_lib().kh_xent_grad, 1, logits.data_ptr(), logits.stride(0), V, target.data_ptr(), int(v0), gmax.data_ptr(),
           gsum.data_ptr(), _p(coef), float(uniform), logits.shape[0], _stream())
@@ -303,14 +329,14 @@ def adamw(p, g, m, v, pb, *, lr, beta1, beta2, eps, wd, step, grad_scale=1.0, ze
 
 
 def cast_f32_bf16(x, y):
-    if not x.is_cuda:
+    if not x.is_cuda or y.dtype == torch.float32:
         y.copy_(x)
         return
     _call(_lib().kh_cast_f32_bf16, 1, x.data_ptr(), y.data_ptr(), x.numel(), _stream())
 
 
 def add_bf16(a, b, c):
-    if not a.is_cuda:
+    if _use_reference(a):
         c.copy_((a.float() + b.float()))
         return
     _call(_lib().kh_add_bf16, 1, a.data_ptr(), b.data_ptr(), c.data_ptr(), a.numel(), _stream())
@@ -352,7 +378,7 @@ def _pad_out(src, dst, parts, H, hd, hp):
 def flash_fwd(qkv, out, lse, B, T, H, hd):
     """Causal attention over the fused projection ``qkv`` [B*T, 3*H*hd] (q | k | v blocks,
     head-major inside each); writes ``out`` [B*T, H*hd] and ``lse`` [B, H, T] (fp32)."""
-    if not qkv.is_cuda:
+    if _use_reference(qkv):
         return ref.flash_fwd(qkv, out, lse, B, T, H, hd)
     scale = 1.0 / math.sqrt(hd)
     if hd not in (64, 128):
@@ -370,7 +396,7 @@ def flash_fwd(qkv, out, lse, B, T, H, hd):
 def flash_bwd(qkv, out, dout, lse, dqkv, delta, B, T, H, hd):
     """Gradient of ``flash_fwd`` w.r.t. the fused projection: fills ``dqkv`` [B*T, 3*H*hd].
     ``delta`` [B, H, T] fp32 is scratch for rowsum(dO * O)."""
-    if not qkv.is_cuda:
+    if _use_reference(qkv):
         return ref.flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd)
     scale = 1.0 / math.sqrt(hd)
     if hd not in (64, 128):
@@ -422,7 +448,7 @@ def p2p_wait(flag_ptr: int, expected, limit_ms: int):
 # ------------------------------------------------------------------------------ paged KV
 def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
     """Scatter k, v of each new token into its block: pool layout [n_blocks, bs, H, hd]."""
-    if not qkv.is_cuda:
+    if _use_reference(qkv):
         return ref.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
     _call(_lib().kh_append_kv, 1, qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(),
                              slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd, ntok, _stream())
@@ -433,7 +459,7 @@ def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx, appe
     through the block table.  ``append``: the kernel itself stores each token's k, v into the cache
     first (valid when no two listed tokens belong to one sequence, i.e. decode steps); otherwise
     ``append_kv`` must have run."""
-    if not qkv.is_cuda:
+    if _use_reference(qkv):
         if append:
             ref.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
         return ref.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok)
@@ -443,7 +469,7 @@ def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx, appe
 
 
 def gather_rows(x, rows, out, nseq):
-    if not x.is_cuda:
+    if _use_reference(x):
         out[:nseq].copy_(x[rows[:nseq].long()])
         return
     _call(_lib().kh_gather_rows, 1, x.data_ptr(), rows.data_ptr(), out.data_ptr(), nseq, x.shape[1], _stream())
@@ -453,7 +479,7 @@ def copy_blocks(kc, vc, pairs, npairs):
     """kc, vc: [n_layer, n_blocks, bs, H, hd]; copies block pairs[2i] -> pairs[2i+1] in all layers."""
     if npairs == 0:
         return
-    if not kc.is_cuda:
+    if _use_reference(kc):
         for i in range(npairs):
             s, d = int(pairs[2 * i]), int(pairs[2 * i + 1])
             kc[:, d].copy_(kc[:, s])
@@ -465,7 +491,7 @@ def copy_blocks(kc, vc, pairs, npairs):
 
 def sample(logits, V, temperature, seed, step, rep, out, nseq):
     """Greedy argmax (temperature <= 0) or a categorical draw from softmax(logits / T), on device."""
-    if not logits.is_cuda:
+    if _use_reference(logits):
         return ref.sample(logits, V, temperature, seed, step, rep, out, nseq)
     _call(_lib().kh_sample, 1, logits.data_ptr(), logits.stride(0), V, float(temperature), int(seed), int(step), rep,
                           out.data_ptr(), nseq, _stream())

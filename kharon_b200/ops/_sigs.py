@@ -16,6 +16,8 @@ def declare(lib):
     _sig(lib, "kh_cuda_error_word", i32, i32)
     _sig(lib, "kh_gemm_bf16", i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp,
          i32, f32, i32, i32, vp)
+    _sig(lib, "kh_gemm_bf16_colsum", i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp,
+         i32, f32, i32, i32, vp, vp)
     _sig(lib, "kh_embed_fwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
     _sig(lib, "kh_embed_bwd", i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp)
     _sig(lib, "kh_colsum", i32, vp, i32, vp, vp, i32, i32, i32, vp)
@@ -36,6 +38,7 @@ def declare(lib):
 
 # entry points that live in translation units added after the first ones; declared when present
 _OPTIONAL = {
+    "kh_gemm_f32": (i32, vp, long_, long_, vp, long_, long_, vp, long_, i32, i32, i32, vp),
     "kh_xent_stats": (i32, vp, i32, i32, vp, i32, vp, i32, vp),
     "kh_xent_grad": (i32, vp, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp),
     "kh_wait_probe": (i32, vp, u32, u32, vp, vp),

@@ -27,10 +27,21 @@ def gelu_grad(x):
     return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * _K * (1.0 + 3.0 * _C * x * x)
 
 
+#: fp32 matrix product used by ``gemm``; the operator layer installs the native CUDA-core kernel
+#: for GPU tensors (see ``ops._matmul_f32``), CPU tensors use torch.
+matmul_f32 = None
+
+
+def _mm(A, B):
+    if matmul_f32 is not None and A.is_cuda:
+        return matmul_f32(A, B)
+    return A @ B
+
+
 def gemm(a, b, out, a_mn, b_mn, accumulate, epi, bias, aux, alpha):
     A = a.float().t() if a_mn else a.float()
     Bm = b.float() if b_mn else b.float().t()
-    acc = (A @ Bm) * alpha
+    acc = _mm(A, Bm) * alpha
     if epi in (EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESID):
         acc = acc + bias.float()
     if epi == EPI_BIAS_GELU:
@@ -194,25 +205,24 @@ def flash_bwd(qkv, out, dout, lse, dqkv, B, T, H, hd):
 
 def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
     d = H * hd
-    for t in range(ntok):
-        p = int(pos[t])
-        blk = int(btab[int(slot[t]), p // bs])
-        kc[blk, p % bs] = qkv[t, d:2 * d].view(H, hd)
-        vc[blk, p % bs] = qkv[t, 2 * d:3 * d].view(H, hd)
+    p = pos[:ntok].long()
+    blk = btab[slot[:ntok].long(), p // bs].long()
+    kc[blk, p % bs] = qkv[:ntok, d:2 * d].reshape(ntok, H, hd).to(kc.dtype)
+    vc[blk, p % bs] = qkv[:ntok, 2 * d:3 * d].reshape(ntok, H, hd).to(vc.dtype)
 
 
 def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok):
     d = H * hd
-    for t in range(ntok):
-        ctx = int(pos[t]) + 1
-        bt = btab[int(slot[t])].long()
-        nb = (ctx + bs - 1) // bs
-        K = kc[bt[:nb]].reshape(nb * bs, H, hd)[:ctx].float()
-        Vv = vc[bt[:nb]].reshape(nb * bs, H, hd)[:ctx].float()
-        q = qkv[t, :d].float().view(H, hd)
-        s = torch.einsum("he,jhe->hj", q, K) / math.sqrt(hd)
-        p = torch.softmax(s, -1)
-        out[t] = torch.einsum("hj,jhe->he", p, Vv).reshape(d).to(out.dtype)
+    p = pos[:ntok].long()
+    ctx = int(p.max()) + 1
+    j = torch.arange(ctx, device=qkv.device)
+    blk = btab[slot[:ntok].long()][:, j // bs].long().clamp_(min=0)          # [ntok, ctx]
+    K = kc[blk, (j % bs)[None, :]].float()                                   # [ntok, ctx, H, hd]
+    Vv = vc[blk, (j % bs)[None, :]].float()
+    q = qkv[:ntok, :d].float().reshape(ntok, H, hd)
+    s = torch.einsum("the,tjhe->thj", q, K) / math.sqrt(hd)
+    s = s.masked_fill((j[None, :] > p[:, None])[:, None, :], float("-inf"))
+    out[:ntok] = torch.einsum("thj,tjhe->the", torch.softmax(s, -1), Vv).reshape(ntok, d).to(out.dtype)
 
 
 def sample(logits, V, temperature, seed, step, rep, out, nseq):
@@ -222,6 +232,6 @@ def sample(logits, V, temperature, seed, step, rep, out, nseq):
         out[:nseq * rep].copy_(idx.repeat_interleave(rep).to(out.dtype))
         return
     g = torch.Generator().manual_seed((int(seed) * 1000003 + int(step)) & 0x7FFFFFFF)
-    p = torch.softmax(lg / temperature, -1)
-    idx = torch.multinomial(p, rep, replacement=True, generator=g)
+    p = torch.softmax(lg / temperature, -1).cpu()
+    idx = torch.multinomial(p, rep, replacement=True, generator=g).to(out.device)
     out[:nseq * rep].copy_(idx.reshape(-1).to(out.dtype))

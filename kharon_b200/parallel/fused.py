@@ -3,9 +3,10 @@
 ``FusedTP`` owns the symmetric (peer-mapped) staging buffers and arrival counters that the
 ``kh_gemm_comm`` kernel needs and exposes
 
-* ``gemm_ar``  partial GEMM on every rank, summed across the TP group inside the kernel
-               (GEMM -> reduce-scatter -> all-gather over NVLink P2P stores), bias / residual
-               added in the reduction;
+* ``gemm_ar``  partial GEMM on every rank, summed across the TP group inside the kernel: every rank
+               pushes each partial tile to every peer and reduces every tile itself (one-shot
+               all-reduce: (tp - 1) x M x N bf16 out per rank, the traffic of reduce-scatter +
+               all-gather only at tp = 2), bias / residual added in the reduction;
 * ``gemm_rs``  same, but each rank keeps only its row shard (GEMM -> reduce-scatter);
 * ``ag_gemm``  all-gather -> GEMM: the A operand is the concatenation of per-rank row shards
                that live in symmetric memory and are read tile by tile with TMA.
@@ -68,10 +69,11 @@ def _symm_alloc(nbytes, device, group):
 class _Ctx:
     """Staging + counters for one (M, N, mode) shape."""
 
-    def __init__(self, M, N, tp, rank, device, group):
+    def __init__(self, M, N, tp, rank, device, group, mode=0):
         self.M, self.N, self.tp, self.rank = M, N, tp, rank
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
-        self.slot_bytes = tp * M * N * 2
+        # the all-gather form (mode 2) reduces nothing: no partial-tile staging
+        self.slot_bytes = tp * M * N * 2 if mode != 2 else 0
         self.flag_bytes = tp * tiles * 4
         total = 2 * self.slot_bytes + self.flag_bytes + 256
         self.buf, self.h = _symm_alloc(total, device, group)
@@ -101,7 +103,7 @@ class FusedTP:
         key = (M, N, mode)
         c = self.ctx.get(key)
         if c is None:
-            c = self.ctx[key] = _Ctx(M, N, self.tp, self.rank, self.device, self.group)
+            c = self.ctx[key] = _Ctx(M, N, self.tp, self.rank, self.device, self.group, mode)
         return c
 
     def symmetric_rows(self, rows, cols, dtype=torch.bfloat16):

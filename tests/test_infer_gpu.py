@@ -86,3 +86,23 @@ def test_engine_gpu_matches_cpu_greedy_and_graph_replay():
     g, st, _ = e2.generate_group(prompts[1], 4, 10)
     assert all(x == g[0] for x in g) and st["prefix_blocks_saved"] == 0 * 3 + 3 * (7 // 8)
     assert ops.error_word() == 0
+
+
+def test_fp32_engine_on_gpu_is_token_exact():
+    """The fp32 configuration on the GPU (fp32 weights, activations and KV pool; products on the
+    CUDA-core fp32 kernel) reproduces the fp32 CPU engine token for token -- staggered continuous
+    batching, contiguous blocks and a prefix-shared group (reference tests/test_infer.c:67-95)."""
+    cfg = Config(2, 128, 4, 256, 64, 1)
+    cpu = GPT(cfg, "cpu", torch.float32); cpu.init_weights(1337); cpu.params.w.mul_(4.0)
+    gpu = GPT(cfg, "cuda", torch.float32); gpu.init_weights(1337); gpu.params.w.mul_(4.0)
+    prompts = [[5, 17, 3, 9, 100, 7], [5, 17, 3, 9, 100, 7, 30, 2, 2, 81], [9, 1, 44, 23, 8, 61, 2, 250, 0, 13], [70, 1, 3]]
+    n_new = [20, 16, 24, 28]
+    want, _, _ = InferEngine(cpu, block_size=4, max_seqs=16).generate(prompts, n_new, max_active=2)
+    for bs, active in ((4, 2), (64, 4), (8, 8)):
+        eng = InferEngine(gpu, block_size=bs, max_seqs=16)
+        assert eng.kc.dtype == torch.float32
+        got, _, _ = eng.generate(prompts, n_new, max_active=active)
+        assert got == want, (bs, active)
+    g, st, _ = InferEngine(gpu, block_size=4, max_seqs=16).generate_group(prompts[0], 8, 20)
+    assert all(x == want[0] for x in g) and st["prefix_blocks_saved"] == 7 * (6 // 4)
+    assert ops.error_word() == 0

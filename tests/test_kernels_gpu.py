@@ -71,6 +71,40 @@ def test_gemm_fp32_accumulate_and_alpha():
     assert relerr(out, a.float().t() @ b.float()) < 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(256, 256, 64, 0), (384, 328, 200, 256), (2048, 512, 4096, 512), (1000, 1024, 1032, 0),
+                                      (136, 64, 72, 64), (3072, 2048, 2048, 0), (512, 1536, 640, 128)])
+def test_gemm_weight_gradient_with_bias_gradient(M, N, K, bn):
+    """dW += dY^T X with db += column sums of dY taken from the operand tiles in shared memory
+    (single tiles, CTA pairs, ragged M / N / K, several tiles per CTA) against PyTorch."""
+    torch.manual_seed(12)
+    dy, x = _rand(K, M), _rand(K, N)
+    dw = torch.randn(M, N, device=DEV)
+    db = torch.randn(M, device=DEV)
+    want_w = dw + dy.float().t() @ x.float()
+    want_b = db + dy.float().sum(0)
+    ops.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True, block_n=bn, colsum=db)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+    assert relerr(dw, want_w) < 1e-4, relerr(dw, want_w)
+    assert relerr(db, want_b) < 1e-5, relerr(db, want_b)
+    # overwrite form, and run-to-run identical bits
+    db2, db3 = torch.full((M,), 3.0, device=DEV), torch.full((M,), -1.0, device=DEV)
+    ops.gemm(dy, x, dw, a_mn=True, b_mn=True, block_n=bn, colsum=db2)
+    ops.gemm(dy, x, dw, a_mn=True, b_mn=True, block_n=bn, colsum=db3)
+    assert torch.equal(db2, db3) and relerr(db2, dy.float().sum(0)) < 1e-5
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_gemm_f32_oracle_kernel(ta, tb):
+    torch.manual_seed(13)
+    M, N, K = 150, 77, 203
+    A = torch.randn(K, M, device=DEV).t() if ta else torch.randn(M, K, device=DEV)
+    B = torch.randn(N, K, device=DEV).t() if tb else torch.randn(K, N, device=DEV)
+    got = ops._matmul_f32(A, B)
+    want = (A.double() @ B.double()).float()
+    assert relerr(got, want) < 2e-6
+
+
 @pytest.mark.parametrize("epi", [ops.EPI_BIAS, ops.EPI_BIAS_GELU, ops.EPI_BIAS_RESID, ops.EPI_DGELU, ops.EPI_RESID])
 @pytest.mark.parametrize("N", [512, 328])
 def test_gemm_epilogues(epi, N):

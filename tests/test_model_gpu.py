@@ -82,3 +82,24 @@ def test_gpu_checkpoint_resume_is_bit_exact(tmp_path):
     assert torch.equal(res.model.params.w, full.model.params.w)
     assert torch.equal(res.model.params.wb, full.model.params.wb)
     assert torch.equal(res.model.params.v, full.model.params.v)
+
+
+def test_fp32_gpu_step_matches_fp32_cpu():
+    """fp32 model on the GPU (the oracle configuration: PyTorch fp32 operators + the native fp32
+    product) against the same model on the CPU: loss, gradients and one AdamW step."""
+    cfg = Config(2, 128, 4, 256, 64, 4)
+    ms = []
+    for dev in ("cpu", "cuda"):
+        m = GPT(cfg, dev, torch.float32)
+        m.init_weights(1337)
+        idx, tgt = Rng(5).batch(cfg.batch * cfg.seq, cfg.vocab)
+        m.set_input(idx.to(m.device), tgt.to(m.device))
+        m.forward()
+        m.backward()
+        ms.append(m)
+    cpu, gpu = ms
+    assert abs(cpu.loss() - gpu.loss()) < 1e-5
+    assert torch.allclose(gpu.params.g.cpu(), cpu.params.g, rtol=1e-4, atol=1e-6)
+    for m in ms:
+        m.adamw_step(3e-4)
+    assert torch.allclose(gpu.params.w.cpu(), cpu.params.w, rtol=1e-4, atol=3e-5)
