@@ -179,6 +179,8 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
   // this launch's call number: every CTA reads it before any CTA can have finished, and only the
   // CTA that finishes last advances it
   const uint32_t call = p.epoch ? *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1u : p.call_no;
@@ -617,7 +619,7 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   if (max_ctas > 0 && grid > max_ctas - n_copy) grid = max_ctas - n_copy;
   if (grid < 1) grid = 1;
   grid += n_copy;
-  gemm_comm_kernel<<<grid, THREADS, SMEM, (cudaStream_t)stream>>>(maps, p);
+  KH_LAUNCH(gemm_comm_kernel, grid, THREADS, SMEM, (cudaStream_t)stream, maps, p);
   KH_LAUNCH_CHECK("gemm_comm");
   return 0;
 }

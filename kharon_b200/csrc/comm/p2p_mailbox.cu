@@ -30,6 +30,8 @@ constexpr int PUT_UNROLL = 4;
 
 __global__ void __launch_bounds__(PUT_THREADS)
 p2p_put_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16, uint32_t* peer_flag, uint32_t* local) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t stride = (size_t)gridDim.x * PUT_THREADS;
   size_t i = (size_t)blockIdx.x * PUT_THREADS + threadIdx.x;
   for (; i + (PUT_UNROLL - 1) * stride < n16; i += PUT_UNROLL * stride) {
@@ -55,6 +57,8 @@ p2p_put_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n1
 }
 
 __global__ void p2p_wait_kernel(const uint32_t* flag, uint32_t* expected, unsigned long long limit_ns, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   if (threadIdx.x != 0) return;
   const uint32_t want = *expected + 1u;
   const uint64_t t0 = kh_globaltimer();
@@ -90,7 +94,7 @@ extern "C" int kh_p2p_put(const void* src, void* dst, long long bytes, void* pee
   const size_t n16 = (size_t)bytes / 16;
   size_t want = (n16 + PUT_THREADS * PUT_UNROLL - 1) / (PUT_THREADS * PUT_UNROLL);
   const int grid = (int)(want < (size_t)g_sms ? (want ? want : 1) : (size_t)g_sms);
-  p2p_put_kernel<<<grid, PUT_THREADS, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, n16, (uint32_t*)peer_flag,
+  KH_LAUNCH(p2p_put_kernel, grid, PUT_THREADS, 0, (cudaStream_t)stream, (const uint4*)src, (uint4*)dst, n16, (uint32_t*)peer_flag,
                                                                   (uint32_t*)local);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kh_set_error("p2p_put: %s", cudaGetErrorString(e)); return -1; }
@@ -100,7 +104,7 @@ extern "C" int kh_p2p_put(const void* src, void* dst, long long bytes, void* pee
 // flag: this rank's slot counter (written by the peer), expected: one zero-initialised local device word.
 extern "C" int kh_p2p_wait(const void* flag, void* expected, unsigned limit_ms, void* stream) {
   if (limit_ms == 0 || limit_ms > 60000) { kh_set_error("p2p_wait: limit %u ms outside (0, 60000]", limit_ms); return -1; }
-  p2p_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, (uint32_t*)expected,
+  KH_LAUNCH(p2p_wait_kernel, 1, 32, 0, (cudaStream_t)stream, (const uint32_t*)flag, (uint32_t*)expected,
                                                        (unsigned long long)limit_ms * 1000000ull, kh_error_word_dev());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kh_set_error("p2p_wait: %s", cudaGetErrorString(e)); return -1; }

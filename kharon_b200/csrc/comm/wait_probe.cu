@@ -7,6 +7,8 @@
 
 namespace {
 __global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long limit_ns, int* status, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   if (threadIdx.x != 0) return;
   const uint64_t t0 = kh_globaltimer();
   int st = 5;
@@ -26,7 +28,7 @@ __global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigne
 
 extern "C" int kh_wait_probe(const void* flag, unsigned target, unsigned limit_ms, void* status, void* stream) {
   if (limit_ms > 2000) { kh_set_error("wait_probe: limit above 2000 ms"); return -1; }
-  wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, target, (unsigned long long)limit_ms * 1000000ull,
+  KH_LAUNCH(wait_probe_kernel, 1, 32, 0, (cudaStream_t)stream, (const uint32_t*)flag, target, (unsigned long long)limit_ms * 1000000ull,
                                                        (int*)status, kh_error_word_dev());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kh_set_error("wait_probe: %s", cudaGetErrorString(e)); return -1; }

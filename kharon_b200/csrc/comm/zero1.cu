@@ -71,6 +71,8 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
 
 __global__ void __launch_bounds__(256)
 zero1_step_kernel(const ZeroParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ int s_ok;
   const int tid = threadIdx.x;
   // ---- phase 0
@@ -160,7 +162,26 @@ extern "C" int kh_zero1_step(const unsigned long long* g_ptrs, const unsigned lo
   p.epoch = epoch;
   p.wait_ns = kh_peer_wait_limit_ns();
   p.err = kh_error_word_dev();
-  zero1_step_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  // The exit barrier spans the grid, so every CTA has to be resident at the same time: a cooperative
+  // launch either places the whole grid or fails, also when other streams occupy part of the GPU.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, zero1_step_kernel, p);
+  if (le != cudaSuccess) { kh_set_error("zero1_step: launch of %d CTAs failed: %s", grid, cudaGetErrorString(le)); return -1; }
   KH_LAUNCH_CHECK("zero1_step");
   return 0;
+}
+
+// Largest grid kh_zero1_step can place on the current device (all CTAs resident at once).
+extern "C" int kh_zero1_max_grid() {
+  int dev = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, zero1_step_kernel, 256, 0) != cudaSuccess) return 0;
+  return sms * per_sm;
 }

@@ -46,6 +46,17 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch --------------------------------------------------------
+// Every kernel of the library is launched with programmatic stream serialization (KH_LAUNCH): the
+// next kernel of the stream may be scheduled, and run its prologue (barrier init, TMEM allocation,
+// descriptor prefetch), while the tail of this one is still running.  In exchange every kernel
+// executes pdl_wait() in all threads before its first access to global memory that an earlier
+// kernel may have written or may still read; the wait returns once all earlier kernels of the
+// stream have completed and their writes are visible (at once when the launch carried no such
+// dependency).  pdl_launch_dependents() lets the following kernel start being scheduled.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier --------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -296,3 +307,23 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
 const CUtensorMap* kh_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                    uint32_t box_rows, uint32_t box_cols);
 void kh_set_error(const char* fmt, ...);
+
+// 1 when kernels are launched with programmatic stream serialization (default; KHARON_PDL=0 or
+// kh_set_pdl(0) turns it off).
+int kh_pdl_enabled();
+
+// Launch `kernel` on `stream` with the library's launch attributes; arguments are converted to the
+// kernel's parameter types.
+template <typename... P, typename... A>
+inline cudaError_t kh_launch_ex(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kh_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
+#define KH_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  kh_launch_ex(kernel, dim3(grid), dim3(block), (size_t)(smem), (cudaStream_t)(stream), __VA_ARGS__)

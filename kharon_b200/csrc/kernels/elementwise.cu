@@ -32,6 +32,8 @@ __device__ __forceinline__ float warp_max(float v) {
 // out[r, :] = wte[tok[r], :] + wpe[pos[r], :]   (pos == nullptr: position r % T)
 __global__ void embed_fwd_k(const int* __restrict__ tok, const int* __restrict__ pos, const bf16* __restrict__ wte,
                             const bf16* __restrict__ wpe, bf16* __restrict__ out, int rows, int d, int T, int V) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   int t = tok[r];
   t = min(max(t, 0), V - 1);
@@ -52,7 +54,7 @@ __global__ void embed_fwd_k(const int* __restrict__ tok, const int* __restrict__
 extern "C" int kh_embed_fwd(const void* tok, const void* pos, const void* wte, const void* wpe, void* out, int rows,
                             int d, int T, int V, void* stream) {
   if (d % 8) { kh_set_error("embed: d must be a multiple of 8"); return -1; }
-  embed_fwd_k<<<rows, 128, 0, (cudaStream_t)stream>>>((const int*)tok, (const int*)pos, (const bf16*)wte,
+  KH_LAUNCH(embed_fwd_k, rows, 128, 0, (cudaStream_t)stream, (const int*)tok, (const int*)pos, (const bf16*)wte,
                                                       (const bf16*)wpe, (bf16*)out, rows, d, T, V);
   KH_LAUNCH_CHECK("embed_fwd");
   return 0;
@@ -64,6 +66,8 @@ extern "C" int kh_embed_fwd(const void* tok, const void* pos, const void* wte, c
 // `table` is int scratch of 2*V entries.
 __global__ void embed_bwd_index_k(const int* __restrict__ tok, int* __restrict__ first, int* __restrict__ cnt,
                                   int rows, int V) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const int t = tok[r];
@@ -73,6 +77,8 @@ __global__ void embed_bwd_index_k(const int* __restrict__ tok, int* __restrict__
 }
 __global__ void embed_bwd_wte_k(const int* __restrict__ tok, const bf16* __restrict__ dx, float* __restrict__ dwte,
                                 const int* __restrict__ first, const int* __restrict__ cnt, int rows, int d, int V) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ int s_list[64];
   __shared__ int s_n;
   const int r = blockIdx.x;
@@ -121,6 +127,8 @@ __global__ void embed_bwd_wte_k(const int* __restrict__ tok, const bf16* __restr
 }
 // dwpe[t, :] += sum_b dx[b*T + t, :]
 __global__ void embed_bwd_wpe_k(const bf16* __restrict__ dx, float* __restrict__ dwpe, int B, int T, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long)T * d) return;
   float acc = 0.f;
@@ -137,10 +145,10 @@ extern "C" int kh_embed_bwd(const void* tok, const void* dx, void* dwte, void* d
     int* cnt = first + V;
     cudaMemsetAsync(first, 0x7f, (size_t)V * sizeof(int), st);
     cudaMemsetAsync(cnt, 0, (size_t)V * sizeof(int), st);
-    embed_bwd_index_k<<<cdiv(rows, 256), 256, 0, st>>>((const int*)tok, first, cnt, rows, V);
-    embed_bwd_wte_k<<<rows, 128, 0, st>>>((const int*)tok, (const bf16*)dx, (float*)dwte, first, cnt, rows, d, V);
+    KH_LAUNCH(embed_bwd_index_k, cdiv(rows, 256), 256, 0, st, (const int*)tok, first, cnt, rows, V);
+    KH_LAUNCH(embed_bwd_wte_k, rows, 128, 0, st, (const int*)tok, (const bf16*)dx, (float*)dwte, first, cnt, rows, d, V);
   }
-  if (dwpe) embed_bwd_wpe_k<<<cdiv((long)T * d, 256), 256, 0, st>>>((const bf16*)dx, (float*)dwpe, B, T, d);
+  if (dwpe) KH_LAUNCH(embed_bwd_wpe_k, cdiv((long)T * d, 256), 256, 0, st, (const bf16*)dx, (float*)dwpe, B, T, d);
   KH_LAUNCH_CHECK("embed_bwd");
   return 0;
 }
@@ -154,6 +162,8 @@ extern "C" int kh_embed_bwd(const void* tok, const void* dx, void* dwte, void* d
 #define KH_COUNTER_SLOTS 1024
 __global__ void colsum_k(const bf16* __restrict__ x, int ld, float* __restrict__ out, int* __restrict__ counters,
                          float* __restrict__ scratch, int rows, int N, int rows_per_split, int accumulate) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float part[32][65];
   __shared__ int s_last;
   const int cg = threadIdx.x & 7, rg = threadIdx.x >> 3;
@@ -220,7 +230,7 @@ extern "C" int kh_colsum(const void* x, int ld, void* out, void* scratch, int ro
   const int splits = kh_colsum_splits(rows, N);
   const int rps = (rows + splits - 1) / splits;
   dim3 grid(cdiv(N, 64), splits);
-  colsum_k<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ld, (float*)out, (int*)scratch,
+  KH_LAUNCH(colsum_k, grid, 256, 0, (cudaStream_t)stream, (const bf16*)x, ld, (float*)out, (int*)scratch,
                                                     (float*)scratch + KH_COUNTER_SLOTS, rows, N, rps, accumulate);
   KH_LAUNCH_CHECK("colsum");
   return 0;
@@ -260,7 +270,7 @@ extern "C" int kh_colsum_noalloc(const void* x, int ld, void* out, int rows, int
   if (e != cudaSuccess) { kh_set_error("colsum_noalloc: clearing the counters failed: %s", cudaGetErrorString(e)); return -1; }
   const int rps = (rows + splits - 1) / splits;
   dim3 grid(cdiv(N, 64), splits);
-  colsum_k<<<grid, 256, 0, st>>>((const bf16*)x, ld, (float*)out, (int*)scratch, scratch + KH_COUNTER_SLOTS, rows, N, rps,
+  KH_LAUNCH(colsum_k, grid, 256, 0, st, (const bf16*)x, ld, (float*)out, (int*)scratch, scratch + KH_COUNTER_SLOTS, rows, N, rps,
                                  accumulate);
   KH_LAUNCH_CHECK("colsum_noalloc");
   return 0;
@@ -271,6 +281,8 @@ extern "C" int kh_colsum_noalloc(const void* x, int ld, void* out, int rows, int
 __global__ void layernorm_fwd_k(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
                                 bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows,
                                 int d) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -313,6 +325,8 @@ template <int NPL>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_reg_k(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
                     bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int d = NPL * 256;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -358,13 +372,13 @@ extern "C" int kh_layernorm_fwd(const void* x, const void* w, const void* b, voi
                                 int d, void* stream) {
   if (d % 8) { kh_set_error("layernorm: d must be a multiple of 8"); return -1; }
   if (d == 2048)
-    layernorm_fwd_reg_k<8><<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+    KH_LAUNCH((layernorm_fwd_reg_k<8>), cdiv(rows, 8), 256, 0, (cudaStream_t)stream, (const bf16*)x, (const bf16*)w, (const bf16*)b,
                                                                            (bf16*)y, (float*)mean, (float*)rstd, rows);
   else if (d == 1024)
-    layernorm_fwd_reg_k<4><<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+    KH_LAUNCH((layernorm_fwd_reg_k<4>), cdiv(rows, 8), 256, 0, (cudaStream_t)stream, (const bf16*)x, (const bf16*)w, (const bf16*)b,
                                                                            (bf16*)y, (float*)mean, (float*)rstd, rows);
   else
-    layernorm_fwd_k<<<cdiv(rows, 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+    KH_LAUNCH(layernorm_fwd_k, cdiv(rows, 8), 256, 0, (cudaStream_t)stream, (const bf16*)x, (const bf16*)w, (const bf16*)b,
                                                                       (bf16*)y, (float*)mean, (float*)rstd, rows, d);
   KH_LAUNCH_CHECK("layernorm_fwd");
   return 0;
@@ -381,6 +395,8 @@ extern "C" int kh_layernorm_fwd(const void* x, const void* w, const void* b, voi
 __global__ void layernorm_bwd_dx_k(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                                    const float* __restrict__ mean, const float* __restrict__ rstd,
                                    const bf16* __restrict__ dres, bf16* __restrict__ dx, int rows, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -424,6 +440,8 @@ __global__ void __launch_bounds__(256)
 layernorm_bwd_dx_reg_k(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                        const float* __restrict__ mean, const float* __restrict__ rstd,
                        const bf16* __restrict__ dres, bf16* __restrict__ dx, int rows) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int d = NPL * 256;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -475,6 +493,8 @@ __global__ void layernorm_bwd_dwdb_k(const bf16* __restrict__ dy, const bf16* __
                                      const float* __restrict__ mean, const float* __restrict__ rstd,
                                      int* __restrict__ counters, float* __restrict__ partials,
                                      float* __restrict__ dw, float* __restrict__ db, int rows, int d, int rows_per_split) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float part[32][2][65];
   __shared__ int s_last;
   const int cg = threadIdx.x & 7, rg = threadIdx.x >> 3;
@@ -542,16 +562,16 @@ extern "C" int kh_layernorm_bwd(const void* dy, const void* x, const void* w, co
   const int parts = kh_layernorm_bwd_parts(rows, d);
   const int rps = (rows + parts - 1) / parts;
   if (d == 2048)
-    layernorm_bwd_dx_reg_k<8><<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+    KH_LAUNCH((layernorm_bwd_dx_reg_k<8>), cdiv(rows, 8), 256, 0, st, (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
                                                             (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows);
   else if (d == 1024)
-    layernorm_bwd_dx_reg_k<4><<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+    KH_LAUNCH((layernorm_bwd_dx_reg_k<4>), cdiv(rows, 8), 256, 0, st, (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
                                                             (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows);
   else
-    layernorm_bwd_dx_k<<<cdiv(rows, 8), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
+    KH_LAUNCH(layernorm_bwd_dx_k, cdiv(rows, 8), 256, 0, st, (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean,
                                                      (const float*)rstd, (const bf16*)dres, (bf16*)dx, rows, d);
   dim3 grid(cdiv(d, 64), parts);
-  layernorm_bwd_dwdb_k<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd,
+  KH_LAUNCH(layernorm_bwd_dwdb_k, grid, 256, 0, st, (const bf16*)dy, (const bf16*)x, (const float*)mean, (const float*)rstd,
                                               (int*)partials, (float*)partials + KH_COUNTER_SLOTS, (float*)dw,
                                               (float*)db, rows, d, rps);
   KH_LAUNCH_CHECK("layernorm_bwd");
@@ -567,6 +587,8 @@ extern "C" int kh_layernorm_bwd(const void* dy, const void* x, const void* w, co
 __global__ void xent_k(bf16* __restrict__ logits, int ld, int V, const int* __restrict__ target,
                        const float* __restrict__ coef, float uniform, float* __restrict__ rowloss,
                        float* __restrict__ prob, int write_grad) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s_m[32], s_s[32];
   __shared__ float s_max, s_sum;
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -634,7 +656,7 @@ __global__ void xent_k(bf16* __restrict__ logits, int ld, int V, const int* __re
 extern "C" int kh_xent(void* logits, int ld, int V, const void* target, const void* coef, float uniform,
                        void* rowloss, void* prob, int write_grad, int rows, void* stream) {
   if (ld % 8 || ld < V) { kh_set_error("xent: ld=%d must be a multiple of 8 and >= V=%d", ld, V); return -1; }
-  xent_k<<<rows, 512, 0, (cudaStream_t)stream>>>((bf16*)logits, ld, V, (const int*)target, (const float*)coef, uniform,
+  KH_LAUNCH(xent_k, rows, 512, 0, (cudaStream_t)stream, (bf16*)logits, ld, V, (const int*)target, (const float*)coef, uniform,
                                                   (float*)rowloss, (float*)prob, write_grad);
   KH_LAUNCH_CHECK("xent");
   return 0;
@@ -646,6 +668,8 @@ extern "C" int kh_xent(void* logits, int ld, int V, const void* target, const vo
 // stage 2 overwrites the local logits with scale_r * (exp(x - gmax) / gsum - onehot).
 __global__ void xent_stats_k(const bf16* __restrict__ logits, int ld, int V, const int* __restrict__ target, int v0,
                              float* __restrict__ stats) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s_m[32], s_s[32];
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   const bf16* row = logits + (size_t)r * ld;
@@ -687,6 +711,8 @@ __global__ void xent_stats_k(const bf16* __restrict__ logits, int ld, int V, con
 __global__ void xent_grad_k(bf16* __restrict__ logits, int ld, int V, const int* __restrict__ target, int v0,
                             const float* __restrict__ gmax, const float* __restrict__ gsum,
                             const float* __restrict__ coef, float uniform) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   bf16* row = logits + (size_t)r * ld;
   const int tg = target[r];
@@ -712,14 +738,14 @@ __global__ void xent_grad_k(bf16* __restrict__ logits, int ld, int V, const int*
 }
 extern "C" int kh_xent_stats(const void* logits, int ld, int V, const void* target, int v0, void* stats, int rows, void* stream) {
   if (ld % 8 || ld < V) { kh_set_error("xent_stats: ld=%d must be a multiple of 8 and >= V=%d", ld, V); return -1; }
-  xent_stats_k<<<rows, 512, 0, (cudaStream_t)stream>>>((const bf16*)logits, ld, V, (const int*)target, v0, (float*)stats);
+  KH_LAUNCH(xent_stats_k, rows, 512, 0, (cudaStream_t)stream, (const bf16*)logits, ld, V, (const int*)target, v0, (float*)stats);
   KH_LAUNCH_CHECK("xent_stats");
   return 0;
 }
 extern "C" int kh_xent_grad(void* logits, int ld, int V, const void* target, int v0, const void* gmax, const void* gsum,
                             const void* coef, float uniform, int rows, void* stream) {
   if (ld % 8 || ld < V) { kh_set_error("xent_grad: ld=%d must be a multiple of 8 and >= V=%d", ld, V); return -1; }
-  xent_grad_k<<<rows, 512, 0, (cudaStream_t)stream>>>((bf16*)logits, ld, V, (const int*)target, v0, (const float*)gmax,
+  KH_LAUNCH(xent_grad_k, rows, 512, 0, (cudaStream_t)stream, (bf16*)logits, ld, V, (const int*)target, v0, (const float*)gmax,
                                                        (const float*)gsum, (const float*)coef, uniform);
   KH_LAUNCH_CHECK("xent_grad");
   return 0;
@@ -727,6 +753,8 @@ extern "C" int kh_xent_grad(void* logits, int ld, int V, const void* target, int
 
 // out[0] (+)= scale * sum_i x[i], single CTA, fixed-order tree (loss reduction on the device)
 __global__ void sum_f32_k(const float* __restrict__ x, long n, float scale, float* __restrict__ out, int accumulate) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s[1024];
   float acc = 0.f;
   for (long i = threadIdx.x; i < n; i += blockDim.x) acc += x[i];
@@ -739,7 +767,7 @@ __global__ void sum_f32_k(const float* __restrict__ x, long n, float scale, floa
   if (threadIdx.x == 0) out[0] = (accumulate ? out[0] : 0.f) + s[0] * scale;
 }
 extern "C" int kh_sum_f32(const void* x, long n, float scale, void* out, int accumulate, void* stream) {
-  sum_f32_k<<<1, 1024, 0, (cudaStream_t)stream>>>((const float*)x, n, scale, (float*)out, accumulate);
+  KH_LAUNCH(sum_f32_k, 1, 1024, 0, (cudaStream_t)stream, (const float*)x, n, scale, (float*)out, accumulate);
   KH_LAUNCH_CHECK("sum_f32");
   return 0;
 }
@@ -751,6 +779,8 @@ extern "C" int kh_sum_f32(const void* x, long n, float scale, void* out, int acc
 __global__ void adamw_k(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                         bf16* __restrict__ pb, long n, float lr, float b1, float b2, float eps, float wd, float bc1,
                         float bc2, float grad_scale, int zero_grad) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long i4 = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i4 >= n) return;
   if (i4 + 4 <= n) {
@@ -791,7 +821,7 @@ extern "C" int kh_adamw(void* p, void* g, void* m, void* v, void* pb, long n, fl
     kh_set_error("adamw: buffers must be 16-byte aligned");
     return -1;
   }
-  adamw_k<<<cdiv(cdiv(n, 4), 256), 256, 0, (cudaStream_t)stream>>>((float*)p, (float*)g, (float*)m, (float*)v, (bf16*)pb,
+  KH_LAUNCH(adamw_k, cdiv(cdiv(n, 4), 256), 256, 0, (cudaStream_t)stream, (float*)p, (float*)g, (float*)m, (float*)v, (bf16*)pb,
                                                                    n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, zero_grad);
   KH_LAUNCH_CHECK("adamw");
   return 0;
@@ -799,6 +829,8 @@ extern "C" int kh_adamw(void* p, void* g, void* m, void* v, void* pb, long n, fl
 
 // -------------------------------------------------------------------------------- utilities
 __global__ void cast_f32_bf16_k(const float* __restrict__ x, bf16* __restrict__ y, long n) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i + 4 <= n) {
     float4 v = *reinterpret_cast<const float4*>(x + i);
@@ -808,12 +840,14 @@ __global__ void cast_f32_bf16_k(const float* __restrict__ x, bf16* __restrict__ 
   }
 }
 extern "C" int kh_cast_f32_bf16(const void* x, void* y, long n, void* stream) {
-  cast_f32_bf16_k<<<cdiv(cdiv(n, 4), 256), 256, 0, (cudaStream_t)stream>>>((const float*)x, (bf16*)y, n);
+  KH_LAUNCH(cast_f32_bf16_k, cdiv(cdiv(n, 4), 256), 256, 0, (cudaStream_t)stream, (const float*)x, (bf16*)y, n);
   KH_LAUNCH_CHECK("cast_f32_bf16");
   return 0;
 }
 // c = a + b (bf16), n a multiple of 8
 __global__ void add_bf16_k(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ c, long nv) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nv) return;
   uint4 x = a[i], y = b[i], z;
@@ -827,16 +861,18 @@ __global__ void add_bf16_k(const uint4* __restrict__ a, const uint4* __restrict_
 }
 extern "C" int kh_add_bf16(const void* a, const void* b, void* c, long n, void* stream) {
   if (n % 8) { kh_set_error("add: n must be a multiple of 8"); return -1; }
-  add_bf16_k<<<cdiv(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)a, (const uint4*)b, (uint4*)c, n / 8);
+  KH_LAUNCH(add_bf16_k, cdiv(n / 8, 256), 256, 0, (cudaStream_t)stream, (const uint4*)a, (const uint4*)b, (uint4*)c, n / 8);
   KH_LAUNCH_CHECK("add_bf16");
   return 0;
 }
 // Writes a buffer larger than L2 so that the next timed iteration starts from DRAM.
 __global__ void fill_u32_k(uint32_t* p, long n, uint32_t v) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) p[i] = v;
 }
 extern "C" int kh_fill_u32(void* p, long n, unsigned v, void* stream) {
-  fill_u32_k<<<1184, 256, 0, (cudaStream_t)stream>>>((uint32_t*)p, n, v);
+  KH_LAUNCH(fill_u32_k, 1184, 256, 0, (cudaStream_t)stream, (uint32_t*)p, n, v);
   KH_LAUNCH_CHECK("fill_u32");
   return 0;
 }

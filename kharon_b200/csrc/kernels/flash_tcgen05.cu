@@ -104,6 +104,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tS = tmem, tO = tmem + 128;
   const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
 
@@ -233,6 +235,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // delta[b,h,t] = sum_e dO[b,t,h,e] * O[b,t,h,e]; one warp per (row, head)
 __global__ void flash_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout, float* __restrict__ delta,
                                    int B, int T, int H, int hd) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (long)B * T * H) return;
@@ -290,6 +294,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 256 + HD;
   const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
 
@@ -448,6 +454,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
   const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
 
@@ -568,7 +576,7 @@ int launch_fwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
   static bool once = false;
   if (!once) { if (set_smem(flash_fwd_kernel<HD, BKV>, SMEM, "flash_fwd")) return -1; once = true; }
   dim3 grid((p.T + 127) / 128, p.H, p.B);
-  flash_fwd_kernel<HD, BKV><<<grid, 128, SMEM, st>>>(*mq, *mkv, p);
+  KH_LAUNCH((flash_fwd_kernel<HD, BKV>), grid, 128, SMEM, st, *mq, *mkv, p);
   KH_LAUNCH_CHECK("flash_fwd");
   return 0;
 }
@@ -580,7 +588,7 @@ int launch_bwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
   const CUtensorMap* md = kh_tmap_2d_bf16(p.dout, rows, p.H * HD, p.H * HD, 128, 64);
   if (!mq || !md) return -1;
   const long nw = (long)rows * p.H;
-  flash_delta_kernel<<<(unsigned)((nw * 32 + 255) / 256), 256, 0, st>>>(p.o, p.dout, p.delta, p.B, p.T, p.H, HD);
+  KH_LAUNCH(flash_delta_kernel, (unsigned)((nw * 32 + 255) / 256), 256, 0, st, p.o, p.dout, p.delta, p.B, p.T, p.H, HD);
   constexpr int SMEM_KV = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 1024 + 1024 + 64;
   constexpr int SMEM_Q = 4 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 64;
   static bool once = false;
@@ -589,8 +597,8 @@ int launch_bwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
     once = true;
   }
   dim3 grid((p.T + 127) / 128, p.H, p.B);
-  flash_dkv_kernel<HD><<<grid, 128, SMEM_KV, st>>>(*mq, *md, p);
-  flash_dq_kernel<HD><<<grid, 128, SMEM_Q, st>>>(*mq, *md, p);
+  KH_LAUNCH((flash_dkv_kernel<HD>), grid, 128, SMEM_KV, st, *mq, *md, p);
+  KH_LAUNCH((flash_dq_kernel<HD>), grid, 128, SMEM_Q, st, *mq, *md, p);
   KH_LAUNCH_CHECK("flash_bwd");
   return 0;
 }

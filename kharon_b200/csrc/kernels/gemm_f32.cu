@@ -15,6 +15,8 @@ constexpr int TS = 64, TK = 16;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, long sa_m, long sa_k, const float* __restrict__ B, long sb_k, long sb_n,
                 float* __restrict__ C, long ldc, int M, int N, int K) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float As[TK][TS + 1];
   __shared__ float Bs[TK][TS + 1];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -67,7 +69,7 @@ extern "C" int kh_gemm_f32(const void* A, long sa_m, long sa_k, const void* B, l
   if (M <= 0 || N <= 0 || K <= 0) { kh_set_error("gemm_f32: empty problem %dx%dx%d", M, N, K); return -1; }
   dim3 grid((N + TS - 1) / TS, (M + TS - 1) / TS);
   if (grid.y > 65535) { kh_set_error("gemm_f32: M=%d is beyond the grid limit of this oracle kernel", M); return -1; }
-  gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)A, sa_m, sa_k, (const float*)B, sb_k, sb_n,
+  KH_LAUNCH(gemm_f32_kernel, grid, 256, 0, (cudaStream_t)stream, (const float*)A, sa_m, sa_k, (const float*)B, sb_k, sb_n,
                                                           (float*)C, ldc, M, N, K);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kh_set_error("gemm_f32 launch failed: %s", cudaGetErrorString(e)); return -1; }

@@ -50,6 +50,8 @@ template <int MP>   // padded row count = MMA N (16, 32 or 64)
 __global__ void __launch_bounds__(128, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const SkinnyParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int W_BYTES = TN * BK * 2, X_BYTES = MP * BK * 2, STAGE = W_BYTES + X_BYTES;
   constexpr int TMEM_COLS = MP < 32 ? 32 : MP;
   extern __shared__ uint8_t smem_raw[];
@@ -249,7 +251,7 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const SkinnyParams& p, 
     attr = true;
   }
   dim3 grid(n_tiles, split);
-  gemm_skinny_kernel<MP><<<grid, 128, SMEM, st>>>(*mw, *mx, p);
+  KH_LAUNCH((gemm_skinny_kernel<MP>), grid, 128, SMEM, st, *mw, *mx, p);
   KH_LAUNCH_CHECK("gemm_skinny");
   return 0;
 }

@@ -71,6 +71,20 @@ extern "C" long kh_set_peer_wait_limit_ms(long ms) {
   if (ms > 0) g_peer_wait_ns = (unsigned long long)ms * 1000000ull;
   return old;
 }
+static int g_pdl = -1;
+int kh_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("KHARON_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+// Programmatic dependent launch for all kernels of the library on/off; returns the previous setting.
+extern "C" int kh_set_pdl(int on) {
+  const int old = kh_pdl_enabled();
+  g_pdl = on ? 1 : 0;
+  return old;
+}
 static thread_local std::string g_host_err;
 void kh_set_error(const char* fmt, ...) {
   char buf[512];
@@ -252,6 +266,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                        // operands and outputs belong to earlier kernels of the stream up to here
+  pdl_launch_dependents();
 
   // tile id -> (tm, tn): bands of 8 M-tiles, N fastest inside a band keeps both panels in L2
   auto tile_coord = [&](int t, int& tm, int& tn) {
@@ -575,10 +591,13 @@ static int launch_gemm_pair(const CUtensorMap* ta, const CUtensorMap* tb, const 
   using Cfg = GemmCfg<256, true>;
   auto kern = gemm_kernel<256, true>;
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(p.colsum ? CSUM_THREADS : GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.blockDim = dim3(p.colsum ? CSUM_THREADS : GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st; cfg.attrs = attr;
+  cfg.numAttrs = kh_pdl_enabled() ? 2 : 1;
   if (g_pair_clusters < 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) { kh_set_error("gemm: cannot opt in to %d bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e)); return -1; }
@@ -611,8 +630,7 @@ static int launch_gemm(const CUtensorMap* ta, const CUtensorMap* tb, const GemmP
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_kernel<BN, false><<<grid, p.colsum ? CSUM_THREADS : GEMM_THREADS, Cfg::SMEM, st>>>(*ta, *tb, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = KH_LAUNCH((gemm_kernel<BN, false>), grid, p.colsum ? CSUM_THREADS : GEMM_THREADS, Cfg::SMEM, st, *ta, *tb, p);
   if (e != cudaSuccess) { kh_set_error("gemm launch failed: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }

@@ -23,6 +23,8 @@ static inline int cdiv(long a, long b) { return (int)((a + b - 1) / b); }
 __global__ void append_kv_k(const bf16* __restrict__ qkv, int ld, bf16* __restrict__ kc, bf16* __restrict__ vc,
                             const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ btab,
                             int max_lb, int bs, int d, int ntok) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int per = d / 8;
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long)ntok * per) return;
@@ -38,7 +40,7 @@ extern "C" int kh_append_kv(const void* qkv, int ld, void* kc, void* vc, const v
                             const void* btab, int max_lb, int bs, int H, int hd, int ntok, void* stream) {
   const int d = H * hd;
   if (d % 8) { kh_set_error("append_kv: H*hd must be a multiple of 8"); return -1; }
-  append_kv_k<<<cdiv((long)ntok * d / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+  KH_LAUNCH(append_kv_k, cdiv((long)ntok * d / 8, 256), 256, 0, (cudaStream_t)stream, 
       (const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, d, ntok);
   KH_LAUNCH_CHECK("append_kv");
   return 0;
@@ -58,6 +60,8 @@ __global__ void __launch_bounds__(128)
 paged_attn_k(const bf16* __restrict__ qkv, int ld, bf16* __restrict__ kc, bf16* __restrict__ vc,
              bf16* __restrict__ out, const int* __restrict__ pos, const int* __restrict__ slot,
              const int* __restrict__ btab, int max_lb, int bs, int H, float scale, int max_ctx, int append) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ float sm[];
   constexpr int TPR = HD / 8;               // threads per value row
   constexpr int GROUPS = 128 / TPR;         // value rows in flight
@@ -145,7 +149,7 @@ extern "C" int kh_paged_attn(const void* qkv, int ld, void* kc, void* vc, void* 
   {                                                                                                                  \
     static size_t attr = 48 * 1024;                                                                                  \
     if (smem > attr) { cudaFuncSetAttribute(paged_attn_k<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; } \
-    paged_attn_k<HD><<<grid, 128, smem, st>>>((const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (bf16*)out,                 \
+    KH_LAUNCH((paged_attn_k<HD>), grid, 128, smem, st, (const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (bf16*)out,                 \
                                               (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, H,    \
                                               scale, max_ctx, append);                                               \
   }
@@ -161,19 +165,23 @@ extern "C" int kh_paged_attn(const void* qkv, int ld, void* kc, void* vc, void* 
 
 // ------------------------------------------------------------------------------- gather / copy
 __global__ void gather_rows_k(const bf16* __restrict__ x, const int* __restrict__ rows, bf16* __restrict__ out, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)rows[blockIdx.x] * d);
   uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * d);
   for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
 }
 extern "C" int kh_gather_rows(const void* x, const void* rows, void* out, int nseq, int d, void* stream) {
   if (d % 8) { kh_set_error("gather_rows: d must be a multiple of 8"); return -1; }
-  gather_rows_k<<<nseq, 128, 0, (cudaStream_t)stream>>>((const bf16*)x, (const int*)rows, (bf16*)out, d);
+  KH_LAUNCH(gather_rows_k, nseq, 128, 0, (cudaStream_t)stream, (const bf16*)x, (const int*)rows, (bf16*)out, d);
   KH_LAUNCH_CHECK("gather_rows");
   return 0;
 }
 // Copies whole KV blocks (src -> dst pairs) in every layer: the device half of copy-on-write.
 __global__ void copy_blocks_k(bf16* __restrict__ kc, bf16* __restrict__ vc, const int* __restrict__ pairs,
                               size_t block_elems, size_t layer_elems) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int pr = blockIdx.x, layer = blockIdx.y;
   const size_t src = (size_t)layer * layer_elems + (size_t)pairs[2 * pr] * block_elems;
   const size_t dst = (size_t)layer * layer_elems + (size_t)pairs[2 * pr + 1] * block_elems;
@@ -187,7 +195,7 @@ extern "C" int kh_copy_blocks(void* kc, void* vc, const void* pairs, int npairs,
   if (npairs <= 0) return 0;
   if (block_elems % 8) { kh_set_error("copy_blocks: block size must be a multiple of 8 elements"); return -1; }
   dim3 grid(npairs, n_layer);
-  copy_blocks_k<<<grid, 128, 0, (cudaStream_t)stream>>>((bf16*)kc, (bf16*)vc, (const int*)pairs, (size_t)block_elems,
+  KH_LAUNCH(copy_blocks_k, grid, 128, 0, (cudaStream_t)stream, (bf16*)kc, (bf16*)vc, (const int*)pairs, (size_t)block_elems,
                                                         (size_t)layer_elems);
   KH_LAUNCH_CHECK("copy_blocks");
   return 0;
@@ -206,6 +214,8 @@ __device__ __forceinline__ uint32_t mix32(uint64_t x) {
 __global__ void __launch_bounds__(256)
 sample_k(const bf16* __restrict__ logits, int ld, int V, float temperature, unsigned long long seed, int step,
          int rep, int* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float s_v[256];
   __shared__ int s_i[256];
   __shared__ float s_scan[257];
@@ -263,7 +273,7 @@ sample_k(const bf16* __restrict__ logits, int ld, int V, float temperature, unsi
 extern "C" int kh_sample(const void* logits, int ld, int V, float temperature, unsigned long long seed, int step,
                          int rep, void* out, int nseq, void* stream) {
   if (rep < 1 || rep > 256) { kh_set_error("sample: rep must be in [1, 256]"); return -1; }
-  sample_k<<<nseq, 256, 0, (cudaStream_t)stream>>>((const bf16*)logits, ld, V, temperature, seed, step, rep, (int*)out);
+  KH_LAUNCH(sample_k, nseq, 256, 0, (cudaStream_t)stream, (const bf16*)logits, ld, V, temperature, seed, step, rep, (int*)out);
   KH_LAUNCH_CHECK("sample");
   return 0;
 }

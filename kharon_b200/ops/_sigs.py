@@ -48,6 +48,9 @@ _OPTIONAL = {
     "kh_gemm_comm": (i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, u32, u32,
                      C.c_uint64, vp, vp, vp, vp, i32, i32, vp),
     "kh_tmap_cache_limit": (long_, long_),
+    "kh_zero1_max_grid": (i32,),
+    "kh_set_pdl": (i32, i32),
+    "kh_set_peer_wait_limit_ms": (long_, long_),
     "kh_p2p_put": (i32, vp, vp, C.c_longlong, vp, vp, vp),
     "kh_p2p_wait": (i32, vp, vp, u32, vp),
     "kh_append_kv": (i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp),

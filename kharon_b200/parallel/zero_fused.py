@@ -46,7 +46,11 @@ class ZeroFused:
         self.c_wb = U(*self.ptrs["wb"]) if "wb" in self.ptrs else None
         self.c_ctr = U(*self.ptrs["ctr"])
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.grid = 2 * sms          # every CTA must be resident: the exit barrier spans the grid
+        # every CTA must be resident (the exit barrier spans the grid): the launch is cooperative and
+        # the grid is capped by what the occupancy query says the device can hold
+        lib = _native.cuda()
+        fit = int(lib.kh_zero1_max_grid()) if hasattr(lib, "kh_zero1_max_grid") else 2 * sms
+        self.grid = max(1, min(2 * sms, fit))
 
     def step(self, ps, shard, step_no, o):
         self.epoch += 1
