@@ -263,7 +263,8 @@ def test_embed_and_colsum():
         assert relerr(cs, 1 + x.float().sum(0)) < 1e-5
 
 
-@pytest.mark.parametrize("B,T,H,hd", [(2, 256, 4, 64), (1, 512, 2, 128), (3, 64, 2, 64), (2, 200, 2, 128), (1, 1024, 1, 64)])
+@pytest.mark.parametrize("B,T,H,hd", [(2, 256, 4, 64), (1, 512, 2, 128), (3, 64, 2, 64), (2, 200, 2, 128), (1, 1024, 1, 64),
+                                      (2, 384, 3, 128), (1, 130, 2, 64), (40, 512, 8, 128), (5, 72, 1, 128)])
 def test_flash_fwd_bwd(B, T, H, hd):
     torch.manual_seed(8)
     d = H * hd
@@ -287,6 +288,30 @@ def test_flash_fwd_bwd(B, T, H, hd):
     for i, name in enumerate("qkv"):
         e = relerr(dqkv[:, i * d:(i + 1) * d], dqkv2[:, i * d:(i + 1) * d])
         assert e < 2e-2, (name, e)
+    # every output element has one writer and a fixed summation order: identical bits on a second run
+    out3, lse3, dqkv3 = torch.zeros_like(out), torch.zeros_like(lse), torch.zeros_like(dqkv)
+    ops.flash_fwd(qkv, out3, lse3, B, T, H, hd)
+    ops.flash_bwd(qkv, out, dout, lse, dqkv3, delta, B, T, H, hd)
+    assert torch.equal(out, out3) and torch.equal(lse, lse3) and torch.equal(dqkv, dqkv3)
+
+
+def test_flash_large_scores_rescale():
+    """Scores that keep growing along the keys force the in-place rescaling of the output accumulator."""
+    torch.manual_seed(21)
+    B, T, H, hd = 1, 512, 2, 128
+    d = H * hd
+    qkv = _rand(B * T, 3 * d, scale=1.0)
+    ramp = torch.linspace(0.2, 6.0, T, device=DEV)[:, None]
+    qkv[:, d:2 * d] = (qkv[:, d:2 * d].float() * ramp).bfloat16()      # later keys have larger norms
+    out = torch.zeros(B * T, d, device=DEV, dtype=torch.bfloat16)
+    lse = torch.zeros(B, H, T, device=DEV)
+    ops.flash_fwd(qkv, out, lse, B, T, H, hd)
+    out2 = torch.empty_like(out); lse2 = torch.empty_like(lse)
+    ref.flash_fwd(qkv, out2, lse2, B, T, H, hd)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 0
+    assert relerr(out, out2) < 1e-2, relerr(out, out2)
+    assert relerr(lse, lse2) < 1e-3
 
 
 @pytest.mark.parametrize("M", [1, 8, 17, 32, 64])
