@@ -119,6 +119,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Tiled stores shared memory -> global (bulk async group of the issuing thread).  The box is
+// clipped at the tensor's extents, so a tile that sticks out past the end of a [batch, time, column]
+// tensor's time axis writes only its valid rows.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(m), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed bulk stores of this thread have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have completed
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // generic-proxy writes to smem -> visible to the async proxy (UMMA / TMA reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -318,6 +330,10 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
 // alignment rules.
 const CUtensorMap* kh_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                    uint32_t box_rows, uint32_t box_cols);
+// [d2, d1, d0] bf16 tensor (d0 contiguous, pitch `ld1` elements between d1 steps, `ld2` between d2
+// steps); box = box_d0 x box_d1 x 1, 128-byte swizzle.  Same caching and error convention.
+const CUtensorMap* kh_tmap_3d_bf16(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t ld1, uint64_t ld2,
+                                   uint32_t box_d1, uint32_t box_d0);
 void kh_set_error(const char* fmt, ...);
 
 // 1 when kernels are launched with programmatic stream serialization (default; KHARON_PDL=0 or

@@ -234,62 +234,65 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ================================================================================ forward, warp-specialised
-// Persistent CTAs, ten warps.  A work item is (batch, head, 256 consecutive queries): query tile A
-// (rows 0..127) belongs to warps 0-3, tile B (rows 128..255) to warps 4-7, one thread per query row.
-// Warp 8 streams Q tiles and a three-stage ring of (K, V) tiles of 64 keys with TMA; one lane of warp 9
-// issues every tcgen05.mma.  Per key tile j and query tile g:
+// Persistent CTAs of six warps, two CTAs per SM.  A work item is (batch, head, 128 consecutive
+// queries), one thread of warps 0-3 per query row.  Warp 4 streams the Q tile and a two-stage ring of
+// (K, V) tiles of 64 keys with TMA; one lane of warp 5 issues every tcgen05.mma.  Per key tile j:
 //
-//   S_g(j) = Q_g K_j^T  -> TMEM (two S buffers per g)        MMA warp, as soon as K_j has landed
-//   softmax warps of g:   read S_g(j), online softmax, P_g(j) -> shared memory (bf16)
-//   O_g  += P_g(j) V_j   accumulated in TMEM                  MMA warp, when P_g(j) is ready
+//   S(j) = Q K_j^T  -> TMEM (two S buffers)        MMA warp, as soon as K_j has landed
+//   softmax warps:     read S(j), online softmax, P(j) -> shared memory (bf16)
+//   O   += P(j) V_j   accumulated in TMEM           MMA warp, when P(j) is ready
 //
-// so the tensor cores work on tile B (and on the next S of tile A) while the threads of tile A are
-// in their exponentials, and the other way round.  O stays in TMEM for the whole item; when a
-// row's running maximum grows by more than 2^8 the row is rescaled in place (tcgen05.ld / st),
-// otherwise the older maximum stays the reference of the exponentials, which keeps the result
-// exact (the normaliser uses the same reference) and makes rescaling rare after the first tiles.
-// Items are handed out heaviest first (most key tiles); Q of the next item is prefetched while the
-// current one is still being multiplied.
+// S(j+1) is already in TMEM when the softmax of tile j ends, and the second CTA of the SM keeps the
+// tensor cores and the exponential unit busy while this one waits, loads or stores.  O stays in TMEM
+// for the whole item; when a row's running maximum grows by more than 2^8 the row is rescaled in
+// place (tcgen05.ld / st), otherwise the older maximum stays the reference of the exponentials,
+// which keeps the result exact (the normaliser uses the same reference) and makes rescaling rare
+// after the first tiles.  Items are handed out longest first (most key tiles).
 template <int HD>
 struct FwdWs {
-  static constexpr int BQ = 128, BKV = 64, NS = 3;
+  static constexpr int BQ = 128, BKV = 64, NS = 2;
   static constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
-  static constexpr int SMEM = 2 * Q_BYTES + NS * 2 * KV_BYTES + 2 * P_BYTES + 1024 + 256;
-  static constexpr int THREADS = 320, TMEM_COLS = 512;     // S: 4 x 64 columns, O: 2 x HD columns from 256
+  static constexpr int DATA = Q_BYTES + NS * 2 * KV_BYTES + P_BYTES;
+  static constexpr int SMEM = DATA + 256;      // the tiles start at the (1024-byte aligned) base of dynamic shared memory
+  static constexpr int THREADS = 192, TMEM_COLS = 256;     // S: 2 x 64 columns, O: HD columns from 128
 };
 
 template <int HD>
-__global__ void __launch_bounds__(320, 1)
-flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const AttnParams p,
-                    int n_items, int n_pairs) {
+__global__ void __launch_bounds__(192, 2)
+flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                    const __grid_constant__ CUtensorMap map_o, const AttnParams p, int n_items, int n_qt) {
   using C = FwdWs<HD>;
   constexpr int BQ = C::BQ, BKV = C::BKV, NS = C::NS;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sKV = sQ + 2 * C::Q_BYTES, sP = sKV + NS * 2 * C::KV_BYTES;
-  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(al + 2 * C::Q_BYTES + NS * 2 * C::KV_BYTES + 2 * C::P_BYTES);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  const uint32_t sQ = base, sKV = sQ + C::Q_BYTES, sP = sKV + NS * 2 * C::KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + C::DATA);
   const uint32_t b0 = smem_u32(bars);
-  const uint32_t bar_qfull = b0, bar_qfree = b0 + 16, bar_kvfull = b0 + 32, bar_kvfree = bar_kvfull + 8 * NS,
-                 bar_sfull = bar_kvfree + 8 * NS, bar_pready = bar_sfull + 32, bar_odone = bar_pready + 16,
-                 bar_ofree = bar_odone + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 + 2 + 2 * NS + 4 + 2 + 2 + 2);
+  // K and V stages are released separately: a K stage as soon as S(j) has retired, a V stage after PV(j)
+  const uint32_t bar_qfull = b0, bar_qfree = b0 + 8, bar_kfull = b0 + 16, bar_kfree = bar_kfull + 8 * NS,
+                 bar_vfull = bar_kfree + 8 * NS, bar_vfree = bar_vfull + 8 * NS,
+                 bar_sfull = bar_vfree + 8 * NS, bar_pready = bar_sfull + 16, bar_odone = bar_pready + 8,
+                 bar_ofree = bar_odone + 8, bar_epi = bar_ofree + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 + 4 * NS + 2 + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int g = 0; g < 2; g++) {
-      mbar_init(bar_qfull + 8 * g, 1); mbar_init(bar_qfree + 8 * g, 1);
-      mbar_init(bar_sfull + 16 * g, 1); mbar_init(bar_sfull + 16 * g + 8, 1);
-      mbar_init(bar_pready + 8 * g, 4); mbar_init(bar_odone + 8 * g, 1); mbar_init(bar_ofree + 8 * g, 4);
+    mbar_init(bar_qfull, 1); mbar_init(bar_qfree, 1);
+    for (int s = 0; s < NS; s++) {
+      mbar_init(bar_kfull + 8 * s, 1); mbar_init(bar_kfree + 8 * s, 1);
+      mbar_init(bar_vfull + 8 * s, 1); mbar_init(bar_vfree + 8 * s, 1);
     }
-    for (int s = 0; s < NS; s++) { mbar_init(bar_kvfull + 8 * s, 1); mbar_init(bar_kvfree + 8 * s, 1); }
-    *abort_flag = 0;
+    mbar_init(bar_sfull, 1); mbar_init(bar_sfull + 8, 1);
+    mbar_init(bar_pready, 4); mbar_init(bar_odone, 1); mbar_init(bar_ofree, 4); mbar_init(bar_epi, 128);
+    *abort_flag = (base & 1023u) ? 6 : 0;       // swizzled tiles need the 1024-byte alignment
+    if (base & 1023u) atomicCAS(p.err, 0, 6);
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_kv);
+    tma_prefetch_desc(&map_o);
   }
-  if (warp == 9) { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 5) { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -298,137 +301,120 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   pdl_launch_dependents();
 
   const int d = p.H * HD, BH = p.B * p.H;
-  // item w -> (pair of query tiles, batch, head); the pairs with the most key tiles come first
-  auto decode = [&](int w, int& b, int& h, int& q0, int& nA, int& nB) {
-    const int pair = n_pairs - 1 - w / BH, bh = w % BH;
-    b = bh / p.H; h = bh % p.H; q0 = pair * 2 * BQ;
-    nA = (min(q0 + BQ, p.T) + BKV - 1) / BKV;
-    nB = (q0 + BQ < p.T) ? (min(q0 + 2 * BQ, p.T) + BKV - 1) / BKV : 0;
+  // item w -> (query tile, batch, head); the tiles that see the most keys come first
+  auto decode = [&](int w, int& b, int& h, int& q0, int& n) {
+    const int qt = n_qt - 1 - w / BH, bh = w % BH;
+    b = bh / p.H; h = bh % p.H; q0 = qt * BQ;
+    n = (min(q0 + BQ, p.T) + BKV - 1) / BKV;
   };
+  const bool live = *abort_flag == 0;
 
-  if (warp == 8) {
+  if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int qc[2] = {0, 0}, kvc = 0;
+    if (lane == 0 && live) {
+      int ic = 0, kvc = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x) {
-        int b, h, q0, nA, nB;
-        decode(w, b, h, q0, nA, nB);
-        for (int g = 0; g < 2 && ok; g++) {
-          if (g == 1 && nB == 0) break;
-          if (!mbar_wait(bar_qfree + 8 * g, (qc[g] & 1) ^ 1, abort_flag, 6, p.err)) { ok = false; break; }
-          mbar_expect_tx(bar_qfull + 8 * g, C::Q_BYTES);
-          load_tile<HD>(sQ + g * C::Q_BYTES, &map_q, bar_qfull + 8 * g, h * HD, b * p.T + q0 + g * BQ, BQ);
-          qc[g]++;
-        }
-        const int n = max(nA, nB);
-        for (int j = 0; j < n && ok; j++, kvc++) {
+      for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
+        int b, h, q0, n;
+        decode(w, b, h, q0, n);
+        if (!mbar_wait(bar_qfree, (ic & 1) ^ 1, abort_flag, 6, p.err)) break;
+        mbar_expect_tx(bar_qfull, C::Q_BYTES);
+        load_tile<HD>(sQ, &map_q, bar_qfull, h * HD, b * p.T + q0, BQ);
+        for (int j = 0; j < n; j++, kvc++) {
           const int s = kvc % NS;
-          if (!mbar_wait(bar_kvfree + 8 * s, ((kvc / NS) & 1) ^ 1, abort_flag, 6, p.err)) { ok = false; break; }
+          const uint32_t par = ((kvc / NS) & 1) ^ 1;
           const uint32_t sk = sKV + s * 2 * C::KV_BYTES, sv = sk + C::KV_BYTES;
-          mbar_expect_tx(bar_kvfull + 8 * s, 2 * C::KV_BYTES);
-          load_tile<HD>(sk, &map_kv, bar_kvfull + 8 * s, d + h * HD, b * p.T + j * BKV, BKV);
-          load_tile<HD>(sv, &map_kv, bar_kvfull + 8 * s, 2 * d + h * HD, b * p.T + j * BKV, BKV);
+          if (!mbar_wait(bar_kfree + 8 * s, par, abort_flag, 6, p.err)) { ok = false; break; }
+          mbar_expect_tx(bar_kfull + 8 * s, C::KV_BYTES);
+          load_tile<HD>(sk, &map_kv, bar_kfull + 8 * s, d + h * HD, b * p.T + j * BKV, BKV);
+          if (!mbar_wait(bar_vfree + 8 * s, par, abort_flag, 6, p.err)) { ok = false; break; }
+          mbar_expect_tx(bar_vfull + 8 * s, C::KV_BYTES);
+          load_tile<HD>(sv, &map_kv, bar_vfull + 8 * s, 2 * d + h * HD, b * p.T + j * BKV, BKV);
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && live) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BKV, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
-      int qc[2] = {0, 0}, pc[2] = {0, 0}, ofc[2] = {0, 0}, kvc = 0;
+      int ic = 0, pc = 0, kvc = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x) {
-        int b, h, q0, nA, nB;
-        decode(w, b, h, q0, nA, nB);
-        const int ng[2] = {nA, nB};
-        const int n = max(nA, nB);
-        for (int g = 0; g < 2 && ok; g++) {
-          if (ng[g] == 0) continue;
-          if (!mbar_wait(bar_qfull + 8 * g, qc[g] & 1, abort_flag, 6, p.err)) ok = false;
-          qc[g]++;
-        }
+      for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
+        int b, h, q0, n;
+        decode(w, b, h, q0, n);
+        if (!mbar_wait(bar_qfull, ic & 1, abort_flag, 6, p.err)) break;
         const int kv_base = kvc;
         for (int j = 0; j <= n && ok; j++) {
           if (j < n) {
             const int s = kvc % NS;
-            if (!mbar_wait(bar_kvfull + 8 * s, (kvc / NS) & 1, abort_flag, 6, p.err)) { ok = false; break; }
+            if (!mbar_wait(bar_kfull + 8 * s, (kvc / NS) & 1, abort_flag, 6, p.err)) { ok = false; break; }
             kvc++;
             tc_fence_after();
             const uint32_t sk = sKV + s * 2 * C::KV_BYTES;
-            for (int g = 0; g < 2; g++) {
-              if (j >= ng[g]) continue;
-              const uint32_t tS = tmem + g * 128 + (j & 1) * 64;
+            const uint32_t tS = tmem + (j & 1) * 64;
 #pragma unroll
-              for (int kk = 0; kk < HD / 16; kk++)
-                umma_f16_ss(tS, desc_k(sQ + g * C::Q_BYTES, BQ, kk), desc_k(sk, BKV, kk), idesc_s, kk > 0);
-              umma_commit(bar_sfull + 16 * g + 8 * (j & 1));
-              if (j == ng[g] - 1) umma_commit(bar_qfree + 8 * g);       // last use of this item's Q_g
-            }
+            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sQ, BQ, kk), desc_k(sk, BKV, kk), idesc_s, kk > 0);
+            umma_commit(bar_sfull + 8 * (j & 1));
+            umma_commit(bar_kfree + 8 * s);
+            if (j == n - 1) umma_commit(bar_qfree);         // last use of this item's Q
           }
           if (j >= 1) {
             const int jj = j - 1;
             const int s = (kv_base + jj) % NS;
             const uint32_t sv = sKV + s * 2 * C::KV_BYTES + C::KV_BYTES;
-            for (int g = 0; g < 2 && ok; g++) {
-              if (jj >= ng[g]) continue;
-              if (jj == 0) {      // the previous item's O_g has been read out
-                if (!mbar_wait(bar_ofree + 8 * g, (ofc[g] & 1) ^ 1, abort_flag, 6, p.err)) { ok = false; break; }
-                ofc[g]++;
-              }
-              if (!mbar_wait(bar_pready + 8 * g, pc[g] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-              pc[g]++;
-              tc_fence_after();
-              const uint32_t tO = tmem + 256 + g * HD;
+            if (!mbar_wait(bar_vfull + 8 * s, ((kv_base + jj) / NS) & 1, abort_flag, 6, p.err)) { ok = false; break; }
+            // the previous item's O has been read out
+            if (jj == 0 && !mbar_wait(bar_ofree, (ic & 1) ^ 1, abort_flag, 6, p.err)) { ok = false; break; }
+            if (!mbar_wait(bar_pready, pc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+            pc++;
+            tc_fence_after();
 #pragma unroll
-              for (int kk = 0; kk < BKV / 16; kk++)
-                umma_f16_ss(tO, desc_k(sP + g * C::P_BYTES, BQ, kk), desc_mn(sv, BKV, kk), idesc_o, (jj > 0 || kk > 0));
-              umma_commit(bar_odone + 8 * g);
-            }
-            if (ok) umma_commit(bar_kvfree + 8 * s);
+            for (int kk = 0; kk < BKV / 16; kk++)
+              umma_f16_ss(tmem + 128, desc_k(sP, BQ, kk), desc_mn(sv, BKV, kk), idesc_o, (jj > 0 || kk > 0));
+            umma_commit(bar_odone);
+            umma_commit(bar_vfree + 8 * s);
           }
         }
       }
     }
-  } else {
+  } else if (live) {
     // ------------------------------------------------------------------ softmax warps
-    const int g = warp >> 2, w4 = warp & 3;
-    const int row = w4 * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(w4 * 32) << 16;
-    const uint32_t tO = tmem + 256 + g * HD + lane_off;
-    const uint32_t sPg = sP + g * C::P_BYTES;
+    const int row = tid;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t tO = tmem + 128 + lane_off;
     const float sl2 = p.scale * LOG2E;
-    int sfc[2] = {0, 0}, odc = 0;
+    int sfc[2] = {0, 0}, odc = 0, epc = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x) {
-      int b, h, q0, nA, nB;
-      decode(w, b, h, q0, nA, nB);
-      const int n_g = g == 0 ? nA : nB;
-      if (n_g == 0) continue;
-      const int qt0 = q0 + g * BQ;          // first query of this tile
-      const int qpos = qt0 + row;
-      float m_ref = -INFINITY, l_run = 0.f;
-      for (int j = 0; j < n_g; j++) {
+      int b, h, q0, n;
+      decode(w, b, h, q0, n);
+      const int qpos = q0 + row;
+      float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (scaled to log2 units) and normaliser
+      for (int j = 0; j < n; j++) {
         const int buf = j & 1;
-        if (!mbar_wait(bar_sfull + 16 * g + 8 * buf, sfc[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        if (!mbar_wait(bar_sfull + 8 * buf, sfc[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
         sfc[buf]++;
         tc_fence_after();
         uint32_t r[64];
-        const uint32_t tS = tmem + g * 128 + buf * 64 + lane_off;
+        const uint32_t tS = tmem + buf * 64 + lane_off;
         tmem_ld32(tS, r);
         tmem_ld32(tS + 32, r + 32);
         tmem_ld_wait();
         const int k0 = j * BKV;
-        const bool need_mask = k0 + BKV - 1 > qt0;
-        float mt = -INFINITY;
+        if (k0 + BKV - 1 > q0) {               // tile touches the diagonal: mask keys after the query
 #pragma unroll
-        for (int i = 0; i < 64; i++) {
-          float sv = __uint_as_float(r[i]) * sl2;
-          if (need_mask && k0 + i > qpos) sv = -INFINITY;
-          r[i] = __float_as_uint(sv);
-          mt = fmaxf(mt, sv);
+          for (int i = 0; i < 64; i++)
+            if (k0 + i > qpos) r[i] = 0xff800000u;
         }
+        // maximum of the raw scores over four independent chains (the scale is positive)
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mx[0] = fmaxf(mx[0], __uint_as_float(r[i])); mx[1] = fmaxf(mx[1], __uint_as_float(r[i + 1]));
+          mx[2] = fmaxf(mx[2], __uint_as_float(r[i + 2])); mx[3] = fmaxf(mx[3], __uint_as_float(r[i + 3]));
+        }
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sl2;
         bool waited = false;
         if (j == 0) {
           m_ref = mt;
@@ -436,7 +422,7 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const bool grow = mt > m_ref + 8.f;
           if (__any_sync(0xffffffffu, grow)) {
             // rescale O in place: PV(j-1) must have retired, PV(j) is issued only after P(j) below
-            if (!mbar_wait(bar_odone + 8 * g, odc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+            if (!mbar_wait(bar_odone, odc & 1, abort_flag, 6, p.err)) { ok = false; break; }
             odc++;
             waited = true;
             tc_fence_after();
@@ -455,59 +441,76 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (grow) m_ref = mt;
           }
         }
-        float rowsum = 0.f;
+        float rs[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[32];
+        const float nm = -m_ref;
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float p0 = exp2f(__uint_as_float(r[i]) - m_ref), p1 = exp2f(__uint_as_float(r[i + 1]) - m_ref);
-          rowsum += p0 + p1;
+        for (int i = 0; i < 64; i += 4) {
+          const float p0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, nm)), p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, nm));
+          const float p2 = exp2f(fmaf(__uint_as_float(r[i + 2]), sl2, nm)), p3 = exp2f(fmaf(__uint_as_float(r[i + 3]), sl2, nm));
+          rs[0] += p0; rs[1] += p1; rs[2] += p2; rs[3] += p3;
           pk[i >> 1] = pack_bf16(p0, p1);
+          pk[(i >> 1) + 1] = pack_bf16(p2, p3);
         }
-        l_run += rowsum;
+        l_run += (rs[0] + rs[1]) + (rs[2] + rs[3]);
         if (j >= 1 && !waited) {      // PV(j-1) no longer reads the P buffer
-          if (!mbar_wait(bar_odone + 8 * g, odc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+          if (!mbar_wait(bar_odone, odc & 1, abort_flag, 6, p.err)) { ok = false; break; }
           odc++;
         }
 #pragma unroll
         for (int c = 0; c < 8; c++)
-          st_shared_v4(chunk_addr(sPg, BQ, row, c), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          st_shared_v4(chunk_addr(sP, BQ, row, c), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pready + 8 * g);
+        if (lane == 0) mbar_arrive(bar_pready);
       }
       if (!ok) break;
-      if (!mbar_wait(bar_odone + 8 * g, odc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+      if (!mbar_wait(bar_odone, odc & 1, abort_flag, 6, p.err)) { ok = false; break; }
       odc++;
       tc_fence_after();
+      // O tile -> bf16 -> the P buffer (free now) in the swizzled tile layout, 64 columns at a time -> one
+      // TMA store per slab; rows past the end of the sequence are clipped by the tensor map
       const float inv = 1.f / l_run;
-      bf16* op = p.out + (size_t)(b * p.T + qpos) * d + h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t o[32];
-        tmem_ld32(tO + c, o);
-        tmem_ld_wait();
-        if (qpos < p.T) {
+      for (int hf = 0; hf < HD / 64; hf++) {
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c + 8 * q) = v;
-          }
+        for (int c = 0; c < 64; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tO + hf * 64 + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; q++)
+            st_shared_v4(chunk_addr(sP, BQ, row, (c >> 3) + q),
+                         pack_bf16(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv),
+                         pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv),
+                         pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv),
+                         pack_bf16(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv));
         }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_epi);
+        if (!mbar_wait(bar_epi, epc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        epc++;
+        if (tid == 0) {
+          tma_store_3d(&map_o, sP, h * HD + hf * 64, q0, b);
+          bulk_commit();
+          bulk_wait_read_all();           // the buffer may be overwritten (next slab, next item's P)
+        }
+        mbar_arrive(bar_epi);
+        if (!mbar_wait(bar_epi, epc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        epc++;
       }
-      if (qpos < p.T && p.lse) p.lse[((size_t)b * p.H + h) * p.T + qpos] = (m_ref + log2f(l_run)) / LOG2E;
+      if (!ok) break;
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ofree + 8 * g);
+      if (lane == 0) mbar_arrive(bar_ofree);
+      if (qpos < p.T && p.lse) p.lse[((size_t)b * p.H + h) * p.T + qpos] = (m_ref + log2f(l_run)) / LOG2E;
     }
+    if (tid == 0) bulk_wait_all();
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
 }
 
 // ================================================================================ delta
@@ -839,54 +842,57 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 }
 
 // ================================================================================ backward, warp-specialised
-// Both backward kernels are persistent and split like the forward one: four compute warps (one
-// thread per row of the CTA's 128-row tile), a TMA warp and an MMA warp.  The other sequence
-// dimension is walked in sub-tiles of 64, so S and dP take 64 TMEM columns each and fit twice:
-// the MMA warp issues S(t+1), dP(t+1) while the compute warps turn S(t), dP(t) into P(t), dS(t),
-// and issues the accumulating products of sub-tile t as soon as those are in shared memory (two
-// buffers).  Gradients stay in TMEM for the whole item.  Work items are handed out longest first.
+// Both backward kernels are persistent (one CTA per SM) with ten warps: eight compute warps (two
+// threads per row of the CTA's 128-row tile, each taking 32 of a sub-tile's 64 columns), a TMA warp
+// and an MMA warp.  The other sequence dimension is walked in sub-tiles of 64 through a four-stage
+// TMA ring, so S and dP take 64 TMEM columns each and fit twice: the MMA warp issues S(t+1),
+// dP(t+1) while the compute warps turn S(t), dP(t) into P(t), dS(t), and issues the accumulating
+// products of sub-tile t as soon as those are in shared memory.  Gradients stay in TMEM for the
+// whole item.  Work items are handed out longest first.
 template <int HD>
 struct BwdWs {
-  static constexpr int BT = 128, BS = 64;
+  static constexpr int BT = 128, BS = 64, NS = 4;
   static constexpr int TILE = BT * HD * 2, SUB = BS * HD * 2, PS_BYTES = BT * BS * 2;
-  static constexpr int THREADS = 192, TMEM_COLS = 512;
-  // dK/dV: K, V tiles; ring of 2 (Q, dO) sub-tiles; P^T and dS^T twice; lse / delta of two sub-tiles
-  static constexpr int NS_KV = 2;
-  static constexpr int SMEM_KV = 2 * TILE + NS_KV * 2 * SUB + 4 * PS_BYTES + 2 * 128 * 4 + 1024 + 256;
-  // dQ: Q, dO tiles; ring of 3 (K, V) sub-tiles; dS twice
-  static constexpr int NS_Q = 3;
-  static constexpr int SMEM_Q = 2 * TILE + NS_Q * 2 * SUB + 2 * PS_BYTES + 1024 + 256;
+  static constexpr int THREADS = 320, TMEM_COLS = 512;
+  // dK/dV: K, V tiles; ring of (Q, dO) sub-tiles; P^T and dS^T; lse / delta of two sub-tiles
+  static constexpr int DATA_KV = 2 * TILE + NS * 2 * SUB + 2 * PS_BYTES + 2 * 128 * 4;
+  static constexpr int SMEM_KV = DATA_KV + 256;
+  // dQ: Q, dO tiles; ring of (K, V) sub-tiles; dS, with 16 KB behind it so that the pair stages the dQ tile
+  static constexpr int DATA_Q = 2 * TILE + NS * 2 * SUB + 2 * PS_BYTES;
+  static constexpr int SMEM_Q = DATA_Q + 256;
 };
 
 // ---- dK, dV: item = (batch, head, 128 keys); sub-tiles of 64 queries from the diagonal to the end
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_q,
-                    const __grid_constant__ CUtensorMap map_do, const AttnParams p, int n_items, int n_kt) {
+                    const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dqkv, const AttnParams p,
+                    int n_items, int n_kt) {
   using C = BwdWs<HD>;
-  constexpr int BT = C::BT, BS = C::BS, NS = C::NS_KV;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sK = base, sV = sK + C::TILE, sQD = sV + C::TILE, sP = sQD + NS * 2 * C::SUB, sDS = sP + 2 * C::PS_BYTES;
-  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
-  float* s_stat = reinterpret_cast<float*>(al + 2 * C::TILE + NS * 2 * C::SUB + 4 * C::PS_BYTES);   // [2][128]: lse | delta
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stat + 256);
+  constexpr int BT = C::BT, BS = C::BS, NS = C::NS;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  const uint32_t sK = base, sV = sK + C::TILE, sQD = sV + C::TILE, sP = sQD + NS * 2 * C::SUB, sDS = sP + C::PS_BYTES;
+  float* s_stat = reinterpret_cast<float*>(smem_raw + 2 * C::TILE + NS * 2 * C::SUB + 2 * C::PS_BYTES);   // [2][128]: lse | delta
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + C::DATA_KV);
   const uint32_t b0 = smem_u32(bars);
   const uint32_t bar_kvfull = b0, bar_kvfree = b0 + 8, bar_qfull = b0 + 16, bar_qfree = bar_qfull + 8 * NS,
-                 bar_sfull = bar_qfree + 8 * NS, bar_ready = bar_sfull + 16, bar_gdone = bar_ready + 16, bar_accfree = bar_gdone + 16,
-                 bar_stat = bar_accfree + 8;       // all 128 compute threads have written the next sub-tile's lse / delta
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 + 2 * NS + 2 + 2 + 2 + 1 + 1);
+                 bar_sfull = bar_qfree + 8 * NS, bar_ready = bar_sfull + 16, bar_gdone = bar_ready + 8,
+                 bar_accfree = bar_gdone + 8, bar_stat = bar_accfree + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 + 2 * NS + 2 + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    mbar_init(bar_kvfull, 1); mbar_init(bar_kvfree, 1); mbar_init(bar_accfree, 4); mbar_init(bar_stat, 128);
+    mbar_init(bar_kvfull, 1); mbar_init(bar_kvfree, 1);
     for (int s = 0; s < NS; s++) { mbar_init(bar_qfull + 8 * s, 1); mbar_init(bar_qfree + 8 * s, 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(bar_sfull + 8 * i, 1); mbar_init(bar_ready + 8 * i, 4); mbar_init(bar_gdone + 8 * i, 1); }
-    *abort_flag = 0;
+    mbar_init(bar_sfull, 1); mbar_init(bar_sfull + 8, 1);
+    mbar_init(bar_ready, 8); mbar_init(bar_gdone, 1); mbar_init(bar_accfree, 8); mbar_init(bar_stat, 256);
+    *abort_flag = (base & 1023u) ? 6 : 0;
+    if (base & 1023u) atomicCAS(p.err, 0, 6);
     mbar_fence_init();
-    tma_prefetch_desc(&map_kv); tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_kv); tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_dqkv);
   }
-  if (warp == 5) { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -900,9 +906,10 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
     b = bh / p.H; h = bh % p.H; k0 = jt * BT;
     n = (p.T - k0 + BS - 1) / BS;
   };
+  const bool live = *abort_flag == 0;
 
-  if (warp == 4) {
-    if (lane == 0) {
+  if (warp == 8) {
+    if (lane == 0 && live) {
       int ic = 0, qc = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
@@ -922,11 +929,11 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
         }
       }
     }
-  } else if (warp == 5) {
-    if (lane == 0) {
+  } else if (warp == 9) {
+    if (lane == 0 && live) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BS, 0, 0);
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, HD, 0, 1);
-      int ic = 0, qc = 0, rc[2] = {0, 0};
+      int ic = 0, qc = 0, rc = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
         int b, h, k0, n;
@@ -949,40 +956,44 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
             if (t == n - 1) umma_commit(bar_kvfree);        // K and V are only read by these products
           }
           if (t >= 1) {
-            const int tt = t - 1, s = (q_base + tt) % NS, buf = tt & 1;
+            const int tt = t - 1, s = (q_base + tt) % NS;
             const uint32_t sq = sQD + s * 2 * C::SUB, sdo = sq + C::SUB;
             if (tt == 0 && !mbar_wait(bar_accfree, (ic & 1) ^ 1, abort_flag, 6, p.err)) { ok = false; break; }
-            if (!mbar_wait(bar_ready + 8 * buf, rc[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-            rc[buf]++;
+            if (!mbar_wait(bar_ready, rc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+            rc++;
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < BS / 16; kk++)
-              umma_f16_ss(tmem + 256, desc_k(sP + buf * C::PS_BYTES, BT, kk), desc_mn(sdo, BS, kk), idesc_g, (tt > 0 || kk > 0));
+              umma_f16_ss(tmem + 256, desc_k(sP, BT, kk), desc_mn(sdo, BS, kk), idesc_g, (tt > 0 || kk > 0));
 #pragma unroll
             for (int kk = 0; kk < BS / 16; kk++)
-              umma_f16_ss(tmem + 256 + HD, desc_k(sDS + buf * C::PS_BYTES, BT, kk), desc_mn(sq, BS, kk), idesc_g, (tt > 0 || kk > 0));
-            umma_commit(bar_gdone + 8 * buf);
+              umma_f16_ss(tmem + 256 + HD, desc_k(sDS, BT, kk), desc_mn(sq, BS, kk), idesc_g, (tt > 0 || kk > 0));
+            umma_commit(bar_gdone);
             umma_commit(bar_qfree + 8 * s);
           }
         }
       }
     }
-  } else {
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+  } else if (live) {
+    const int row = tid & 127, half = tid >> 7;          // this thread: key row `row`, columns [32 half, 32 half + 32) of a sub-tile
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    int sfc[2] = {0, 0}, uses[2] = {0, 0}, obs[2] = {0, 0}, stc = 0;
+    int sfc[2] = {0, 0}, uses = 0, obs = 0, stc = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x) {
       int b, h, k0, n;
       decode(w, b, h, k0, n);
-      const int kpos = k0 + tid;
+      const int kpos = k0 + row;
       const size_t stat0 = ((size_t)b * p.H + h) * p.T;
-      auto fetch_stat = [&](int t) -> float {      // threads 0-63: lse of query tid of sub-tile t; 64-127: delta
+      // threads 0-63 fetch the lse of query tid of sub-tile t, threads 64-127 its delta.  The value is only
+      // touched (scaled, stored) at the end of the iteration, so the load is in flight during the sub-tile.
+      const float stat_mul = tid < 64 ? LOG2E : 1.f;
+      auto fetch_stat = [&](int t) -> float {
         const int qp = k0 + t * BS + (tid & 63);
-        if (t >= n || qp >= p.T) return tid < 64 ? INFINITY : 0.f;
-        return tid < 64 ? p.lse[stat0 + qp] * LOG2E : p.delta[stat0 + qp];
+        if (tid >= 128 || t >= n || qp >= p.T) return tid < 64 ? INFINITY : 0.f;
+        return __ldg((tid < 64 ? p.lse : p.delta) + stat0 + qp);
       };
-      s_stat[tid] = fetch_stat(0);
+      if (tid < 128) s_stat[tid] = fetch_stat(0) * stat_mul;
       mbar_arrive(bar_stat);
       if (!mbar_wait(bar_stat, stc & 1, abort_flag, 6, p.err)) break;
       stc++;
@@ -995,122 +1006,129 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
         tc_fence_after();
         const int q0s = k0 + t * BS;
         const bool diag = k0 + BT - 1 > q0s;
-        // the products that read P^T / dS^T of this buffer two sub-tiles ago have retired
-        while (obs[buf] < uses[buf]) {
-          if (!mbar_wait(bar_gdone + 8 * buf, obs[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-          obs[buf]++;
+        const int c = half * 32;
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + buf * 64 + lane_off + c, rs);
+        tmem_ld32(tmem + 128 + buf * 64 + lane_off + c, rd);
+        tmem_ld_wait();
+        uint32_t pp[16], ds[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            const int qi = c + e + u;
+            float pr = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -st[qi]));
+            if (diag && kpos > q0s + qi) pr = 0.f;
+            pv[u] = pr;
+            dv[u] = pr * (__uint_as_float(rd[e + u]) - st[64 + qi]) * p.scale;
+          }
+          pp[e >> 1] = pack_bf16(pv[0], pv[1]);
+          ds[e >> 1] = pack_bf16(dv[0], dv[1]);
+        }
+        // the products that read P^T / dS^T of the previous sub-tile have retired
+        while (obs < uses) {
+          if (!mbar_wait(bar_gdone, obs & 1, abort_flag, 6, p.err)) { ok = false; break; }
+          obs++;
         }
         if (!ok) break;
-#pragma unroll 1
-        for (int c = 0; c < BS; c += 32) {
-          uint32_t rs[32], rd[32];
-          tmem_ld32(tmem + buf * 64 + lane_off + c, rs);
-          tmem_ld32(tmem + 128 + buf * 64 + lane_off + c, rd);
-          tmem_ld_wait();
-          uint32_t pp[16], ds[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float pv[2], dv[2];
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-              const int qi = c + e + u;
-              float pr = exp2f(__uint_as_float(rs[e + u]) * sl2 - st[qi]);
-              if (diag && kpos > q0s + qi) pr = 0.f;
-              pv[u] = pr;
-              dv[u] = pr * (__uint_as_float(rd[e + u]) - st[64 + qi]) * p.scale;
-            }
-            pp[e >> 1] = pack_bf16(pv[0], pv[1]);
-            ds[e >> 1] = pack_bf16(dv[0], dv[1]);
-          }
-#pragma unroll
-          for (int g = 0; g < 4; g++) {
-            st_shared_v4(chunk_addr(sP + buf * C::PS_BYTES, BT, tid, (c >> 3) + g), pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
-            st_shared_v4(chunk_addr(sDS + buf * C::PS_BYTES, BT, tid, (c >> 3) + g), ds[4 * g], ds[4 * g + 1], ds[4 * g + 2], ds[4 * g + 3]);
-          }
+        for (int g = 0; g < 4; g++) {
+          st_shared_v4(chunk_addr(sP, BT, row, (c >> 3) + g), pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
+          st_shared_v4(chunk_addr(sDS, BT, row, (c >> 3) + g), ds[4 * g], ds[4 * g + 1], ds[4 * g + 2], ds[4 * g + 3]);
         }
-        uses[buf]++;
+        uses++;
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ready + 8 * buf);
-        s_stat[(buf ^ 1) * 128 + tid] = next_stat;
+        if (lane == 0) mbar_arrive(bar_ready);
+        if (tid < 128) s_stat[(buf ^ 1) * 128 + tid] = next_stat * stat_mul;
         mbar_arrive(bar_stat);
         if (!mbar_wait(bar_stat, stc & 1, abort_flag, 6, p.err)) { ok = false; break; }
         stc++;
       }
       if (!ok) break;
-      {   // the last accumulating products have retired
-        const int buf = (n - 1) & 1;
-        while (obs[buf] < uses[buf]) {
-          if (!mbar_wait(bar_gdone + 8 * buf, obs[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-          obs[buf]++;
-        }
-        if (!ok) break;
+      while (obs < uses) {      // the last accumulating products have retired
+        if (!mbar_wait(bar_gdone, obs & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        obs++;
       }
+      if (!ok) break;
       tc_fence_after();
-      const bool store = kpos < p.T;
-      bf16* dk = p.dqkv + (size_t)(b * p.T + kpos) * p.ld + d + h * HD;
-      bf16* dv = p.dqkv + (size_t)(b * p.T + kpos) * p.ld + 2 * d + h * HD;
+      // dV, then dK: TMEM -> bf16 -> the P^T / dS^T buffers (free now, 2 x 16 KB = one 128 x 128 tile in the
+      // swizzled layout) -> one TMA store per 64-column slab; rows past the end of the sequence are clipped
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t r1[32], r2[32];
-        tmem_ld32(tmem + 256 + lane_off + c, r1);
-        tmem_ld32(tmem + 256 + HD + lane_off + c, r2);
-        tmem_ld_wait();
-        if (store) {
+      for (int which = 0; which < 2; which++) {
+        const uint32_t tacc = tmem + 256 + which * HD + lane_off;
+#pragma unroll 1
+        for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+          uint32_t r1[32];
+          tmem_ld32(tacc + c, r1);
+          tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(r1[8 * g]), __uint_as_float(r1[8 * g + 1]));
-            o.y = pack_bf16(__uint_as_float(r1[8 * g + 2]), __uint_as_float(r1[8 * g + 3]));
-            o.z = pack_bf16(__uint_as_float(r1[8 * g + 4]), __uint_as_float(r1[8 * g + 5]));
-            o.w = pack_bf16(__uint_as_float(r1[8 * g + 6]), __uint_as_float(r1[8 * g + 7]));
-            *reinterpret_cast<uint4*>(dv + c + 8 * g) = o;
-            o.x = pack_bf16(__uint_as_float(r2[8 * g]), __uint_as_float(r2[8 * g + 1]));
-            o.y = pack_bf16(__uint_as_float(r2[8 * g + 2]), __uint_as_float(r2[8 * g + 3]));
-            o.z = pack_bf16(__uint_as_float(r2[8 * g + 4]), __uint_as_float(r2[8 * g + 5]));
-            o.w = pack_bf16(__uint_as_float(r2[8 * g + 6]), __uint_as_float(r2[8 * g + 7]));
-            *reinterpret_cast<uint4*>(dk + c + 8 * g) = o;
-          }
+          for (int g = 0; g < 4; g++)
+            st_shared_v4(chunk_addr(sP, BT, row, (c >> 3) + g),
+                         pack_bf16(__uint_as_float(r1[8 * g]), __uint_as_float(r1[8 * g + 1])),
+                         pack_bf16(__uint_as_float(r1[8 * g + 2]), __uint_as_float(r1[8 * g + 3])),
+                         pack_bf16(__uint_as_float(r1[8 * g + 4]), __uint_as_float(r1[8 * g + 5])),
+                         pack_bf16(__uint_as_float(r1[8 * g + 6]), __uint_as_float(r1[8 * g + 7])));
         }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_stat);
+        if (!mbar_wait(bar_stat, stc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        stc++;
+        if (tid == 0) {
+          const int col0 = (which == 0 ? 2 * d : d) + h * HD;
+#pragma unroll
+          for (int sl = 0; sl < HD / 64; sl++) tma_store_3d(&map_dqkv, sP + sl * C::PS_BYTES, col0 + sl * 64, k0, b);
+          bulk_commit();
+          bulk_wait_read_all();
+        }
+        mbar_arrive(bar_stat);
+        if (!mbar_wait(bar_stat, stc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        stc++;
       }
+      if (!ok) break;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_accfree);
     }
+    if (tid == 0) bulk_wait_all();
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
 }
 
 // ---- dQ: item = (batch, head, 128 queries); sub-tiles of 64 keys up to the diagonal
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
-                   const __grid_constant__ CUtensorMap map_kv, const AttnParams p, int n_items, int n_qt) {
+                   const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_dqkv, const AttnParams p,
+                   int n_items, int n_qt) {
   using C = BwdWs<HD>;
-  constexpr int BT = C::BT, BS = C::BS, NS = C::NS_Q;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  constexpr int BT = C::BT, BS = C::BS, NS = C::NS;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
   const uint32_t sQ = base, sDO = sQ + C::TILE, sKV = sDO + C::TILE, sDS = sKV + NS * 2 * C::SUB;
-  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(al + 2 * C::TILE + NS * 2 * C::SUB + 2 * C::PS_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + C::DATA_Q);
   const uint32_t b0 = smem_u32(bars);
   const uint32_t bar_qfull = b0, bar_qfree = b0 + 8, bar_kvfull = b0 + 16, bar_kvfree = bar_kvfull + 8 * NS,
-                 bar_sfull = bar_kvfree + 8 * NS, bar_ready = bar_sfull + 16, bar_gdone = bar_ready + 16, bar_accfree = bar_gdone + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 + 2 * NS + 2 + 2 + 2 + 1);
+                 bar_sfull = bar_kvfree + 8 * NS, bar_ready = bar_sfull + 16, bar_gdone = bar_ready + 8, bar_accfree = bar_gdone + 8,
+                 bar_epi = bar_accfree + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 + 2 * NS + 2 + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    mbar_init(bar_qfull, 1); mbar_init(bar_qfree, 1); mbar_init(bar_accfree, 4);
+    mbar_init(bar_qfull, 1); mbar_init(bar_qfree, 1);
     for (int s = 0; s < NS; s++) { mbar_init(bar_kvfull + 8 * s, 1); mbar_init(bar_kvfree + 8 * s, 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(bar_sfull + 8 * i, 1); mbar_init(bar_ready + 8 * i, 4); mbar_init(bar_gdone + 8 * i, 1); }
-    *abort_flag = 0;
+    mbar_init(bar_sfull, 1); mbar_init(bar_sfull + 8, 1);
+    mbar_init(bar_ready, 8); mbar_init(bar_gdone, 1); mbar_init(bar_accfree, 8); mbar_init(bar_epi, 256);
+    *abort_flag = (base & 1023u) ? 6 : 0;
+    if (base & 1023u) atomicCAS(p.err, 0, 6);
     mbar_fence_init();
-    tma_prefetch_desc(&map_kv); tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_kv); tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_dqkv);
   }
-  if (warp == 5) { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1124,9 +1142,10 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     b = bh / p.H; h = bh % p.H; q0 = qt * BT;
     n = (min(q0 + BT, p.T) + BS - 1) / BS;
   };
+  const bool live = *abort_flag == 0;
 
-  if (warp == 4) {
-    if (lane == 0) {
+  if (warp == 8) {
+    if (lane == 0 && live) {
       int ic = 0, kvc = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
@@ -1146,11 +1165,11 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
     }
-  } else if (warp == 5) {
-    if (lane == 0) {
+  } else if (warp == 9) {
+    if (lane == 0 && live) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BS, 0, 0);
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, HD, 0, 1);
-      int ic = 0, kvc = 0, rc[2] = {0, 0};
+      int ic = 0, kvc = 0, rc = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
         int b, h, q0, n;
@@ -1173,30 +1192,31 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (j == n - 1) umma_commit(bar_qfree);         // Q and dO are only read by these products
           }
           if (j >= 1) {
-            const int jj = j - 1, s = (kv_base + jj) % NS, buf = jj & 1;
+            const int jj = j - 1, s = (kv_base + jj) % NS;
             const uint32_t sk = sKV + s * 2 * C::SUB;
             if (jj == 0 && !mbar_wait(bar_accfree, (ic & 1) ^ 1, abort_flag, 6, p.err)) { ok = false; break; }
-            if (!mbar_wait(bar_ready + 8 * buf, rc[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-            rc[buf]++;
+            if (!mbar_wait(bar_ready, rc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+            rc++;
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < BS / 16; kk++)
-              umma_f16_ss(tmem + 256, desc_k(sDS + buf * C::PS_BYTES, BT, kk), desc_mn(sk, BS, kk), idesc_g, (jj > 0 || kk > 0));
-            umma_commit(bar_gdone + 8 * buf);
+              umma_f16_ss(tmem + 256, desc_k(sDS, BT, kk), desc_mn(sk, BS, kk), idesc_g, (jj > 0 || kk > 0));
+            umma_commit(bar_gdone);
             umma_commit(bar_kvfree + 8 * s);
           }
         }
       }
     }
-  } else {
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+  } else if (live) {
+    const int row = tid & 127, half = tid >> 7;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    int sfc[2] = {0, 0}, uses[2] = {0, 0}, obs[2] = {0, 0};
+    int sfc[2] = {0, 0}, uses = 0, obs = 0, epc = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x) {
       int b, h, q0, n;
       decode(w, b, h, q0, n);
-      const int qpos = q0 + tid;
+      const int qpos = q0 + row;
       const bool qvalid = qpos < p.T;
       const size_t sidx = ((size_t)b * p.H + h) * p.T + qpos;
       const float my_lse = qvalid ? p.lse[sidx] * LOG2E : INFINITY;
@@ -1208,75 +1228,80 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_fence_after();
         const int k0 = j * BS;
         const bool diag = k0 + BS - 1 > q0;
-        while (obs[buf] < uses[buf]) {
-          if (!mbar_wait(bar_gdone + 8 * buf, obs[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-          obs[buf]++;
+        const int c = half * 32;
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + buf * 64 + lane_off + c, rs);
+        tmem_ld32(tmem + 128 + buf * 64 + lane_off + c, rd);
+        tmem_ld_wait();
+        uint32_t ds[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            float pr = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -my_lse));
+            if (diag && k0 + c + e + u > qpos) pr = 0.f;
+            dv[u] = pr * (__uint_as_float(rd[e + u]) - my_delta) * p.scale;
+          }
+          ds[e >> 1] = pack_bf16(dv[0], dv[1]);
+        }
+        while (obs < uses) {
+          if (!mbar_wait(bar_gdone, obs & 1, abort_flag, 6, p.err)) { ok = false; break; }
+          obs++;
         }
         if (!ok) break;
-#pragma unroll 1
-        for (int c = 0; c < BS; c += 32) {
-          uint32_t rs[32], rd[32];
-          tmem_ld32(tmem + buf * 64 + lane_off + c, rs);
-          tmem_ld32(tmem + 128 + buf * 64 + lane_off + c, rd);
-          tmem_ld_wait();
-          uint32_t ds[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float dv[2];
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-              float pr = exp2f(__uint_as_float(rs[e + u]) * sl2 - my_lse);
-              if (diag && k0 + c + e + u > qpos) pr = 0.f;
-              dv[u] = pr * (__uint_as_float(rd[e + u]) - my_delta) * p.scale;
-            }
-            ds[e >> 1] = pack_bf16(dv[0], dv[1]);
-          }
-#pragma unroll
-          for (int g = 0; g < 4; g++)
-            st_shared_v4(chunk_addr(sDS + buf * C::PS_BYTES, BT, tid, (c >> 3) + g), ds[4 * g], ds[4 * g + 1], ds[4 * g + 2], ds[4 * g + 3]);
-        }
-        uses[buf]++;
+        for (int g = 0; g < 4; g++)
+          st_shared_v4(chunk_addr(sDS, BT, row, (c >> 3) + g), ds[4 * g], ds[4 * g + 1], ds[4 * g + 2], ds[4 * g + 3]);
+        uses++;
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ready + 8 * buf);
+        if (lane == 0) mbar_arrive(bar_ready);
       }
       if (!ok) break;
-      {
-        const int buf = (n - 1) & 1;
-        while (obs[buf] < uses[buf]) {
-          if (!mbar_wait(bar_gdone + 8 * buf, obs[buf] & 1, abort_flag, 6, p.err)) { ok = false; break; }
-          obs[buf]++;
-        }
-        if (!ok) break;
+      while (obs < uses) {
+        if (!mbar_wait(bar_gdone, obs & 1, abort_flag, 6, p.err)) { ok = false; break; }
+        obs++;
       }
+      if (!ok) break;
       tc_fence_after();
-      bf16* dq = p.dqkv + (size_t)(b * p.T + qpos) * p.ld + h * HD;
+      // dQ: TMEM -> bf16 -> staging tile (the dS buffer and the 16 KB behind it) -> one TMA store per slab
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
         uint32_t r1[32];
         tmem_ld32(tmem + 256 + lane_off + c, r1);
         tmem_ld_wait();
-        if (qvalid) {
 #pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(r1[8 * g]), __uint_as_float(r1[8 * g + 1]));
-            o.y = pack_bf16(__uint_as_float(r1[8 * g + 2]), __uint_as_float(r1[8 * g + 3]));
-            o.z = pack_bf16(__uint_as_float(r1[8 * g + 4]), __uint_as_float(r1[8 * g + 5]));
-            o.w = pack_bf16(__uint_as_float(r1[8 * g + 6]), __uint_as_float(r1[8 * g + 7]));
-            *reinterpret_cast<uint4*>(dq + c + 8 * g) = o;
-          }
-        }
+        for (int g = 0; g < 4; g++)
+          st_shared_v4(chunk_addr(sDS, BT, row, (c >> 3) + g),
+                       pack_bf16(__uint_as_float(r1[8 * g]), __uint_as_float(r1[8 * g + 1])),
+                       pack_bf16(__uint_as_float(r1[8 * g + 2]), __uint_as_float(r1[8 * g + 3])),
+                       pack_bf16(__uint_as_float(r1[8 * g + 4]), __uint_as_float(r1[8 * g + 5])),
+                       pack_bf16(__uint_as_float(r1[8 * g + 6]), __uint_as_float(r1[8 * g + 7])));
       }
+      fence_proxy_async_smem();
+      mbar_arrive(bar_epi);
+      if (!mbar_wait(bar_epi, epc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+      epc++;
+      if (tid == 0) {
+#pragma unroll
+        for (int sl = 0; sl < HD / 64; sl++) tma_store_3d(&map_dqkv, sDS + sl * C::PS_BYTES, h * HD + sl * 64, q0, b);
+        bulk_commit();
+        bulk_wait_read_all();
+      }
+      mbar_arrive(bar_epi);
+      if (!mbar_wait(bar_epi, epc & 1, abort_flag, 6, p.err)) { ok = false; break; }
+      epc++;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_accfree);
     }
+    if (tid == 0) bulk_wait_all();
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
 }
 
 template <typename K>
@@ -1299,13 +1324,16 @@ int launch_fwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
     if (!mkv) return -1;
     static bool once_ws = false;
     if (!once_ws) { if (set_smem(flash_fwd_ws_kernel<HD>, C::SMEM, "flash_fwd")) return -1; once_ws = true; }
-    const int n_pairs = (p.T + 255) / 256;
-    const int n_items = p.B * p.H * n_pairs;
+    const int n_qt = (p.T + 127) / 128;
+    const int n_items = p.B * p.H * n_qt;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
-    KH_LAUNCH((flash_fwd_ws_kernel<HD>), n_items < sms ? n_items : sms, C::THREADS, C::SMEM, st, *mq, *mkv, p, n_items, n_pairs);
+    const int ctas = 2 * sms;                  // two CTAs per SM
+    const CUtensorMap* mo = kh_tmap_3d_bf16(p.out, (uint64_t)p.H * HD, p.T, p.B, (uint64_t)p.H * HD, (uint64_t)p.T * p.H * HD, 128, 64);
+    if (!mo) return -1;
+    KH_LAUNCH((flash_fwd_ws_kernel<HD>), n_items < ctas ? n_items : ctas, C::THREADS, C::SMEM, st, *mq, *mkv, *mo, p, n_items, n_qt);
     KH_LAUNCH_CHECK("flash_fwd");
     return 0;
   }
@@ -1344,8 +1372,10 @@ int launch_bwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     const int grid = n_items < sms ? n_items : sms;
-    KH_LAUNCH((flash_dkv_ws_kernel<HD>), grid, C::THREADS, C::SMEM_KV, st, *mq, *mq64, *md64, p, n_items, n_t);
-    KH_LAUNCH((flash_dq_ws_kernel<HD>), grid, C::THREADS, C::SMEM_Q, st, *mq, *md, *mq64, p, n_items, n_t);
+    const CUtensorMap* mg = kh_tmap_3d_bf16(p.dqkv, (uint64_t)3 * p.H * HD, p.T, p.B, (uint64_t)p.ld, (uint64_t)p.T * p.ld, 128, 64);
+    if (!mg) return -1;
+    KH_LAUNCH((flash_dkv_ws_kernel<HD>), grid, C::THREADS, C::SMEM_KV, st, *mq, *mq64, *md64, *mg, p, n_items, n_t);
+    KH_LAUNCH((flash_dq_ws_kernel<HD>), grid, C::THREADS, C::SMEM_Q, st, *mq, *md, *mq64, *mg, p, n_items, n_t);
     KH_LAUNCH_CHECK("flash_bwd");
     return 0;
   }

@@ -187,6 +187,55 @@ const CUtensorMap* kh_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t col
   return m;
 }
 
+const CUtensorMap* kh_tmap_3d_bf16(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t ld1, uint64_t ld2,
+                                   uint32_t box_d1, uint32_t box_d0) {
+  struct Key3 {
+    uint64_t v[6];
+    uint32_t b[2];
+    bool operator==(const Key3& o) const { return memcmp(this, &o, sizeof(Key3)) == 0; }
+  };
+  struct Hash3 {
+    size_t operator()(const Key3& k) const {
+      uint64_t h = 0x9E3779B97F4A7C15ull;
+      for (int i = 0; i < 6; i++) h ^= (k.v[i] + 0x632BE59BD9B4E019ull) + (h << 6) + (h >> 2);
+      h ^= ((uint64_t)k.b[0] << 32 | k.b[1]) + (h << 6) + (h >> 2);
+      return (size_t)h;
+    }
+  };
+  static std::unordered_map<Key3, CUtensorMap*, Hash3> cache;
+  static std::mutex mu;
+  Key3 key;
+  memset(&key, 0, sizeof(key));
+  key.v[0] = (uint64_t)base; key.v[1] = d0; key.v[2] = d1; key.v[3] = d2; key.v[4] = ld1; key.v[5] = ld2;
+  key.b[0] = box_d1; key.b[1] = box_d0;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { kh_set_error("cuTensorMapEncodeTiled is not available from the driver"); return nullptr; }
+  if (((uint64_t)base & 15) || ((ld1 * 2) & 15) || ((ld2 * 2) & 15)) {
+    kh_set_error("TMA operand needs a 16-byte aligned base and pitches (base %p, pitches %llu / %llu elements)", base,
+                 (unsigned long long)ld1, (unsigned long long)ld2);
+    return nullptr;
+  }
+  CUtensorMap* m = new CUtensorMap;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {ld1 * 2, ld2 * 2};
+  cuuint32_t box[3] = {box_d0, box_d1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    delete m;
+    kh_set_error("cuTensorMapEncodeTiled (3-D) failed with %d", (int)rc);
+    return nullptr;
+  }
+  if (cache.size() >= g_tmap_limit) cache.clear();      // descriptors stay allocated, see kh_tmap_2d_bf16
+  cache[key] = m;
+  return m;
+}
+
 // ------------------------------------------------------------------------------- kernel
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_BIAS_RESID = 3, EPI_DGELU = 4, EPI_RESID = 5 };
 
