@@ -11,19 +11,17 @@
 // operand (contraction over hd) or as an MN-major operand (contraction over rows) just by
 // changing the UMMA descriptor -- e.g. V for O = P V, dO for dV = P^T dO, Q for dK = dS^T Q.
 //
-// forward   CTA = (128 queries, head, batch); S = Q K^T into TMEM, one thread per query row
-//           does the online softmax straight out of TMEM, P goes to shared memory as bf16 and
-//           P V lands in a second TMEM region that is folded into register accumulators.
-//           Two CTAs share an SM, so one CTA's softmax overlaps the other's MMAs.
-// backward  delta = rowsum(dO * O); a dK/dV kernel per key tile (S^T, dP^T, dV += P^T dO,
-//           dK += dS^T Q accumulated in TMEM) and a dQ kernel per query tile (S, dP,
-//           dQ += dS K).  No atomics: every output element is produced by exactly one CTA
-//           in a fixed order, so gradients are reproducible bit for bit.
+// All three kernels are persistent and warp-specialised: a TMA warp streams operand tiles through
+// mbarrier-guarded rings, one lane of an MMA warp issues every tcgen05.mma, and the remaining warps
+// own the rows of the CTA's tile (softmax in the forward pass, P / dS in the backward pass).  S, dP
+// and the accumulators (O; dK and dV; dQ) live in TMEM; finished tiles are staged in shared memory
+// and written with TMA stores.  Details stand in front of each kernel.
+// backward  delta = rowsum(dO * O); a dK/dV kernel per key tile and a dQ kernel per query tile.
+//           No atomics: every output element is produced by exactly one CTA in a fixed order, so
+//           gradients are reproducible bit for bit.
 //
 // All mbarrier waits are bounded (error word code 6); after a timeout the CTA skips its
 // stores, releases TMEM and returns.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 #define KH_LAUNCH_CHECK(name)                                                     \
@@ -55,182 +53,22 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* m, ui
 #pragma unroll
   for (int s = 0; s < HD / 64; s++) tma_load_2d(dst + s * rows * 128, m, bar, col0 + s * 64, row0);
 }
-// descriptor for contraction over the tile's columns (K-major), k-step kk of 16 columns
-__device__ __forceinline__ uint64_t desc_k(uint32_t base, int rows, int kk) {
-  return umma_desc_sw128(base + (kk >> 2) * rows * 128 + (kk & 3) * 32, 16, 1024);
-}
-// descriptor for contraction over the tile's rows (MN-major), k-step kk of 16 rows
-__device__ __forceinline__ uint64_t desc_mn(uint32_t base, int rows, int kk) {
-  return umma_desc_sw128(base + kk * 2048, rows * 128, 1024);
-}
+// UMMA descriptors.  Contraction over the tile's columns (K-major): k-step kk of 16 columns starts
+// (kk >> 2) slabs + (kk & 3) * 32 bytes into the tile.  Contraction over the tile's rows (MN-major):
+// k-step kk of 16 rows starts kk * 2048 bytes in, slabs are `rows * 128` bytes apart (LBO).
+// The MMA warp's single lane issues every product of a CTA, so its instruction count per tcgen05.mma
+// bounds the rate: descriptors are built once per tile (dk0 / dmn0) and advanced by compile-time
+// constants per k-step (one 64-bit add each).
+__device__ __forceinline__ uint64_t dk0(uint32_t base) { return umma_desc_sw128(base, 16, 1024); }
+__device__ __forceinline__ uint64_t dmn0(uint32_t base, int rows) { return umma_desc_sw128(base, rows * 128, 1024); }
+#define DK(d0, rows, kk) ((d0) + (uint64_t)((((kk) >> 2) * (rows) * 128 + ((kk) & 3) * 32) >> 4))
+#define DMN(d0, kk) ((d0) + (uint64_t)(((kk) * 2048) >> 4))
 // address of the 16-byte chunk (row, chunk c of 8 bf16) in a K-major tile with `rows` rows
 __device__ __forceinline__ uint32_t chunk_addr(uint32_t base, int rows, int row, int c) {
   return base + (c >> 3) * rows * 128 + row * 128 + (((c & 7) ^ (row & 7)) << 4);
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-
-// ================================================================================ forward
-template <int HD, int BKV>
-__global__ void __launch_bounds__(128, 2)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const AttnParams p) {
-  constexpr int BQ = 128;
-  constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
-  constexpr int TMEM_COLS = 256;          // S: BKV columns at 0, PV: HD columns at 128
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + KV_BYTES, sP = sV + KV_BYTES;
-  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(al + Q_BYTES + 2 * KV_BYTES + P_BYTES);
-  const uint32_t bar_q = smem_u32(bars), bar_k = bar_q + 8, bar_v = bar_q + 16, bar_s = bar_q + 24, bar_o = bar_q + 32;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int d = p.H * HD;
-  const int q0 = qt * BQ;                              // first query position of the tile
-  const int row0 = b * p.T + q0;                       // its row in qkv
-  const int n_kv = min((q0 + BQ + BKV - 1) / BKV, (p.T + BKV - 1) / BKV);
-
-  if (tid == 0) {
-    for (int i = 0; i < 5; i++) mbar_init(bar_q + 8 * i, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&map_q);
-    tma_prefetch_desc(&map_kv);
-  }
-  if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  pdl_wait();
-  pdl_launch_dependents();
-  const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, Q_BYTES);
-    load_tile<HD>(sQ, &map_q, bar_q, h * HD, row0, BQ);
-    mbar_expect_tx(bar_k, KV_BYTES);
-    load_tile<HD>(sK, &map_kv, bar_k, d + h * HD, b * p.T, BKV);
-    mbar_expect_tx(bar_v, KV_BYTES);
-    load_tile<HD>(sV, &map_kv, bar_v, 2 * d + h * HD, b * p.T, BKV);
-  }
-  constexpr uint32_t idesc_s = umma_idesc_bf16(128, BKV, 0, 0);
-  constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
-  const float sl2 = p.scale * LOG2E;
-
-  float o_acc[HD];
-#pragma unroll
-  for (int i = 0; i < HD; i++) o_acc[i] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-  const int qpos = q0 + tid;
-  bool ok = true;
-
-  for (int j = 0; j < n_kv; j++) {
-    const uint32_t ph = j & 1;
-    if (tid == 0) {
-      if (j == 0) ok = mbar_wait(bar_q, 0, abort_flag, 6, p.err);
-      ok = ok && mbar_wait(bar_k, ph, abort_flag, 6, p.err);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sQ, BQ, kk), desc_k(sK, BKV, kk), idesc_s, kk > 0);
-        umma_commit(bar_s);
-      }
-    }
-    if (!mbar_wait(bar_s, ph, abort_flag, 6, p.err)) { ok = false; break; }
-    tc_fence_after();
-    if (tid == 0 && j + 1 < n_kv) {     // K tile is free again
-      mbar_expect_tx(bar_k, KV_BYTES);
-      load_tile<HD>(sK, &map_kv, bar_k, d + h * HD, b * p.T + (j + 1) * BKV, BKV);
-    }
-    // ---- online softmax on this thread's query row
-    const int k0 = j * BKV;
-    const bool need_mask = k0 + BKV - 1 > q0;
-    float m_new = m_run;
-#pragma unroll 1
-    for (int c = 0; c < BKV; c += 32) {
-      uint32_t r[32];
-      tmem_ld32(tS + lane_off + c, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; i++) {
-        float s = __uint_as_float(r[i]) * sl2;
-        if (need_mask && k0 + c + i > qpos) s = -INFINITY;
-        m_new = fmaxf(m_new, s);
-      }
-    }
-    const float alpha = exp2f(m_run - m_new);
-    float rowsum = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < BKV; c += 32) {
-      uint32_t r[32];
-      tmem_ld32(tS + lane_off + c, r);
-      tmem_ld_wait();
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float s0 = __uint_as_float(r[i]) * sl2, s1 = __uint_as_float(r[i + 1]) * sl2;
-        if (need_mask && k0 + c + i > qpos) s0 = -INFINITY;
-        if (need_mask && k0 + c + i + 1 > qpos) s1 = -INFINITY;
-        float p0 = exp2f(s0 - m_new), p1 = exp2f(s1 - m_new);
-        rowsum += p0 + p1;
-        pk[i >> 1] = pack_bf16(p0, p1);
-      }
-#pragma unroll
-      for (int g = 0; g < 4; g++)
-        st_shared_v4(chunk_addr(sP, BQ, tid, (c >> 3) + g), pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-    }
-    l_run = l_run * alpha + rowsum;
-    m_run = m_new;
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      ok = mbar_wait(bar_v, ph, abort_flag, 6, p.err);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BKV / 16; kk++) umma_f16_ss(tO, desc_k(sP, BQ, kk), desc_mn(sV, BKV, kk), idesc_o, kk > 0);
-        umma_commit(bar_o);
-      }
-    }
-    if (!mbar_wait(bar_o, ph, abort_flag, 6, p.err)) { ok = false; break; }
-    tc_fence_after();
-    if (tid == 0 && j + 1 < n_kv) {     // V and P are free again
-      mbar_expect_tx(bar_v, KV_BYTES);
-      load_tile<HD>(sV, &map_kv, bar_v, 2 * d + h * HD, b * p.T + (j + 1) * BKV, BKV);
-    }
-#pragma unroll
-    for (int c = 0; c < HD; c += 32) {
-      uint32_t r[32];
-      tmem_ld32(tO + lane_off + c, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; i++) o_acc[c + i] = o_acc[c + i] * alpha + __uint_as_float(r[i]);
-    }
-    tc_fence_before();
-  }
-
-  if (ok && !*abort_flag && qpos < p.T) {
-    const float inv = 1.f / l_run;
-    bf16* op = p.out + (size_t)(row0 + tid) * d + h * HD;
-#pragma unroll
-    for (int c = 0; c < HD; c += 8) {
-      uint4 o;
-      o.x = pack_bf16(o_acc[c] * inv, o_acc[c + 1] * inv); o.y = pack_bf16(o_acc[c + 2] * inv, o_acc[c + 3] * inv);
-      o.z = pack_bf16(o_acc[c + 4] * inv, o_acc[c + 5] * inv); o.w = pack_bf16(o_acc[c + 6] * inv, o_acc[c + 7] * inv);
-      *reinterpret_cast<uint4*>(op + c) = o;
-    }
-    if (p.lse) p.lse[((size_t)b * p.H + h) * p.T + qpos] = (m_run + log2f(l_run)) / LOG2E;
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
 // ================================================================================ forward, warp-specialised
@@ -340,6 +178,7 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
       int ic = 0, pc = 0, kvc = 0;
       bool ok = true;
+      const uint64_t dQ0 = dk0(sQ), dP0 = dk0(sP);
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
         int b, h, q0, n;
         decode(w, b, h, q0, n);
@@ -353,8 +192,9 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_fence_after();
             const uint32_t sk = sKV + s * 2 * C::KV_BYTES;
             const uint32_t tS = tmem + (j & 1) * 64;
+            const uint64_t dK0 = dk0(sk);
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sQ, BQ, kk), desc_k(sk, BKV, kk), idesc_s, kk > 0);
+            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, DK(dQ0, BQ, kk), DK(dK0, BKV, kk), idesc_s, kk > 0);
             umma_commit(bar_sfull + 8 * (j & 1));
             umma_commit(bar_kfree + 8 * s);
             if (j == n - 1) umma_commit(bar_qfree);         // last use of this item's Q
@@ -369,9 +209,10 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (!mbar_wait(bar_pready, pc & 1, abort_flag, 6, p.err)) { ok = false; break; }
             pc++;
             tc_fence_after();
+            const uint64_t dV0 = dmn0(sv, BKV);
 #pragma unroll
             for (int kk = 0; kk < BKV / 16; kk++)
-              umma_f16_ss(tmem + 128, desc_k(sP, BQ, kk), desc_mn(sv, BKV, kk), idesc_o, (jj > 0 || kk > 0));
+              umma_f16_ss(tmem + 128, DK(dP0, BQ, kk), DMN(dV0, kk), idesc_o, (jj > 0 || kk > 0));
             umma_commit(bar_odone);
             umma_commit(bar_vfree + 8 * s);
           }
@@ -514,331 +355,34 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 }
 
 // ================================================================================ delta
-// delta[b,h,t] = sum_e dO[b,t,h,e] * O[b,t,h,e]; one warp per (row, head)
+// delta[b,h,t] = sum_e dO[b,t,h,e] * O[b,t,h,e].  One warp per row of O / dO: the lanes read the row in
+// 16-byte pieces (512 contiguous bytes per step), a head is HD / 8 adjacent lanes, summed with shuffles.
+template <int HD>
 __global__ void flash_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout, float* __restrict__ delta,
-                                   int B, int T, int H, int hd) {
+                                   int B, int T, int H) {
   pdl_wait();
   pdl_launch_dependents();
-  const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (w >= (long)B * T * H) return;
-  const long row = w / H;
-  const int h = (int)(w % H);
-  const bf16* a = o + row * H * hd + (long)h * hd;
-  const bf16* g = dout + row * H * hd + (long)h * hd;
-  float s = 0.f;
-  for (int e = lane * 2; e < hd; e += 64) {
-    float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(a + e)), y = unpack_bf16(*reinterpret_cast<const uint32_t*>(g + e));
-    s += x.x * y.x + x.y * y.y;
+  if (row >= (long)B * T) return;
+  constexpr int LPH = HD / 8;                      // lanes per head
+  const int d = H * HD;
+  const uint4* a = reinterpret_cast<const uint4*>(o + row * d);
+  const uint4* g = reinterpret_cast<const uint4*>(dout + row * d);
+  const int b = (int)(row / T), t = (int)(row % T);
+  for (int c0 = 0; c0 < d / 8; c0 += 32) {
+    const int c = c0 + lane;
+    float s = 0.f;
+    if (c < d / 8) {
+      const uint4 x = __ldg(a + c), y = __ldg(g + c);
+      const float2 x0 = unpack_bf16(x.x), x1 = unpack_bf16(x.y), x2 = unpack_bf16(x.z), x3 = unpack_bf16(x.w);
+      const float2 y0 = unpack_bf16(y.x), y1 = unpack_bf16(y.y), y2 = unpack_bf16(y.z), y3 = unpack_bf16(y.w);
+      s = (x0.x * y0.x + x0.y * y0.y) + (x1.x * y1.x + x1.y * y1.y) + (x2.x * y2.x + x2.y * y2.y) + (x3.x * y3.x + x3.y * y3.y);
+    }
+#pragma unroll
+    for (int off = LPH / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (c < d / 8 && (lane % LPH) == 0) delta[((size_t)b * H + c / LPH) * T + t] = s;
   }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
-    const int b = (int)(row / T), t = (int)(row % T);
-    delta[((size_t)b * H + h) * T + t] = s;
-  }
-}
-
-// ================================================================================ dK / dV
-// CTA = (128 keys, head, batch); loops over the query tiles i >= j.  One thread per key row.
-template <int HD>
-__global__ void __launch_bounds__(128, 1)
-flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const AttnParams p) {
-  constexpr int BT = 128;
-  constexpr int TILE = BT * HD * 2, PT_BYTES = BT * BT * 2;
-  constexpr int TMEM_COLS = 512;      // S^T 0..127, dP^T 128..255, dV 256.., dK 256+HD..
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sK = base, sV = sK + TILE, sQ = sV + TILE, sDO = sQ + TILE, sP = sDO + TILE, sDS = sP + PT_BYTES;
-  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
-  float* s_lse = reinterpret_cast<float*>(al + 4 * TILE + 2 * PT_BYTES);
-  float* s_delta = s_lse + BT;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + BT);
-  const uint32_t bar_kv = smem_u32(bars), bar_q = bar_kv + 8, bar_s = bar_kv + 16, bar_g = bar_kv + 24;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int jt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int d = p.H * HD;
-  const int k0 = jt * BT;
-  const int n_qt = (p.T + BT - 1) / BT;
-
-  if (tid == 0) {
-    for (int i = 0; i < 4; i++) mbar_init(bar_kv + 8 * i, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&map_qkv);
-    tma_prefetch_desc(&map_do);
-  }
-  if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  pdl_wait();
-  pdl_launch_dependents();
-  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 256 + HD;
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_kv, 2 * TILE);
-    load_tile<HD>(sK, &map_qkv, bar_kv, d + h * HD, b * p.T + k0, BT);
-    load_tile<HD>(sV, &map_qkv, bar_kv, 2 * d + h * HD, b * p.T + k0, BT);
-    mbar_expect_tx(bar_q, 2 * TILE);
-    load_tile<HD>(sQ, &map_qkv, bar_q, h * HD, b * p.T + jt * BT, BT);
-    load_tile<HD>(sDO, &map_do, bar_q, h * HD, b * p.T + jt * BT, BT);
-  }
-  constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_g = umma_idesc_bf16(128, HD, 0, 1);
-  const float sl2 = p.scale * LOG2E;
-  const int kpos = k0 + tid;
-  bool ok = true;
-  int it = 0;
-  for (int i = jt; i < n_qt; i++, it++) {
-    const uint32_t ph = it & 1;
-    const int q0 = i * BT;
-    // per-query statistics of this tile
-    {
-      const int qp = q0 + tid;
-      const size_t idx = ((size_t)b * p.H + h) * p.T + qp;
-      s_lse[tid] = qp < p.T ? p.lse[idx] * LOG2E : INFINITY;
-      s_delta[tid] = qp < p.T ? p.delta[idx] : 0.f;
-    }
-    if (tid == 0) {
-      if (it == 0) ok = mbar_wait(bar_kv, 0, abort_flag, 6, p.err);
-      ok = ok && mbar_wait(bar_q, ph, abort_flag, 6, p.err);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sK, BT, kk), desc_k(sQ, BT, kk), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tDP, desc_k(sV, BT, kk), desc_k(sDO, BT, kk), idesc_s, kk > 0);
-        umma_commit(bar_s);
-      }
-    }
-    __syncthreads();   // s_lse / s_delta visible
-    if (!mbar_wait(bar_s, ph, abort_flag, 6, p.err)) { ok = false; break; }
-    tc_fence_after();
-    const bool diag = (i == jt);
-#pragma unroll 1
-    for (int c = 0; c < BT; c += 32) {
-      uint32_t rs[32], rd[32];
-      tmem_ld32(tS + lane_off + c, rs);
-      tmem_ld32(tDP + lane_off + c, rd);
-      tmem_ld_wait();
-      uint32_t pp[16], ds[16];
-#pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float pv[2], dv[2];
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int qi = c + e + u;
-          float pr = exp2f(__uint_as_float(rs[e + u]) * sl2 - s_lse[qi]);
-          if (diag && kpos > q0 + qi) pr = 0.f;
-          pv[u] = pr;
-          dv[u] = pr * (__uint_as_float(rd[e + u]) - s_delta[qi]) * p.scale;
-        }
-        pp[e >> 1] = pack_bf16(pv[0], pv[1]);
-        ds[e >> 1] = pack_bf16(dv[0], dv[1]);
-      }
-#pragma unroll
-      for (int g = 0; g < 4; g++) {
-        st_shared_v4(chunk_addr(sP, BT, tid, (c >> 3) + g), pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
-        st_shared_v4(chunk_addr(sDS, BT, tid, (c >> 3) + g), ds[4 * g], ds[4 * g + 1], ds[4 * g + 2], ds[4 * g + 3]);
-      }
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < BT / 16; kk++) umma_f16_ss(tDV, desc_k(sP, BT, kk), desc_mn(sDO, BT, kk), idesc_g, (it > 0 || kk > 0));
-#pragma unroll
-      for (int kk = 0; kk < BT / 16; kk++) umma_f16_ss(tDK, desc_k(sDS, BT, kk), desc_mn(sQ, BT, kk), idesc_g, (it > 0 || kk > 0));
-      umma_commit(bar_g);
-    }
-    if (!mbar_wait(bar_g, ph, abort_flag, 6, p.err)) { ok = false; break; }
-    tc_fence_after();
-    if (tid == 0 && i + 1 < n_qt) {
-      mbar_expect_tx(bar_q, 2 * TILE);
-      load_tile<HD>(sQ, &map_qkv, bar_q, h * HD, b * p.T + (i + 1) * BT, BT);
-      load_tile<HD>(sDO, &map_do, bar_q, h * HD, b * p.T + (i + 1) * BT, BT);
-    }
-    __syncthreads();   // s_lse / s_delta may be overwritten by the next iteration
-  }
-
-  if (ok && !*abort_flag) {
-    const bool store = kpos < p.T;
-    bf16* dk = p.dqkv + (size_t)(b * p.T + kpos) * p.ld + d + h * HD;
-    bf16* dv = p.dqkv + (size_t)(b * p.T + kpos) * p.ld + 2 * d + h * HD;
-#pragma unroll 1
-    for (int c = 0; c < HD; c += 32) {
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tDV + lane_off + c, r1);
-      tmem_ld32(tDK + lane_off + c, r2);
-      tmem_ld_wait();
-      if (store) {
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(r1[8 * g]), __uint_as_float(r1[8 * g + 1]));
-          o.y = pack_bf16(__uint_as_float(r1[8 * g + 2]), __uint_as_float(r1[8 * g + 3]));
-          o.z = pack_bf16(__uint_as_float(r1[8 * g + 4]), __uint_as_float(r1[8 * g + 5]));
-          o.w = pack_bf16(__uint_as_float(r1[8 * g + 6]), __uint_as_float(r1[8 * g + 7]));
-          *reinterpret_cast<uint4*>(dv + c + 8 * g) = o;
-          o.x = pack_bf16(__uint_as_float(r2[8 * g]), __uint_as_float(r2[8 * g + 1]));
-          o.y = pack_bf16(__uint_as_float(r2[8 * g + 2]), __uint_as_float(r2[8 * g + 3]));
-          o.z = pack_bf16(__uint_as_float(r2[8 * g + 4]), __uint_as_float(r2[8 * g + 5]));
-          o.w = pack_bf16(__uint_as_float(r2[8 * g + 6]), __uint_as_float(r2[8 * g + 7]));
-          *reinterpret_cast<uint4*>(dk + c + 8 * g) = o;
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
-}
-
-// ================================================================================ dQ
-// CTA = (128 queries, head, batch); loops over the key tiles j <= i.  One thread per query row.
-template <int HD>
-__global__ void __launch_bounds__(128, 1)
-flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const AttnParams p) {
-  constexpr int BT = 128;
-  constexpr int TILE = BT * HD * 2, PT_BYTES = BT * BT * 2;
-  constexpr int TMEM_COLS = 512;      // S 0..127, dP 128..255, dQ 256..
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sDO = sQ + TILE, sK = sDO + TILE, sV = sK + TILE, sDS = sV + TILE;
-  uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(al + 4 * TILE + PT_BYTES);
-  const uint32_t bar_q = smem_u32(bars), bar_kv = bar_q + 8, bar_s = bar_q + 16, bar_g = bar_q + 24;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int d = p.H * HD;
-  const int q0 = qt * BT;
-
-  if (tid == 0) {
-    for (int i = 0; i < 4; i++) mbar_init(bar_q + 8 * i, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&map_qkv);
-    tma_prefetch_desc(&map_do);
-  }
-  if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  pdl_wait();
-  pdl_launch_dependents();
-  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, 2 * TILE);
-    load_tile<HD>(sQ, &map_qkv, bar_q, h * HD, b * p.T + q0, BT);
-    load_tile<HD>(sDO, &map_do, bar_q, h * HD, b * p.T + q0, BT);
-    mbar_expect_tx(bar_kv, 2 * TILE);
-    load_tile<HD>(sK, &map_qkv, bar_kv, d + h * HD, b * p.T, BT);
-    load_tile<HD>(sV, &map_qkv, bar_kv, 2 * d + h * HD, b * p.T, BT);
-  }
-  constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_g = umma_idesc_bf16(128, HD, 0, 1);
-  const float sl2 = p.scale * LOG2E;
-  const int qpos = q0 + tid;
-  const bool qvalid = qpos < p.T;
-  const size_t sidx = ((size_t)b * p.H + h) * p.T + qpos;
-  const float my_lse = qvalid ? p.lse[sidx] * LOG2E : INFINITY;
-  const float my_delta = qvalid ? p.delta[sidx] : 0.f;
-  bool ok = true;
-  const int n_kv = qt + 1;
-  for (int j = 0; j < n_kv; j++) {
-    const uint32_t ph = j & 1;
-    if (tid == 0) {
-      if (j == 0) ok = mbar_wait(bar_q, 0, abort_flag, 6, p.err);
-      ok = ok && mbar_wait(bar_kv, ph, abort_flag, 6, p.err);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sQ, BT, kk), desc_k(sK, BT, kk), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tDP, desc_k(sDO, BT, kk), desc_k(sV, BT, kk), idesc_s, kk > 0);
-        umma_commit(bar_s);
-      }
-    }
-    if (!mbar_wait(bar_s, ph, abort_flag, 6, p.err)) { ok = false; break; }
-    tc_fence_after();
-    const bool diag = (j == qt);
-    const int k0 = j * BT;
-#pragma unroll 1
-    for (int c = 0; c < BT; c += 32) {
-      uint32_t rs[32], rd[32];
-      tmem_ld32(tS + lane_off + c, rs);
-      tmem_ld32(tDP + lane_off + c, rd);
-      tmem_ld_wait();
-      uint32_t ds[16];
-#pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float dv[2];
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          float pr = exp2f(__uint_as_float(rs[e + u]) * sl2 - my_lse);
-          if (diag && k0 + c + e + u > qpos) pr = 0.f;
-          dv[u] = pr * (__uint_as_float(rd[e + u]) - my_delta) * p.scale;
-        }
-        ds[e >> 1] = pack_bf16(dv[0], dv[1]);
-      }
-#pragma unroll
-      for (int g = 0; g < 4; g++)
-        st_shared_v4(chunk_addr(sDS, BT, tid, (c >> 3) + g), ds[4 * g], ds[4 * g + 1], ds[4 * g + 2], ds[4 * g + 3]);
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < BT / 16; kk++) umma_f16_ss(tDQ, desc_k(sDS, BT, kk), desc_mn(sK, BT, kk), idesc_g, (j > 0 || kk > 0));
-      umma_commit(bar_g);
-    }
-    if (!mbar_wait(bar_g, ph, abort_flag, 6, p.err)) { ok = false; break; }
-    tc_fence_after();
-    if (tid == 0 && j + 1 < n_kv) {
-      mbar_expect_tx(bar_kv, 2 * TILE);
-      load_tile<HD>(sK, &map_qkv, bar_kv, d + h * HD, b * p.T + (j + 1) * BT, BT);
-      load_tile<HD>(sV, &map_qkv, bar_kv, 2 * d + h * HD, b * p.T + (j + 1) * BT, BT);
-    }
-  }
-  if (ok && !*abort_flag) {
-    bf16* dq = p.dqkv + (size_t)(b * p.T + qpos) * p.ld + h * HD;
-#pragma unroll 1
-    for (int c = 0; c < HD; c += 32) {
-      uint32_t r1[32];
-      tmem_ld32(tDQ + lane_off + c, r1);
-      tmem_ld_wait();
-      if (qvalid) {
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(r1[8 * g]), __uint_as_float(r1[8 * g + 1]));
-          o.y = pack_bf16(__uint_as_float(r1[8 * g + 2]), __uint_as_float(r1[8 * g + 3]));
-          o.z = pack_bf16(__uint_as_float(r1[8 * g + 4]), __uint_as_float(r1[8 * g + 5]));
-          o.w = pack_bf16(__uint_as_float(r1[8 * g + 6]), __uint_as_float(r1[8 * g + 7]));
-          *reinterpret_cast<uint4*>(dq + c + 8 * g) = o;
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
 // ================================================================================ backward, warp-specialised
@@ -935,6 +479,7 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, HD, 0, 1);
       int ic = 0, qc = 0, rc = 0;
       bool ok = true;
+      const uint64_t dK0 = dk0(sK), dV0 = dk0(sV), dP0 = dk0(sP), dDS0 = dk0(sDS);
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
         int b, h, k0, n;
         decode(w, b, h, k0, n);
@@ -948,10 +493,12 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
             tc_fence_after();
             const uint32_t sq = sQD + s * 2 * C::SUB, sdo = sq + C::SUB;
             const uint32_t tS = tmem + (t & 1) * 64, tDP = tmem + 128 + (t & 1) * 64;
+            const uint64_t dq0 = dk0(sq), ddo0 = dk0(sdo);
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sK, BT, kk), desc_k(sq, BS, kk), idesc_s, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tDP, desc_k(sV, BT, kk), desc_k(sdo, BS, kk), idesc_s, kk > 0);
+            for (int kk = 0; kk < HD / 16; kk++) {
+              umma_f16_ss(tS, DK(dK0, BT, kk), DK(dq0, BS, kk), idesc_s, kk > 0);
+              umma_f16_ss(tDP, DK(dV0, BT, kk), DK(ddo0, BS, kk), idesc_s, kk > 0);
+            }
             umma_commit(bar_sfull + 8 * (t & 1));
             if (t == n - 1) umma_commit(bar_kvfree);        // K and V are only read by these products
           }
@@ -962,12 +509,12 @@ flash_dkv_ws_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_con
             if (!mbar_wait(bar_ready, rc & 1, abort_flag, 6, p.err)) { ok = false; break; }
             rc++;
             tc_fence_after();
+            const uint64_t mdo0 = dmn0(sdo, BS), mq0 = dmn0(sq, BS);
 #pragma unroll
-            for (int kk = 0; kk < BS / 16; kk++)
-              umma_f16_ss(tmem + 256, desc_k(sP, BT, kk), desc_mn(sdo, BS, kk), idesc_g, (tt > 0 || kk > 0));
-#pragma unroll
-            for (int kk = 0; kk < BS / 16; kk++)
-              umma_f16_ss(tmem + 256 + HD, desc_k(sDS, BT, kk), desc_mn(sq, BS, kk), idesc_g, (tt > 0 || kk > 0));
+            for (int kk = 0; kk < BS / 16; kk++) {
+              umma_f16_ss(tmem + 256, DK(dP0, BT, kk), DMN(mdo0, kk), idesc_g, (tt > 0 || kk > 0));
+              umma_f16_ss(tmem + 256 + HD, DK(dDS0, BT, kk), DMN(mq0, kk), idesc_g, (tt > 0 || kk > 0));
+            }
             umma_commit(bar_gdone);
             umma_commit(bar_qfree + 8 * s);
           }
@@ -1171,6 +718,7 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, HD, 0, 1);
       int ic = 0, kvc = 0, rc = 0;
       bool ok = true;
+      const uint64_t dQ0 = dk0(sQ), dDO0 = dk0(sDO), dDS0 = dk0(sDS);
       for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ic++) {
         int b, h, q0, n;
         decode(w, b, h, q0, n);
@@ -1184,10 +732,12 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc_fence_after();
             const uint32_t sk = sKV + s * 2 * C::SUB, sv = sk + C::SUB;
             const uint32_t tS = tmem + (j & 1) * 64, tDP = tmem + 128 + (j & 1) * 64;
+            const uint64_t dk_0 = dk0(sk), dv_0 = dk0(sv);
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tS, desc_k(sQ, BT, kk), desc_k(sk, BS, kk), idesc_s, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) umma_f16_ss(tDP, desc_k(sDO, BT, kk), desc_k(sv, BS, kk), idesc_s, kk > 0);
+            for (int kk = 0; kk < HD / 16; kk++) {
+              umma_f16_ss(tS, DK(dQ0, BT, kk), DK(dk_0, BS, kk), idesc_s, kk > 0);
+              umma_f16_ss(tDP, DK(dDO0, BT, kk), DK(dv_0, BS, kk), idesc_s, kk > 0);
+            }
             umma_commit(bar_sfull + 8 * (j & 1));
             if (j == n - 1) umma_commit(bar_qfree);         // Q and dO are only read by these products
           }
@@ -1198,9 +748,10 @@ flash_dq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (!mbar_wait(bar_ready, rc & 1, abort_flag, 6, p.err)) { ok = false; break; }
             rc++;
             tc_fence_after();
+            const uint64_t mk0 = dmn0(sk, BS);
 #pragma unroll
             for (int kk = 0; kk < BS / 16; kk++)
-              umma_f16_ss(tmem + 256, desc_k(sDS, BT, kk), desc_mn(sk, BS, kk), idesc_g, (jj > 0 || kk > 0));
+              umma_f16_ss(tmem + 256, DK(dDS0, BT, kk), DMN(mk0, kk), idesc_g, (jj > 0 || kk > 0));
             umma_commit(bar_gdone);
             umma_commit(bar_kvfree + 8 * s);
           }
@@ -1311,84 +862,53 @@ int set_smem(K kernel, int bytes, const char* name) {
   return 0;
 }
 
-template <int HD, int BKV>
+static int num_sms_attn() {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+
+template <int HD>
 int launch_fwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
+  using C = FwdWs<HD>;
   const size_t rows = (size_t)p.B * p.T;
-  const CUtensorMap* mq = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, 128, 64);
-  const CUtensorMap* mkv = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, BKV, 64);
-  if (!mq || !mkv) return -1;
-  static const bool serial = [] { const char* e = getenv("KHARON_FLASH_SERIAL"); return e && e[0] == '1'; }();
-  if (!serial) {
-    using C = FwdWs<HD>;
-    mkv = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, C::BKV, 64);
-    if (!mkv) return -1;
-    static bool once_ws = false;
-    if (!once_ws) { if (set_smem(flash_fwd_ws_kernel<HD>, C::SMEM, "flash_fwd")) return -1; once_ws = true; }
-    const int n_qt = (p.T + 127) / 128;
-    const int n_items = p.B * p.H * n_qt;
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-    const int ctas = 2 * sms;                  // two CTAs per SM
-    const CUtensorMap* mo = kh_tmap_3d_bf16(p.out, (uint64_t)p.H * HD, p.T, p.B, (uint64_t)p.H * HD, (uint64_t)p.T * p.H * HD, 128, 64);
-    if (!mo) return -1;
-    KH_LAUNCH((flash_fwd_ws_kernel<HD>), n_items < ctas ? n_items : ctas, C::THREADS, C::SMEM, st, *mq, *mkv, *mo, p, n_items, n_qt);
-    KH_LAUNCH_CHECK("flash_fwd");
-    return 0;
-  }
-  constexpr int SMEM = 128 * HD * 2 + 2 * BKV * HD * 2 + 128 * BKV * 2 + 1024 + 64;
+  const CUtensorMap* mq = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, C::BQ, 64);
+  const CUtensorMap* mkv = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, C::BKV, 64);
+  const CUtensorMap* mo = kh_tmap_3d_bf16(p.out, (uint64_t)p.H * HD, p.T, p.B, (uint64_t)p.H * HD, (uint64_t)p.T * p.H * HD, 128, 64);
+  if (!mq || !mkv || !mo) return -1;
   static bool once = false;
-  if (!once) { if (set_smem(flash_fwd_kernel<HD, BKV>, SMEM, "flash_fwd")) return -1; once = true; }
-  dim3 grid((p.T + 127) / 128, p.H, p.B);
-  KH_LAUNCH((flash_fwd_kernel<HD, BKV>), grid, 128, SMEM, st, *mq, *mkv, p);
+  if (!once) { if (set_smem(flash_fwd_ws_kernel<HD>, C::SMEM, "flash_fwd")) return -1; once = true; }
+  const int n_qt = (p.T + 127) / 128;
+  const int n_items = p.B * p.H * n_qt;
+  const int ctas = 2 * num_sms_attn();                  // two CTAs per SM
+  KH_LAUNCH((flash_fwd_ws_kernel<HD>), n_items < ctas ? n_items : ctas, C::THREADS, C::SMEM, st, *mq, *mkv, *mo, p, n_items, n_qt);
   KH_LAUNCH_CHECK("flash_fwd");
   return 0;
 }
 
 template <int HD>
 int launch_bwd(const void* qkv, const AttnParams& p, cudaStream_t st) {
+  using C = BwdWs<HD>;
   const size_t rows = (size_t)p.B * p.T;
   const CUtensorMap* mq = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, 128, 64);
   const CUtensorMap* md = kh_tmap_2d_bf16(p.dout, rows, p.H * HD, p.H * HD, 128, 64);
-  if (!mq || !md) return -1;
-  const long nw = (long)rows * p.H;
-  KH_LAUNCH(flash_delta_kernel, (unsigned)((nw * 32 + 255) / 256), 256, 0, st, p.o, p.dout, p.delta, p.B, p.T, p.H, HD);
-  static const bool serial = [] { const char* e = getenv("KHARON_FLASH_SERIAL"); return e && e[0] == '1'; }();
-  if (!serial) {
-    using C = BwdWs<HD>;
-    const CUtensorMap* mq64 = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, 64, 64);
-    const CUtensorMap* md64 = kh_tmap_2d_bf16(p.dout, rows, p.H * HD, p.H * HD, 64, 64);
-    if (!mq64 || !md64) return -1;
-    static bool once_ws = false;
-    if (!once_ws) {
-      if (set_smem(flash_dkv_ws_kernel<HD>, C::SMEM_KV, "flash_dkv") || set_smem(flash_dq_ws_kernel<HD>, C::SMEM_Q, "flash_dq")) return -1;
-      once_ws = true;
-    }
-    const int n_t = (p.T + 127) / 128;
-    const int n_items = p.B * p.H * n_t;
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-    const int grid = n_items < sms ? n_items : sms;
-    const CUtensorMap* mg = kh_tmap_3d_bf16(p.dqkv, (uint64_t)3 * p.H * HD, p.T, p.B, (uint64_t)p.ld, (uint64_t)p.T * p.ld, 128, 64);
-    if (!mg) return -1;
-    KH_LAUNCH((flash_dkv_ws_kernel<HD>), grid, C::THREADS, C::SMEM_KV, st, *mq, *mq64, *md64, *mg, p, n_items, n_t);
-    KH_LAUNCH((flash_dq_ws_kernel<HD>), grid, C::THREADS, C::SMEM_Q, st, *mq, *md, *mq64, *mg, p, n_items, n_t);
-    KH_LAUNCH_CHECK("flash_bwd");
-    return 0;
-  }
-  constexpr int SMEM_KV = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 1024 + 1024 + 64;
-  constexpr int SMEM_Q = 4 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 64;
+  const CUtensorMap* mq64 = kh_tmap_2d_bf16(qkv, rows, 3 * p.H * HD, p.ld, 64, 64);
+  const CUtensorMap* md64 = kh_tmap_2d_bf16(p.dout, rows, p.H * HD, p.H * HD, 64, 64);
+  const CUtensorMap* mg = kh_tmap_3d_bf16(p.dqkv, (uint64_t)3 * p.H * HD, p.T, p.B, (uint64_t)p.ld, (uint64_t)p.T * p.ld, 128, 64);
+  if (!mq || !md || !mq64 || !md64 || !mg) return -1;
+  KH_LAUNCH((flash_delta_kernel<HD>), (unsigned)((rows * 32 + 255) / 256), 256, 0, st, p.o, p.dout, p.delta, p.B, p.T, p.H);
   static bool once = false;
   if (!once) {
-    if (set_smem(flash_dkv_kernel<HD>, SMEM_KV, "flash_dkv") || set_smem(flash_dq_kernel<HD>, SMEM_Q, "flash_dq")) return -1;
+    if (set_smem(flash_dkv_ws_kernel<HD>, C::SMEM_KV, "flash_dkv") || set_smem(flash_dq_ws_kernel<HD>, C::SMEM_Q, "flash_dq")) return -1;
     once = true;
   }
-  dim3 grid((p.T + 127) / 128, p.H, p.B);
-  KH_LAUNCH((flash_dkv_kernel<HD>), grid, 128, SMEM_KV, st, *mq, *md, p);
-  KH_LAUNCH((flash_dq_kernel<HD>), grid, 128, SMEM_Q, st, *mq, *md, p);
+  const int n_t = (p.T + 127) / 128;
+  const int n_items = p.B * p.H * n_t;
+  const int sms = num_sms_attn();
+  const int grid = n_items < sms ? n_items : sms;
+  KH_LAUNCH((flash_dkv_ws_kernel<HD>), grid, C::THREADS, C::SMEM_KV, st, *mq, *mq64, *md64, *mg, p, n_items, n_t);
+  KH_LAUNCH((flash_dq_ws_kernel<HD>), grid, C::THREADS, C::SMEM_Q, st, *mq, *md, *mq64, *mg, p, n_items, n_t);
   KH_LAUNCH_CHECK("flash_bwd");
   return 0;
 }
@@ -1401,7 +921,7 @@ extern "C" int kh_flash_fwd(const void* qkv, void* out, void* lse, int B, int T,
   AttnParams p = {};
   p.B = B; p.T = T; p.H = H; p.ld = ld; p.scale = scale; p.out = (bf16*)out; p.lse = (float*)lse;
   p.err = kh_error_word_dev();
-  return hd == 64 ? launch_fwd<64, 128>(qkv, p, (cudaStream_t)stream) : launch_fwd<128, 64>(qkv, p, (cudaStream_t)stream);
+  return hd == 64 ? launch_fwd<64>(qkv, p, (cudaStream_t)stream) : launch_fwd<128>(qkv, p, (cudaStream_t)stream);
 }
 
 extern "C" int kh_flash_bwd(const void* qkv, const void* out, const void* dout, const void* lse, void* dqkv,
