@@ -87,7 +87,7 @@ class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
                  fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None, vocab_parallel=True,
-                 defer_dw=None, eager_p2p=None):
+                 defer_dw=None, eager_p2p=None, bucket_optimizer=True):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
         # The in-kernel collectives move bf16 activations / weights; an fp32 model (the oracle
@@ -170,6 +170,15 @@ class TrainEngine:
             self.g_shard = None if self.zero_fused else torch.zeros(self.shard, dtype=torch.float32, device=dev)
             if self.zero_fused:
                 self.zero_fused.finalize()
+        # Optimizer buckets: without ZeRO, a layer's AdamW range is launched on a side stream as soon as the
+        # layer's gradients are final, i.e. under the backward pass of the layers below it (memory-bound
+        # work next to compute-bound work); the rest of the arena follows after the last backward.
+        self.bucketed = bool(not self.zero and self.device.type == "cuda" and dtype == torch.bfloat16 and bucket_optimizer)
+        self._opt_pending = False
+        if self.bucketed:
+            self.opt_stream = torch.cuda.Stream(self.device)
+            self.opt_events = [torch.cuda.Event() for _ in range(nl)]
+            self.opt_done = torch.cuda.Event()
         self.plans = {}
         # launch plans replay native calls only; the fp32 oracle path also runs PyTorch operators
         self.use_plans = self.device.type == "cuda" and dtype == torch.bfloat16
@@ -262,8 +271,10 @@ class TrainEngine:
             if self.defer_dw and op in (PP_FWD, PP_BWD):
                 a1 = a0                 # one slot per micro-batch
             if op == PP_FLUSH_DW:
+                m.on_layer_grads = self._adamw_layer if (self.bucketed and a1 == M) else None
                 with tr.range("weight gradients"):
                     self._compute(("W", a0, a1), lambda: m.flush_dw(a0, a1))
+                m.on_layer_grads = None
                 continue
             if box is not None and op not in (PP_FWD, PP_BWD):
                 with tr.range("pipeline p2p"):
@@ -287,9 +298,12 @@ class TrainEngine:
             if op == PP_BWD:
                 dxo = None if c.last else cur_grad
                 first_loss = n_loss == 0
+                # the last micro-batch's backward completes the gradients layer by layer
+                m.on_layer_grads = self._adamw_layer if (self.bucketed and not self.defer_dw and n_loss == M - 1) else None
                 with tr.range("backward"):
                     in_grad[a0] = self._compute(("B", a0, a1), lambda: m.backward(
                         slot=a1, dx_out=dxo, inv_mb=inv, loss_scale=inv, accumulate_loss=not first_loss))
+                m.on_layer_grads = None
                 n_loss += 1
                 continue
             with tr.range("pipeline p2p"):
@@ -325,9 +339,34 @@ class TrainEngine:
             g = m.params.grad["wte"] if m.first else m.params.grad["head_w"]
             dist.all_reduce(g, group=self.mesh.tie_group)
 
+    def _adamw_layer(self, l):
+        """AdamW over layer l's range on the optimizer stream, ordered after everything the compute stream
+        has issued so far (the layer's last gradient kernel)."""
+        m, o = self.model, self.opt
+        if not self._opt_pending:          # first bucket of the step
+            m.step += 1
+            self._opt_pending = True
+        cur = torch.cuda.current_stream(self.device)
+        ev = self.opt_events[l]
+        ev.record(cur)
+        self.opt_stream.wait_event(ev)
+        lo, hi = m.layer_range(l)
+        with torch.cuda.stream(self.opt_stream):
+            m.adamw_step(o["lr"], o["beta1"], o["beta2"], o["eps"], o["wd"], lo=lo, hi=hi, advance=False)
+
     def optimizer_step(self):
         m, ps, o = self.model, self.model.params, self.opt
         if not self.zero:
+            if self._opt_pending:
+                # the layers were updated under the backward pass; what is left: embeddings, final norm, head
+                self._opt_pending = False
+                lo0, _ = m.layer_range(0)
+                _, hi1 = m.layer_range(m.cfg.n_layer - 1)
+                m.adamw_step(o["lr"], o["beta1"], o["beta2"], o["eps"], o["wd"], lo=0, hi=lo0, advance=False)
+                m.adamw_step(o["lr"], o["beta1"], o["beta2"], o["eps"], o["wd"], lo=hi1, hi=ps.w.numel(), advance=False)
+                self.opt_done.record(self.opt_stream)
+                torch.cuda.current_stream(self.device).wait_event(self.opt_done)
+                return
             m.adamw_step(o["lr"], o["beta1"], o["beta2"], o["eps"], o["wd"])
             return
         grp = self.mesh.dp_group

@@ -144,6 +144,10 @@ class GPT:
         self.s_table = torch.empty(2 * cfg.vocab, dtype=torch.int32, device=self.device)
         self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.tp_allreduce = None      # callable(tensor) summing in place over the TP group
+        # callable(layer) invoked as soon as every gradient of that layer is final for the step (last
+        # micro-batch's backward, or the last deferred weight-gradient pass): the engine starts the
+        # layer's optimizer bucket there, under the backward of the layers below
+        self.on_layer_grads = None
         self.skip_loss = False
         # fused tensor-parallel operators (installed by parallel.tp when available)
         self.fused_tp = None
@@ -436,6 +440,8 @@ class GPT:
             ops.layernorm_bwd(self.s_dln, s.x[l], self.L(l, "ln1_w"), a["mean1"], a["rstd1"], dx, other,
                               self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
             dx, other = other, dx
+            if self.on_layer_grads is not None:
+                ops.plan_call_host(self.on_layer_grads, l)
         if self.first:
             ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T, table=self.s_table)
             return None
@@ -456,6 +462,8 @@ class GPT:
                 dyr, xr = g.rows(l, dy, lo, hi), g.rows(l, x, lo, hi)
                 ops.gemm(dyr, xr, self.G(l, name + "_w"), a_mn=True, b_mn=True, accumulate=True,
                          colsum=self.G(l, name + "_b"))
+            if hi == g.n and self.on_layer_grads is not None:
+                ops.plan_call_host(self.on_layer_grads, l)
 
     def gather_prob(self, slot=0):
         """p(target) per row from the logits of the last forward (src/core/kernels.cu:372-378)."""
@@ -464,13 +472,26 @@ class GPT:
         return s.prob
 
     # ------------------------------------------------------------------ optimizer
-    def adamw_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0):
-        """Fused AdamW over the flat arena (src/core/adamw.c:9-16); also refreshes the bf16
-        compute copy and clears the gradients for the next accumulation."""
-        self.step += 1
+    def adamw_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0, lo=0, hi=None, advance=True):
+        """Fused AdamW over the flat arena (src/core/adamw.c:9-16), or over elements [lo, hi) of it; also
+        refreshes the bf16 compute copy and clears the gradients for the next accumulation.  The update
+        is elementwise, so any partition of the arena into ranges gives the same bits as one sweep."""
+        if advance:
+            self.step += 1
         ps = self.params
-        ops.adamw(ps.w, ps.g, ps.m, ps.v, None if ps.wb is ps.w else ps.wb, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+        hi = ps.w.numel() if hi is None else hi
+        if hi <= lo:
+            return
+        wb = None if ps.wb is ps.w else ps.wb[lo:hi]
+        ops.adamw(ps.w[lo:hi], ps.g[lo:hi], ps.m[lo:hi], ps.v[lo:hi], wb, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
                   wd=wd, step=self.step, grad_scale=grad_scale, zero_grad=True)
+
+    def layer_range(self, l):
+        """Elements [lo, hi) of the flat arena that belong to layer l (alignment gaps included)."""
+        off = self.params.offsets
+        lo = off["l%d.ln1_w" % l]
+        hi = off["l%d.ln1_w" % (l + 1)] if l + 1 < self.cfg.n_layer else off["lnf_w"]
+        return lo, hi
 
     # ------------------------------------------------------------------ checkpoint
     def save(self, path, rng_state=0, moments=None):

@@ -102,6 +102,21 @@ def plan_call(fn, *args):
     fn(*args)
 
 
+def plan_call_host(fn, *args):
+    """Like ``plan_call`` for a host callable that itself issues native calls whose arguments change
+    from step to step (an optimizer bucket: the bias corrections depend on the step number): the plan
+    keeps the callable and calls it again on every replay; what it launches is not recorded."""
+    global _recording
+    rec = _recording
+    if rec is not None:
+        rec.append((fn, args, -1))
+    _recording = None
+    try:
+        fn(*args)
+    finally:
+        _recording = rec
+
+
 def _p(t):
     return 0 if t is None else t.data_ptr()
 

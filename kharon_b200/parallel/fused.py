@@ -74,7 +74,7 @@ class _Ctx:
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         # the all-gather form (mode 2) reduces nothing: no partial-tile staging
         self.slot_bytes = tp * M * N * 2 if mode != 2 else 0
-        self.flag_bytes = tp * tiles * 4
+        self.flag_bytes = tp * tiles * 4 * 4          # one counter per (source rank, tile, 64-column chunk)
         total = 2 * self.slot_bytes + self.flag_bytes + 256
         self.buf, self.h = _symm_alloc(total, device, group)
         self.buf.zero_()
@@ -122,7 +122,7 @@ class FusedTP:
         ops._call(_native.cuda().kh_gemm_comm, 1, ptr, a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                   out.data_ptr(), out.stride(0), M, N, K, mode, 0, self.tp, self.rank, c.c_stage, c.c_flags,
                   c.c_ready, 0, 0, c.epoch.data_ptr(), None, None, ops._p(bias), ops._p(resid),
-                  resid.stride(0) if resid is not None else 0, self.max_ctas, ops._stream())
+                  resid.stride(0) if resid is not None else 0, 0, None, 0, self.max_ctas, ops._stream())
         return out
 
     def gemm_ar(self, a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None):
@@ -133,31 +133,44 @@ class FusedTP:
         """out[M/tp,N] = this rank's row block of the summed product (+ bias + resid rows)."""
         return self._gemm(a, b, out, a_mn, b_mn, MODE_RS, bias, resid)
 
-    def ag_gemm(self, shard_ptrs, lda, rows_per_rank, b, out, *, b_mn=False, K=None):
-        """out[M,N] = concat_r(shard_r)[M,K] @ op(b): ``shard_ptrs`` are the tp peer addresses of the
-        row shards ([M/tp, K] each, symmetric memory).  Local product only -- no reduction."""
+    def ag_gemm(self, shard_ptrs, lda, rows_per_rank, b, out, *, b_mn=False, K=None, epi=0, bias=None, aux=None,
+                gather_buf=None):
+        """out[M,N] = epilogue(concat_r(shard_r)[M,K] @ op(b)): ``shard_ptrs`` are the tp peer addresses of
+        the row shards ([M/tp, K] each, symmetric memory).  Local product only -- no reduction.  Epilogues
+        (``ops.EPI_*``): none, bias, bias + GELU (``aux`` receives the pre-activation), dGELU (``aux`` is the
+        pre-activation).  ``gather_buf`` [M, K]: where the remote rows land (default: a buffer owned by the
+        context); when the shards are row blocks of per-rank [M, K] buffers in symmetric memory, passing this
+        rank's buffer leaves the complete gathered operand behind for later use (weight gradients).
+
+        A rank's shard may be rewritten once a LATER collective that needs every rank's contribution has
+        completed on this rank (the peers' copies of the shard precede their contribution); rewriting it
+        earlier races with the peers' copier CTAs."""
         M = rows_per_rank * self.tp
         N = b.shape[1] if b_mn else b.shape[0]
         K = K if K is not None else (b.shape[0] if b_mn else b.shape[1])
         ptrs = (C.c_uint64 * self.tp)(*shard_ptrs)
-        ops.plan_call(self._launch_ag, ptrs, lda, b, b_mn, out, M, N, K)
+        ops.plan_call(self._launch_ag, ptrs, lda, b, b_mn, out, M, N, K, epi, bias, aux, gather_buf)
         return out
 
-    def _launch_ag(self, ptrs, lda, b, b_mn, out, M, N, K):
-        # gather mode uses a context of its own: its "reduction" is local-only (tp slots unused)
+    def _launch_ag(self, ptrs, lda, b, b_mn, out, M, N, K, epi=0, bias=None, aux=None, gather_buf=None):
+        # gather mode uses a context of its own: its "reduction" is local-only (no staging)
         c = self._get(M, N, 2)
         c.gathers += 1
-        if getattr(c, "gbuf_k", None) != K:      # local landing buffer for the remote rows + per-block counters
-            c.gbuf = torch.empty(M, K, dtype=torch.bfloat16, device=self.device)
+        if getattr(c, "gbuf_k", None) != K:      # per-block delivery counters (+ default landing buffer)
+            c.gbuf = None
             c.blk_ready = torch.zeros((M + 127) // 128, dtype=torch.int32, device=self.device)
             c.epoch.zero_()
             c.gbuf_k = K
+        if gather_buf is None:
+            if c.gbuf is None:
+                c.gbuf = torch.empty(M, K, dtype=torch.bfloat16, device=self.device)
+            gather_buf = c.gbuf
         lib = _native.cuda()
         rc = lib.kh_gemm_comm(ptrs, lda, 0, b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0),
                               M, N, K, 2, 1, self.tp, self.rank, c.c_stage, c.c_flags, c.c_ready,
-                              0, c.gathers, c.epoch.data_ptr(), c.gbuf.data_ptr(), c.blk_ready.data_ptr(), None, None, 0,
-                              self.max_ctas,
-                              torch.cuda.current_stream().cuda_stream)
+                              0, c.gathers, c.epoch.data_ptr(), gather_buf.data_ptr(), c.blk_ready.data_ptr(),
+                              ops._p(bias), None, 0, epi, ops._p(aux), aux.stride(0) if aux is not None else 0,
+                              self.max_ctas, torch.cuda.current_stream().cuda_stream)
         ops._chk(rc)
         ops.launch_count += 1
 
