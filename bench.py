@@ -126,7 +126,9 @@ def run_ours():
         fused_check = selfcheck.fused_check(mesh, device)
         gc.collect()
     eng = TrainEngine(L, d, H, V, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
-                      init=arg("init", "device", str), fused_comm=fused_comm, pp_split=arg("pp-split", "auto", str))
+                      init=arg("init", "device", str), fused_comm=fused_comm, pp_split=arg("pp-split", "auto", str),
+                      sp=False if "--no-sp" in sys.argv else None)
+    seq_par = bool(eng.sp)
     ntok = M * mb * S                                    # per replica and step
     data = Rng(42 + mesh.c.dp_rank)
     pin = device.type == "cuda"
@@ -203,7 +205,7 @@ def run_ours():
             Kr = min(K, 10)
             e2 = TrainEngine(L, d, H, 256, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                              init=arg("init", "device", str), fused_comm=fused_comm, untied_head=True,
-                             pp_split=arg("pp-split", "auto", str))
+                             pp_split=arg("pp-split", "auto", str), sp=False if "--no-sp" in sys.argv else None)
             data.batch_into(host_idx[0], host_tgt[0], 256)
             dev_idx.copy_(host_idx[0]); dev_tgt.copy_(host_tgt[0])
             for _ in range(W):
@@ -248,7 +250,7 @@ def run_ours():
             "config": {"model": "GPT L%d d%d H%d V%d tied" % (L, d, H, V), "global_batch": mb * M * dp, "seq_len": S,
                        "micro_batch": mb, "micro_batches": M, "parallelism": "tp%d pp%d dp%d(zero1)" % (tp, pp, dp),
                        "microbatches_fused_on_single_stage": fused_mb, "fused_comm": fused_comm,
-                       "layers_per_stage": stage_layers,
+                       "sequence_parallel": seq_par, "layers_per_stage": stage_layers,
                        "l2": "inputs larger than L2 (step working set > 20 GB)", "loss_last_step": round(final_loss, 4)},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "ms_per_step": round(ms_e2e / K, 3),

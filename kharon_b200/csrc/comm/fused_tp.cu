@@ -15,29 +15,24 @@
 // One kernel, persistent CTAs, ten warps:
 //   warp 0      TMA producer (operand tiles -> 128-byte-swizzled shared-memory ring)
 //   warp 1      tcgen05.mma issuer, two TMEM accumulator buffers
-//   warps 2-5   epilogue: TMEM -> bf16, 64 columns at a time, through a shared-memory chunk and TMA
-//               stores.  Reducing modes: the chunk is PUSHED into the staging slot of every rank that
-//               reduces the tile; when its bulk stores have completed (checked one chunk later, so
-//               the warps never idle on the NVLink round trip) one red.release.sys raises that
-//               rank's arrival counter for (source rank, tile, chunk).  All-gather form: the chunk
-//               is the final result (+ bias, + GELU, * GELU') and goes to the local output.
-//   warps 6-9   reducer: one thread per row of the tile.  For each chunk it waits (bounded) for the
-//               peers' counters, takes the OWN partial straight from TMEM (rounded to bf16 exactly
-//               as the peers received it), adds the peers' partials from local staging in rank
-//               order in fp32, adds bias / residual and stores.  The accumulator buffer is handed
-//               back to the MMA warp when both the epilogue and the reducer warps are done with it,
-//               so the reduction of tile i runs under the main loop of tile i+1.
+//   warps 2-5   epilogue: TMEM -> bf16 partial tile, stored to the local output (if this rank
+//               reduces the tile) and PUSHED with plain st.global into the staging slot of every
+//               rank that reduces it; then fence + one red.release.sys per warp on that rank's
+//               arrival counter for (source rank, tile)
+//   warps 6-9   reducer: for each finished tile, wait (bounded) until every peer's partial has
+//               arrived, add the partials in rank order in fp32, add bias / residual, store.
+//               Runs concurrently with the main loop of the following tiles, so the NVLink
+//               traffic hides behind the tensor-core work.
 //
 // Determinism: partials are rounded to bf16 once, summed in fp32 in rank order 0..tp-1 on every
 // rank -> all ranks hold bit-identical results, run to run.
-// Flow control: arrival counters only grow (4 per call, tile and chunk); staging is double-buffered
+// Flow control: arrival counters only grow (4 per call and tile); staging is double-buffered
 // by call parity, which is sufficient because a rank cannot be two calls ahead of a peer it
 // needs partials from.  The call number lives in device memory (a word per buffer set that the
 // last CTA of a launch advances), so a launch takes the same arguments every time and can be
-// replayed from a CUDA graph or a recorded launch plan.  Every wait is bounded; on expiry the error
-// word gets code 5 and all roles of the CTA unwind.  No TMA load here uses cluster multicast; peer
-// memory is only touched by TMA / plain stores and red (push) and, in gather mode, by non-multicast
-// bulk loads.
+// replayed from a CUDA graph or a recorded launch plan.  Every wait is bounded; on expiry the error word gets code 5 and all
+// roles of the CTA unwind.  No TMA load here uses cluster multicast; peer memory is only
+// touched by st.global / red (push) and, in gather mode, by non-multicast TMA loads.
 #include "../kernels/common.cuh"
 
 #define KH_LAUNCH_CHECK(name)                                                     \
@@ -57,7 +52,6 @@ constexpr int SMEM = STAGES * STAGE_BYTES + 2 * EPI_CHUNK_BYTES + 1024 + 256;
 constexpr int MAX_TP = 8;
 enum { MODE_AR = 0, MODE_RS = 1, MODE_LOCAL = 2 };   // LOCAL: no reduction (all-gather -> GEMM only)
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_DGELU = 4 };
-constexpr int CHUNKS = BN / 64;                      // arrival counters per tile
 
 struct CommParams {
   int M, N, K;
@@ -136,6 +130,25 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
     }
   }
 }
+__device__ __forceinline__ bool wait_smem_count(volatile int* p, int target, volatile int* abort_flag, int* err,
+                                                uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (*p >= target) return true;
+    if ((it & 255) == 255) {
+      if (*abort_flag) return false;
+      const uint64_t now = kh_globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
+        *abort_flag = 5;
+        atomicCAS(err, 0, 5);
+        return false;
+      }
+    }
+    __nanosleep(32);
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -149,6 +162,7 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
   const uint32_t bar_tempty = bar_tfull + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_pub = reinterpret_cast<volatile int*>(tmem_slot + 2);   // epilogue warps that finished a tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -158,9 +172,9 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    // an accumulator buffer is free again when the four epilogue warps and the four reducer warps have read it
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 8); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
     *abort_flag = 0;
+    *s_pub = 0;
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
@@ -322,20 +336,22 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       }
     }
   } else if (warp < 6) {
-    // ---------------------------------------------------------------- epilogue warps
+    // ---------------------------------------------------------------- epilogue: publish partial tiles
     const int q = warp & 3;
-    const bool issuer = (warp == 2 && lane == 0);
-    int tcount = 0, chunk_no = 0;
+    int tcount = 0;
     bool ok = true;
-    // chunk whose bulk stores are in flight and whose arrival has not been signalled yet
-    int pend_t = -1, pend_c = 0, pend_owner = -1;
-    auto signal_chunk = [&](int tt, int cc, int town) {
+    // Arrival of tile t is signalled once its bulk stores have completed; that is checked one
+    // tile later (after the next tile's first store group is queued), so the epilogue never idles
+    // on the NVLink round trip.
+    int pend_t = -1, pend_owner = -1;
+    auto signal_tile = [&](int tt, int town) {
       asm volatile("fence.proxy.async;" ::: "memory");    // bulk (async-proxy) writes -> ordinary loads
       __threadfence_system();
-      for (int pr = 0; pr < p.tp; pr++) {
+      for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
         if (pr == p.rank || (town >= 0 && pr != town)) continue;
-        red_release_sys_add(p.flags[pr] + ((size_t)p.rank * num_tiles + tt) * CHUNKS + cc, 4);
+        red_release_sys_add(p.flags[pr] + (size_t)p.rank * num_tiles + tt, 4);
       }
+      atomicAdd(const_cast<int*>(s_pub), 4);
     };
     for (int t = worker; !copier && ok && t < num_tiles; t += n_workers, tcount++) {
       int tm, tn;
@@ -345,217 +361,197 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
       if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err, p.wait_ns)) { ok = false; break; }
       tc_fence_after();
       const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
-      const bool local = p.mode == MODE_LOCAL;
-      const bool push = !local && owner != p.rank;         // RS: the owner pushes nothing, it only reduces
+      const bool mine = owner < 0 || owner == p.rank;
+      const int out_row0 = p.mode == MODE_RS ? tm * BM - p.rank * rows_per_rank : tm * BM;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       const int r_in = q * 32 + lane;                       // row inside the tile
       const int row = tm * BM + r_in;
       const bool row_ok = row < p.M;
-      if (local || push) {
+      const bool local = p.mode == MODE_LOCAL;
+      const bool issuer = (warp == 2 && lane == 0);
+      int chunk_no = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64, chunk_no++) {
-          const int col = tn * BN + c0;
-          if (col >= p.N) break;
-          const uint32_t sbuf = smem_epi + (chunk_no & 1) * EPI_CHUNK_BYTES;
-          // the bulk store that last read this staging chunk must be done with it
-          if (issuer) tma_store_wait_read1();
-          epi_bar_sync();
+      for (int c0 = 0; c0 < BN; c0 += 64, chunk_no++) {
+        const int col = tn * BN + c0;
+        if (col >= p.N) break;
+        const uint32_t sbuf = smem_epi + (chunk_no & 1) * EPI_CHUNK_BYTES;
+        // the bulk store that last read this staging chunk must be done with it
+        if (issuer) tma_store_wait_read1();
+        epi_bar_sync();
 #pragma unroll
-          for (int h = 0; h < 2; h++) {
-            uint32_t r[32];
-            tmem_ld32(taddr + c0 + 32 * h, r);
-            tmem_ld_wait();
-            float v[32];
+        for (int h = 0; h < 2; h++) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0 + 32 * h, r);
+          tmem_ld_wait();
+          float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
-            if (local && p.epi != EPI_NONE) {
-              const int cb = col + 32 * h;
-              const bool full = cb + 32 <= p.N;
-              if (p.epi == EPI_BIAS || p.epi == EPI_BIAS_GELU) {
+          for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+          if (local && p.epi != EPI_NONE) {
+            const int cb = col + 32 * h;
+            const bool full = cb + 32 <= p.N;
+            if (p.epi == EPI_BIAS || p.epi == EPI_BIAS_GELU) {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                if (cb + 8 * j >= p.N) break;
+                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + cb + 8 * j));
+                const float2 f0 = unpack_bf16(b4.x), f1 = unpack_bf16(b4.y), f2 = unpack_bf16(b4.z), f3 = unpack_bf16(b4.w);
+                v[8 * j] += f0.x; v[8 * j + 1] += f0.y; v[8 * j + 2] += f1.x; v[8 * j + 3] += f1.y;
+                v[8 * j + 4] += f2.x; v[8 * j + 5] += f2.y; v[8 * j + 6] += f3.x; v[8 * j + 7] += f3.y;
+              }
+            }
+            if (p.epi == EPI_BIAS_GELU) {
+              // the stored pre-activation is bf16; GELU is applied to the rounded value (as in the plain GEMM)
+              if (row_ok) {
+                bf16* ap = p.aux + (size_t)row * p.ldaux + cb;
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  if (cb + 8 * j >= p.N) break;
-                  const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + cb + 8 * j));
-                  const float2 f0 = unpack_bf16(b4.x), f1 = unpack_bf16(b4.y), f2 = unpack_bf16(b4.z), f3 = unpack_bf16(b4.w);
-                  v[8 * j] += f0.x; v[8 * j + 1] += f0.y; v[8 * j + 2] += f1.x; v[8 * j + 3] += f1.y;
-                  v[8 * j + 4] += f2.x; v[8 * j + 5] += f2.y; v[8 * j + 6] += f3.x; v[8 * j + 7] += f3.y;
+                  if (!full && cb + 8 * j >= p.N) break;
+                  uint4 o;
+                  o.x = pack_bf16(v[8 * j], v[8 * j + 1]); o.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+                  o.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+                  reinterpret_cast<uint4*>(ap)[j] = o;
                 }
               }
-              if (p.epi == EPI_BIAS_GELU) {
-                // the stored pre-activation is bf16; GELU is applied to the rounded value (as in the plain GEMM)
-                if (row_ok) {
-                  bf16* ap = p.aux + (size_t)row * p.ldaux + cb;
 #pragma unroll
-                  for (int j = 0; j < 4; j++) {
-                    if (!full && cb + 8 * j >= p.N) break;
-                    uint4 o;
-                    o.x = pack_bf16(v[8 * j], v[8 * j + 1]); o.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
-                    o.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
-                    reinterpret_cast<uint4*>(ap)[j] = o;
-                  }
-                }
+              for (int i = 0; i < 32; i++) v[i] = gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+            } else if (p.epi == EPI_DGELU) {
+              if (row_ok) {
+                const bf16* ap = p.aux + (size_t)row * p.ldaux + cb;
 #pragma unroll
-                for (int i = 0; i < 32; i++) v[i] = gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
-              } else if (p.epi == EPI_DGELU) {
-                if (row_ok) {
-                  const bf16* ap = p.aux + (size_t)row * p.ldaux + cb;
-#pragma unroll
-                  for (int j = 0; j < 4; j++) {
-                    if (!full && cb + 8 * j >= p.N) break;
-                    const uint4 x4 = reinterpret_cast<const uint4*>(ap)[j];
-                    const float2 f0 = unpack_bf16(x4.x), f1 = unpack_bf16(x4.y), f2 = unpack_bf16(x4.z), f3 = unpack_bf16(x4.w);
-                    v[8 * j] *= gelu_tanh_grad(f0.x); v[8 * j + 1] *= gelu_tanh_grad(f0.y);
-                    v[8 * j + 2] *= gelu_tanh_grad(f1.x); v[8 * j + 3] *= gelu_tanh_grad(f1.y);
-                    v[8 * j + 4] *= gelu_tanh_grad(f2.x); v[8 * j + 5] *= gelu_tanh_grad(f2.y);
-                    v[8 * j + 6] *= gelu_tanh_grad(f3.x); v[8 * j + 7] *= gelu_tanh_grad(f3.y);
-                  }
+                for (int j = 0; j < 4; j++) {
+                  if (!full && cb + 8 * j >= p.N) break;
+                  const uint4 x4 = reinterpret_cast<const uint4*>(ap)[j];
+                  const float2 f0 = unpack_bf16(x4.x), f1 = unpack_bf16(x4.y), f2 = unpack_bf16(x4.z), f3 = unpack_bf16(x4.w);
+                  v[8 * j] *= gelu_tanh_grad(f0.x); v[8 * j + 1] *= gelu_tanh_grad(f0.y);
+                  v[8 * j + 2] *= gelu_tanh_grad(f1.x); v[8 * j + 3] *= gelu_tanh_grad(f1.y);
+                  v[8 * j + 4] *= gelu_tanh_grad(f2.x); v[8 * j + 5] *= gelu_tanh_grad(f2.y);
+                  v[8 * j + 6] *= gelu_tanh_grad(f3.x); v[8 * j + 7] *= gelu_tanh_grad(f3.y);
                 }
               }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              uint4 o;
-              o.x = pack_bf16(v[8 * j], v[8 * j + 1]); o.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
-              o.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
-              const int chunk16 = h * 4 + j;
-              st_shared_v4(sbuf + r_in * 128 + ((chunk16 ^ (r_in & 7)) << 4), o);
             }
           }
-          fence_proxy_async_smem();
-          epi_bar_sync();
-          if (issuer) {
-            if (local) {
-              tma_store_2d(&maps.out, sbuf, col, tm * BM);
-            } else {
-              for (int pr = 0; pr < p.tp; pr++) {
-                if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
-                tma_store_2d(&maps.st[par][pr], sbuf, col, tm * BM);
-              }
-            }
-            tma_store_commit();
-            if (pend_t >= 0) {
-              asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // everything but the group just queued
-              signal_chunk(pend_t, pend_c, pend_owner);
-              pend_t = -1;
-            }
-            if (push) { pend_t = t; pend_c = c0 / 64; pend_owner = owner; }
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint4 o;
+            o.x = pack_bf16(v[8 * j], v[8 * j + 1]); o.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+            o.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+            const int chunk16 = h * 4 + j;
+            st_shared_v4(sbuf + r_in * 128 + ((chunk16 ^ (r_in & 7)) << 4), o);
+          }
+        }
+        if (c0 + 64 >= BN || col + 64 >= p.N) {            // accumulator fully read: hand it back early
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (issuer) {
+          if (mine) tma_store_2d(&maps.out, sbuf, col, out_row0);
+          for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
+            if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
+            tma_store_2d(&maps.st[par][pr], sbuf, col, tm * BM);
+          }
+          tma_store_commit();
+          if (chunk_no == 0 && pend_t >= 0) {
+            asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // everything but the group just queued
+            signal_tile(pend_t, pend_owner);
+            pend_t = -1;
           }
         }
       }
-      // this warp no longer reads the accumulator
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-      // the tile's last chunk is signalled now: the next one is a whole main loop away
-      if (issuer && pend_t >= 0) {
-        tma_store_wait_all();
-        signal_chunk(pend_t, pend_c, pend_owner);
-        pend_t = -1;
-      }
+      pend_t = t; pend_owner = owner;
     }
-    if (issuer) tma_store_wait_all();
+    if (warp == 2 && lane == 0 && pend_t >= 0) {
+      tma_store_wait_all();
+      signal_tile(pend_t, pend_owner);
+    }
   } else {
     // ---------------------------------------------------------------- reducer warps
-    const int q = warp & 3;                       // TMEM lane quadrant of this warp = rows 32 q .. 32 q + 31 of the tile
+    const int rw = warp - 6;
     int tcount = 0;
     bool ok = true;
-    for (int t = worker; !copier && ok && t < num_tiles; t += n_workers, tcount++) {
+    for (int t = worker; !copier && ok && p.mode != MODE_LOCAL && t < num_tiles; t += n_workers, tcount++) {
       int tm, tn;
       tile_coord(t, tm, tn);
-      const int acc = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, 3, p.err, p.wait_ns)) { ok = false; break; }
-      tc_fence_after();
       const int owner = p.mode == MODE_RS ? owner_of(tm) : -1;
-      const bool reduce_here = p.mode != MODE_LOCAL && (owner < 0 || owner == p.rank);
-      if (reduce_here) {
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-        const int row = tm * BM + q * 32 + lane;
-        const bool row_ok = row < p.M;
-        const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
-        bf16* orow = p.out + (size_t)out_row * p.ldo;
-        const bf16* rrow = p.resid ? p.resid + (size_t)out_row * p.ldr : nullptr;
-#pragma unroll 1
-        for (int cc = 0; cc < CHUNKS && ok; cc++) {
-          const int col0 = tn * BN + cc * 64;
-          if (col0 >= p.N) break;
-          int good = 1;
-          if (lane == 0) {
-            for (int pr = 0; pr < p.tp && good; pr++) {
-              if (pr == p.rank) continue;
-              good = wait_counter(p.flags[p.rank] + ((size_t)pr * num_tiles + t) * CHUNKS + cc, target, abort_flag, p.err, p.wait_ns) ? 1 : 0;
-            }
-          }
-          good = __shfl_sync(0xffffffffu, good, 0);
-          if (!good) { ok = false; break; }
-          __threadfence();
-#pragma unroll 1
-          for (int h = 0; h < 2; h++) {
-            const int col = col0 + 32 * h;
-            uint32_t r[32];
-            tmem_ld32(taddr + cc * 64 + 32 * h, r);         // warp-collective: before any per-thread guard
-            tmem_ld_wait();
-            if (col >= p.N) break;
-            float s[32];
-#pragma unroll
-            for (int i = 0; i < 32; i++) s[i] = 0.f;
-            if (p.bias) {
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                if (col + 8 * j >= p.N) break;
-                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + col + 8 * j));
-                const float2 f0 = unpack_bf16(b4.x), f1 = unpack_bf16(b4.y), f2 = unpack_bf16(b4.z), f3 = unpack_bf16(b4.w);
-                s[8 * j] = f0.x; s[8 * j + 1] = f0.y; s[8 * j + 2] = f1.x; s[8 * j + 3] = f1.y;
-                s[8 * j + 4] = f2.x; s[8 * j + 5] = f2.y; s[8 * j + 6] = f3.x; s[8 * j + 7] = f3.y;
-              }
-            }
-            if (row_ok) {
-              for (int pr = 0; pr < p.tp; pr++) {
-                if (pr == p.rank) {
-                  // own partial: the bf16 value the peers received, taken from the accumulator
-#pragma unroll
-                  for (int i = 0; i < 32; i++) s[i] += __bfloat162float(__float2bfloat16(__uint_as_float(r[i])));
-                } else {
-                  const uint4* src = reinterpret_cast<const uint4*>(my_stage + ((size_t)pr * p.M + row) * p.N + col);
-                  uint4 x4[4];
-#pragma unroll
-                  for (int j = 0; j < 4; j++) x4[j] = (col + 8 * j < p.N) ? __ldcg(src + j) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                  for (int j = 0; j < 4; j++) {
-                    const float2 f0 = unpack_bf16(x4[j].x), f1 = unpack_bf16(x4[j].y), f2 = unpack_bf16(x4[j].z), f3 = unpack_bf16(x4[j].w);
-                    s[8 * j] += f0.x; s[8 * j + 1] += f0.y; s[8 * j + 2] += f1.x; s[8 * j + 3] += f1.y;
-                    s[8 * j + 4] += f2.x; s[8 * j + 5] += f2.y; s[8 * j + 6] += f3.x; s[8 * j + 7] += f3.y;
-                  }
-                }
-              }
-              if (rrow) {
-                uint4 x4[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++)
-                  x4[j] = (col + 8 * j < p.N) ? *reinterpret_cast<const uint4*>(rrow + col + 8 * j) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                  const float2 f0 = unpack_bf16(x4[j].x), f1 = unpack_bf16(x4[j].y), f2 = unpack_bf16(x4[j].z), f3 = unpack_bf16(x4[j].w);
-                  s[8 * j] += f0.x; s[8 * j + 1] += f0.y; s[8 * j + 2] += f1.x; s[8 * j + 3] += f1.y;
-                  s[8 * j + 4] += f2.x; s[8 * j + 5] += f2.y; s[8 * j + 6] += f3.x; s[8 * j + 7] += f3.y;
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                if (col + 8 * j >= p.N) break;
-                uint4 o;
-                o.x = pack_bf16(s[8 * j], s[8 * j + 1]); o.y = pack_bf16(s[8 * j + 2], s[8 * j + 3]);
-                o.z = pack_bf16(s[8 * j + 4], s[8 * j + 5]); o.w = pack_bf16(s[8 * j + 6], s[8 * j + 7]);
-                *reinterpret_cast<uint4*>(orow + col + 8 * j) = o;
-              }
-            }
+      int good = 1;
+      if (lane == 0) {
+        good = wait_smem_count(s_pub, 4 * (tcount + 1), abort_flag, p.err, p.wait_ns) ? 1 : 0;
+        if (good && (owner < 0 || owner == p.rank)) {
+          for (int pr = 0; pr < p.tp && good; pr++) {
+            if (pr == p.rank) continue;
+            good = wait_counter(p.flags[p.rank] + (size_t)pr * num_tiles + t, target, abort_flag, p.err, p.wait_ns) ? 1 : 0;
           }
         }
-        if (!ok) break;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { ok = false; break; }
+      if (owner >= 0 && owner != p.rank) continue;      // another rank reduces this tile
+      __threadfence();
+      const int col = tn * BN + lane * 8;
+      if (col >= p.N) continue;
+      float bias8[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) bias8[k] = 0.f;
+      if (p.bias) {
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+        float2 f0 = unpack_bf16(b.x), f1 = unpack_bf16(b.y), f2 = unpack_bf16(b.z), f3 = unpack_bf16(b.w);
+        bias8[0] = f0.x; bias8[1] = f0.y; bias8[2] = f1.x; bias8[3] = f1.y; bias8[4] = f2.x; bias8[5] = f2.y; bias8[6] = f3.x; bias8[7] = f3.y;
+      }
+      const int row_end = min(p.M, (tm + 1) * BM);
+      // 8 rows per pass so that each lane keeps 8 x (tp + 1) independent 16-byte loads in flight
+      constexpr int RB = 8;
+      for (int row0 = tm * BM + rw * RB; row0 < row_end; row0 += 4 * RB) {
+        float a8[RB][8];
+#pragma unroll
+        for (int i = 0; i < RB; i++)
+#pragma unroll
+          for (int k = 0; k < 8; k++) a8[i][k] = bias8[k];
+        for (int r = 0; r < p.tp; r++) {
+          uint4 v[RB];
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            const int row = row0 + i;
+            const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+            const uint4* src = (r == p.rank)
+                                   ? reinterpret_cast<const uint4*>(p.out + (size_t)out_row * p.ldo + col)
+                                   : reinterpret_cast<const uint4*>(my_stage + ((size_t)r * p.M + row) * p.N + col);
+            v[i] = row < row_end ? __ldcg(src) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y), f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+            a8[i][0] += f0.x; a8[i][1] += f0.y; a8[i][2] += f1.x; a8[i][3] += f1.y;
+            a8[i][4] += f2.x; a8[i][5] += f2.y; a8[i][6] += f3.x; a8[i][7] += f3.y;
+          }
+        }
+        if (p.resid) {
+          uint4 v[RB];
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            const int row = row0 + i;
+            const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+            v[i] = row < row_end ? *reinterpret_cast<const uint4*>(p.resid + (size_t)out_row * p.ldr + col) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < RB; i++) {
+            float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y), f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+            a8[i][0] += f0.x; a8[i][1] += f0.y; a8[i][2] += f1.x; a8[i][3] += f1.y;
+            a8[i][4] += f2.x; a8[i][5] += f2.y; a8[i][6] += f3.x; a8[i][7] += f3.y;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < RB; i++) {
+          const int row = row0 + i;
+          if (row >= row_end) break;
+          const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
+          uint4 o;
+          o.x = pack_bf16(a8[i][0], a8[i][1]); o.y = pack_bf16(a8[i][2], a8[i][3]);
+          o.z = pack_bf16(a8[i][4], a8[i][5]); o.w = pack_bf16(a8[i][6], a8[i][7]);
+          *reinterpret_cast<uint4*>(p.out + (size_t)out_row * p.ldo + col) = o;
+        }
+      }
     }
   }
 
@@ -589,12 +585,12 @@ int num_sms() {
 // to the per-rank row shards [M/tp, K] (or [K, M/tp] when a_mn) mapped into this process.
 // `stage_ptrs`, `flag_ptrs`, `ready_ptrs`: tp entries each, index r = rank r's buffer as seen from
 // this process (own entry = local buffer).  Staging holds tp slots of M*N bf16; flags hold
-// 4 * tp * ceil(M/128) * ceil(N/256) counters (one per 64-column chunk of a tile); ready holds tp counters.
-// `epi` / `aux` / `ldaux`: epilogue of the all-gather form (mode 2): 0 none, 1 + bias, 2 + bias then GELU
-// with the pre-activation stored to aux, 4 times GELU'(aux).  Staging is two parities of
+// tp * ceil(M/128) * ceil(N/256) counters; ready holds tp counters.  Staging is two parities of
 // tp * M * N bf16 each; `stage_ptrs` are the parity-0 bases.  The call count of the buffer set
 // (identical on all ranks) is either kept by the kernel in the two zero-initialised words at
 // `epoch_ptr` (local device memory) or, when that is 0, passed as the 1-based `call_no`.
+// `epi` / `aux` / `ldaux`: epilogue of the all-gather form (mode 2): 0 none, 1 + bias, 2 + bias then GELU
+// with the pre-activation stored to aux, 4 times GELU'(aux).
 // Returns 0 or -1.
 extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn, const void* B, int ldb, int b_mn,
                             void* out, int ldo, int M, int N, int K, int mode, int gather, int tp, int rank,

@@ -87,7 +87,7 @@ class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
                  fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None, vocab_parallel=True,
-                 defer_dw=None, eager_p2p=None, bucket_optimizer=True):
+                 defer_dw=None, eager_p2p=None, bucket_optimizer=True, sp=None):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
         # The in-kernel collectives move bf16 activations / weights; an fp32 model (the oracle
@@ -119,15 +119,28 @@ class TrainEngine:
         if c.dp > 1 and fused_comm and self.device.type == "cuda":
             from .parallel.zero_fused import ZeroFused
             self.zero_fused = ZeroFused(self.mesh, self.device)
+        # Sequence parallelism over the TP group (all-gather -> GEMM, GEMM -> reduce-scatter, LayerNorm and
+        # residual stream on row shards): the default whenever the fused kernels run and a micro-batch
+        # splits into whole sequences per rank; on CPU ranks only on request (collective-based evaluation).
+        if sp is None:
+            sp = c.tp > 1 and fused_comm and self.device.type == "cuda"
+        self.sp = bool(sp and c.tp > 1 and mbatch % c.tp == 0)
+        self.sp_ops = None
+        if self.sp:
+            from .parallel import fused as fused_mod
+            self.sp_ops = fused_mod.make(self.mesh, self.device)
         self.model = GPT(self.cfg, self.device, dtype, tp=c.tp, tp_rank=c.tp_rank, first=c.first, last=c.last,
                          untied_head=untied_head, n_slots=self.n_slots, dp=c.dp,
-                         alloc=self.zero_fused.alloc if self.zero_fused else None, defer_dw=self.defer_dw)
+                         alloc=self.zero_fused.alloc if self.zero_fused else None, defer_dw=self.defer_dw,
+                         sp=self.sp_ops)
         if init == "device":
             self.model.init_weights_device(seed)
         else:
             self.model.init_weights(seed, layer0=layer0, total_layers=layers)
         self.schedule = pp_schedule(c.stage, c.pp, n_micro)
         R = mbatch * seq
+        if self.sp:
+            R //= c.tp          # stages exchange row shards: TP rank r of a stage talks to TP rank r of the next
         dev = self.device
         # Message transport between stages.  With deferred weight gradients and a transport whose
         # sends do not wait for the receiver (mailboxes in peer memory on GPUs, gloo isend on CPU
@@ -144,8 +157,8 @@ class TrainEngine:
             self.schedule = pp_schedule_deferred(c.stage, c.pp, n_micro)
         elif self.defer_dw:
             self.schedule = self.schedule + [(PP_FLUSH_DW, 0, n_micro)]
-        self.tok_dev = torch.zeros(n_micro * R, dtype=torch.int32, device=dev)
-        self.tgt_dev = torch.zeros(n_micro * R, dtype=torch.int32, device=dev)
+        self.tok_dev = torch.zeros(n_micro * mbatch * seq, dtype=torch.int32, device=dev)
+        self.tgt_dev = torch.zeros(n_micro * mbatch * seq, dtype=torch.int32, device=dev)
         if c.pp > 1:
             self.recv_act = [torch.empty(R, d_model, dtype=dtype, device=dev) for _ in range(2)]
             self.recv_grad = [torch.empty(R, d_model, dtype=dtype, device=dev) for _ in range(2)]
@@ -154,7 +167,9 @@ class TrainEngine:
         if c.tp > 1:
             grp = self.mesh.tp_group
             self.model.tp_allreduce = lambda t: dist.all_reduce(t, group=grp)
-            if fused_comm and self.device.type == "cuda":
+            if self.sp_ops is not None:
+                self.fused = self.model.fused_tp = self.sp_ops
+            elif fused_comm and self.device.type == "cuda":
                 from .parallel import fused as fused_mod
                 self.fused = fused_mod.install(self.model, self.mesh)
             if c.last and vocab_parallel:
@@ -173,7 +188,10 @@ class TrainEngine:
         # Optimizer buckets: without ZeRO, a layer's AdamW range is launched on a side stream as soon as the
         # layer's gradients are final, i.e. under the backward pass of the layers below it (memory-bound
         # work next to compute-bound work); the rest of the arena follows after the last backward.
-        self.bucketed = bool(not self.zero and self.device.type == "cuda" and dtype == torch.bfloat16 and bucket_optimizer)
+        # (under sequence parallelism the LayerNorm gradients are only complete after their exchange at the
+        # end of the step, so the layers are not updated early there)
+        self.bucketed = bool(not self.zero and not self.sp and self.device.type == "cuda" and dtype == torch.bfloat16
+                             and bucket_optimizer)
         self._opt_pending = False
         if self.bucketed:
             self.opt_stream = torch.cuda.Stream(self.device)
@@ -330,8 +348,22 @@ class TrainEngine:
         with tr.range("optimizer"):
             m.sync_head_grad()
             self._tie_embedding_grads()
+            self._sync_sp_grads()
             self.optimizer_step()
         return m.loss_acc
+
+    def _sync_sp_grads(self):
+        """Sequence parallelism: LayerNorm gains / biases saw only this rank's rows; sum their gradients
+        over the TP group (one packed all-reduce of a few hundred KB per step)."""
+        if not self.sp:
+            return
+        gs = self.model.sp_partial_grads()
+        if getattr(self, "_sp_pack", None) is None:
+            self._sp_pack = torch.empty(sum(g.numel() for g in gs), dtype=torch.float32, device=self.device)
+            self._sp_views = list(self._sp_pack.split([g.numel() for g in gs]))
+        torch._foreach_copy_(self._sp_views, gs)
+        dist.all_reduce(self._sp_pack, group=self.mesh.tp_group)
+        torch._foreach_copy_(gs, self._sp_views)
 
     def _tie_embedding_grads(self):
         m = self.model

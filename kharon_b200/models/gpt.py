@@ -22,6 +22,15 @@ by ``tp_allreduce`` -- a callback installed by the parallel layer (None = single
 same seam the reference uses (model.h:88-89).  Rank 0 of the TP group folds bias+residual
 into its partial product so the sum needs no extra pass.
 
+Sequence parallelism (``sp``, with tp > 1): between the blocks' products the activations live as row
+shards [R / tp, d] -- residual stream, LayerNorm, bias and residual adds run on a rank's own rows
+only.  A column-parallel product gathers its LayerNorm'd input inside the kernel (all-gather ->
+GEMM), a row-parallel product leaves each rank its own rows of the sum (GEMM -> reduce-scatter);
+backward uses the conjugates (all-gather -> GEMM for the input gradients of the row-parallel layers,
+GEMM -> reduce-scatter for those of the column-parallel ones).  These replace the four all-reduces
+per layer and micro-batch of the reference (src/core/gpt.c:687,693,746,761).  LayerNorm gains and
+biases see only a rank's rows, so their gradients are summed over the TP group once per step.
+
 Pipeline parallelism: a stage owns ``n_layer`` consecutive layers; ``first`` embeds,
 ``last`` applies the final norm, head and loss.  Activations are stashed per ``slot`` so
 that several micro-batches can be in flight (1F1B).
@@ -63,12 +72,24 @@ class _SlotGroup:
     One product over n_slots * R rows then replaces n_slots products over R rows."""
     WIDTHS = ("ln1", "att", "ln2", "act", "d_out", "d_pre", "d_mid", "d_qkv")
 
-    def __init__(self, cfg: Config, tp, dev, dt, n):
+    SYM = ("ln1", "ln2", "d_out", "d_mid")      # gathered across the TP group under sequence parallelism
+
+    def __init__(self, cfg: Config, tp, dev, dt, n, sp=None):
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo = d // tp, 4 * d // tp
         w = dict(ln1=d, att=dl, ln2=d, act=fo, d_out=d, d_pre=fo, d_mid=d, d_qkv=3 * dl)
         self.n, self.R = n, R
-        self.layers = [{k: _buf((n * R, w[k]), dt, dev) for k in self.WIDTHS} for _ in range(cfg.n_layer)]
+        names = [k for k in self.WIDTHS if not (sp is not None and k in self.SYM)]
+        self.layers = [{k: _buf((n * R, w[k]), dt, dev) for k in names} for _ in range(cfg.n_layer)]
+        self.sym = None
+        if sp is not None:
+            # the four [n * R, d] operands per layer that peers read: one symmetric slab
+            syms, slab = sp.sym_rows(R, d, count=4 * cfg.n_layer, slots=n) if not sp.emulated else \
+                sp.sym_rows(R, d, count=4 * cfg.n_layer, slots=n, dtype=dt)
+            self.sym = [{k: syms[4 * l + i] for i, k in enumerate(self.SYM)} for l in range(cfg.n_layer)]
+            for l in range(cfg.n_layer):
+                for i, k in enumerate(self.SYM):
+                    self.layers[l][k] = slab[4 * l + i]
 
     def view(self, l, name, i):
         return self.layers[l][name][i * self.R:(i + 1) * self.R]
@@ -80,27 +101,42 @@ class _SlotGroup:
 class _Slot:
     """Activation stash of one in-flight micro-batch."""
 
-    def __init__(self, cfg: Config, tp, dev, dt, first, last, Vp, group=None, index=0):
+    def __init__(self, cfg: Config, tp, dev, dt, first, last, Vp, group=None, index=0, sp=None, sp_syms=None):
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo, Hl = d // tp, 4 * d // tp, cfg.n_head // tp
+        Rs = R // tp if sp is not None else R          # rows of the residual stream this rank holds
         e = lambda *s: _buf(s, dt, dev)
         f = lambda *s: _buf(s, torch.float32, dev)
-        self.x = [e(R, d) for _ in range(cfg.n_layer + 1)]   # residual stream: x[l] enters layer l
+        self.x = [e(Rs, d) for _ in range(cfg.n_layer + 1)]   # residual stream: x[l] enters layer l
         self.layers = []
         for l in range(cfg.n_layer):
             g = (lambda name, *shp: group.view(l, name, index)) if group is not None else (lambda name, *shp: e(*shp))
             a = dict(
-                ln1=g("ln1", R, d), mean1=f(R), rstd1=f(R), qkv=e(R, 3 * dl), att=g("att", R, dl),
-                lse=f(cfg.batch, Hl, cfg.seq), xmid=e(R, d), ln2=g("ln2", R, d), mean2=f(R), rstd2=f(R),
+                ln1=g("ln1", R, d) if sp is None or group is not None else None, mean1=f(Rs), rstd1=f(Rs),
+                qkv=e(R, 3 * dl), att=g("att", R, dl),
+                lse=f(cfg.batch, Hl, cfg.seq), xmid=e(Rs, d),
+                ln2=g("ln2", R, d) if sp is None or group is not None else None, mean2=f(Rs), rstd2=f(Rs),
                 pre=e(R, fo), act=g("act", R, fo))
             if group is not None:
                 for k in ("d_out", "d_pre", "d_mid", "d_qkv"):
                     a[k] = group.view(l, k, index)
+            if sp is not None:
+                # gathered operands as SymRows: from the slot group (deferred weight gradients) or this slot's own
+                if group is not None:
+                    for k in _SlotGroup.SYM:
+                        a["sym_" + k] = group.sym[l][k][index]
+                else:
+                    a["sym_ln1"], a["sym_ln2"] = sp_syms[2 * l][0], sp_syms[2 * l + 1][0]
+                    a["ln1"], a["ln2"] = a["sym_ln1"].t, a["sym_ln2"].t
             self.layers.append(a)
         self.tok = torch.zeros(R, dtype=torch.int32, device=dev)
         self.tgt = torch.zeros(R, dtype=torch.int32, device=dev)
         if last:
-            self.lnf, self.meanf, self.rstdf = e(R, d), f(R), f(R)
+            if sp is not None:
+                self.sym_lnf = sp_syms[-1][0]
+                self.lnf, self.meanf, self.rstdf = self.sym_lnf.t, f(Rs), f(Rs)
+            else:
+                self.lnf, self.meanf, self.rstdf = e(R, d), f(R), f(R)
             self.logits = torch.zeros(R, Vp, dtype=dt, device=dev)
             self.rowloss = f(R)
             self.prob = f(R)
@@ -112,9 +148,13 @@ class _Slot:
 
 class GPT:
     def __init__(self, cfg: Config, device="cpu", dtype=torch.bfloat16, tp=1, tp_rank=0, first=True, last=True,
-                 untied_head=False, n_slots=1, dp=1, alloc=None, defer_dw=False):
+                 untied_head=False, n_slots=1, dp=1, alloc=None, defer_dw=False, sp=None):
+        """``sp``: the fused tensor-parallel operators (parallel.fused.FusedTP or FusedTPEmu) to run the
+        layers sequence-parallel with; None keeps every activation replicated over the TP group."""
         assert cfg.d_model % cfg.n_head == 0 and cfg.n_head % tp == 0
+        assert sp is None or (tp > 1 and cfg.batch % tp == 0), "sequence parallelism splits whole sequences over tp > 1 ranks"
         self.cfg, self.tp, self.tp_rank = cfg, tp, tp_rank
+        self.sp = sp
         self.first, self.last = first, last
         self.device, self.dtype = torch.device(device), dtype
         # a separate head matrix exists on the last stage of a multi-stage pipeline (tied to the
@@ -127,19 +167,34 @@ class GPT:
         self.Vp = _pad64(cfg.vocab)
         # deferred weight gradients: backward only stores each layer's output gradients; flush_dw()
         # forms all weight and bias gradients of the step in one pass over every micro-batch
-        self.group = _SlotGroup(cfg, tp, self.device, dtype, n_slots) if defer_dw else None
-        self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp, self.group, i) for i in range(n_slots)]
+        self.group = _SlotGroup(cfg, tp, self.device, dtype, n_slots, sp) if defer_dw else None
         R, d = cfg.batch * cfg.seq, cfg.d_model
         dl, fo = d // tp, 4 * d // tp
         e = lambda *s: _buf(s, dtype, self.device)
+        Rs = R // tp if sp is not None else R
+        sp_syms = [None] * n_slots
+        self.sym_dx = None
+        if sp is not None:
+            # per slot: LayerNorm outputs of every layer (unless the slot group holds them) and of the final
+            # norm; shared: two gathered gradient buffers (outside the slot group) and the stage-input gradient
+            kw = {} if not sp.emulated else dict(dtype=dtype)
+            per_slot = (0 if defer_dw else 2 * cfg.n_layer) + (1 if last else 0)
+            if per_slot:
+                syms, _ = sp.sym_rows(R, d, count=per_slot * n_slots, **kw)
+                sp_syms = [syms[i * per_slot:(i + 1) * per_slot] for i in range(n_slots)]
+            (self.sym_dx, _) = sp.sym_rows(R, d, count=3, **kw)
+            self.sym_dx = [g[0] for g in self.sym_dx]
+        self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp, self.group, i, sp, sp_syms[i])
+                      for i in range(n_slots)]
         # backward scratch, shared by all layers and slots
-        self.s_dx = [e(R, d), e(R, d)]
-        self.s_dln = e(R, d)
+        self.s_dx = [e(Rs, d), e(Rs, d)]
+        self.s_dln = e(Rs, d)
+        self.s_dln_full = e(R, d) if sp is not None and last else None
         self.s_dpre = e(R, fo)
         self.s_datt = e(R, dl)
         self.s_dqkv = e(R, 3 * dl)
         self.s_delta = torch.empty(cfg.batch, cfg.n_head // tp, cfg.seq, dtype=torch.float32, device=self.device)
-        self.s_lnpart = torch.zeros(ops.layernorm_bwd_scratch_elems(R, d) if self.device.type == "cuda" else 2 * d,
+        self.s_lnpart = torch.zeros(ops.layernorm_bwd_scratch_elems(Rs, d) if self.device.type == "cuda" else 2 * d,
                                     dtype=torch.float32, device=self.device)
         self.s_table = torch.empty(2 * cfg.vocab, dtype=torch.int32, device=self.device)
         self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -333,10 +388,34 @@ class GPT:
             if hi > lo:
                 dist.broadcast(g[lo:hi], src=self.vp_src[r], group=self.vp_group)
 
+    def forward_layers_sp(self, s: _Slot):
+        """Sequence-parallel layers: x, xmid are row shards; LayerNorm writes this rank's rows of a
+        symmetric [R, d] buffer that the column-parallel product gathers; the row-parallel products
+        reduce-scatter (+ bias + residual on the shard)."""
+        cfg, tp, f = self.cfg, self.tp, self.sp
+        B, T, Hl, hd = cfg.batch, cfg.seq, cfg.n_head // tp, cfg.head_dim
+        for l in range(cfg.n_layer):
+            a = s.layers[l]
+            x = s.x[l]
+            ops.layernorm_fwd(x, self.L(l, "ln1_w"), self.L(l, "ln1_b"), a["sym_ln1"].mine, a["mean1"], a["rstd1"])
+            f.ag_gemm_sym(a["sym_ln1"], self.L(l, "qkv_w"), a["qkv"], epi=ops.EPI_BIAS, bias=self.L(l, "qkv_b"))
+            ops.flash_fwd(a["qkv"], a["att"], a["lse"], B, T, Hl, hd)
+            f.gemm_rs(a["att"], self.L(l, "proj_w"), a["xmid"], bias=self.L(l, "proj_b"), resid=x)
+            ops.layernorm_fwd(a["xmid"], self.L(l, "ln2_w"), self.L(l, "ln2_b"), a["sym_ln2"].mine, a["mean2"], a["rstd2"])
+            f.ag_gemm_sym(a["sym_ln2"], self.L(l, "fc_w"), a["act"], epi=ops.EPI_BIAS_GELU, bias=self.L(l, "fc_b"),
+                          aux=a["pre"])
+            f.gemm_rs(a["act"], self.L(l, "fcproj_w"), s.x[l + 1], bias=self.L(l, "fcproj_b"), resid=a["xmid"])
+
     def forward_head(self, s: _Slot):
         cfg = self.cfg
+        w = self.head_weight()[self.v0:self.v1]
+        if self.sp is not None:
+            ops.layernorm_fwd(s.x[cfg.n_layer], self.params.c["lnf_w"], self.params.c["lnf_b"], s.sym_lnf.mine, s.meanf,
+                              s.rstdf)
+            self.sp.ag_gemm_sym(s.sym_lnf, w, s.logits[:, :self.v1 - self.v0])
+            return
         ops.layernorm_fwd(s.x[cfg.n_layer], self.params.c["lnf_w"], self.params.c["lnf_b"], s.lnf, s.meanf, s.rstdf)
-        ops.gemm(s.lnf, self.head_weight()[self.v0:self.v1], s.logits[:, :self.v1 - self.v0])
+        ops.gemm(s.lnf, w, s.logits[:, :self.v1 - self.v0])
 
     def forward(self, slot=0, x_in=None, loss_scale=1.0, accumulate_loss=False, compute_loss=True):
         """Forward of one micro-batch.  First stage embeds ``tok``; other stages take ``x_in``
@@ -346,10 +425,17 @@ class GPT:
         s = self.slots[slot]
         cfg = self.cfg
         if self.first:
-            ops.embed_fwd(s.tok, None, self.params.c["wte"], self.params.c["wpe"], s.x[0], cfg.seq)
+            tok = s.tok
+            if self.sp is not None:         # this rank's sequences only (a shard is a whole number of sequences)
+                rs = tok.numel() // self.tp
+                tok = tok[self.tp_rank * rs:(self.tp_rank + 1) * rs]
+            ops.embed_fwd(tok, None, self.params.c["wte"], self.params.c["wpe"], s.x[0], cfg.seq)
         else:
             ops.plan_call(s.x[0].copy_, x_in)
-        self.forward_layers(s)
+        if self.sp is not None:
+            self.forward_layers_sp(s)
+        else:
+            self.forward_layers(s)
         if not self.last:
             return s.x[cfg.n_layer]
         self.forward_head(s)
@@ -372,6 +458,8 @@ class GPT:
         the gradient w.r.t. the stage input (None on the first stage).  With ``loss_scale`` the
         same pass over the logits also produces the loss (mean CE x loss_scale into ``loss_acc``),
         so a training step reads the logits once."""
+        if self.sp is not None:
+            return self._backward_sp(slot, dx_out, inv_mb, coef, loss_scale, accumulate_loss)
         s = self.slots[slot]
         cfg, tp = self.cfg, self.tp
         R, V = cfg.batch * cfg.seq, cfg.vocab
@@ -446,6 +534,93 @@ class GPT:
             ops.embed_bwd(s.tok, dx, Gd["wte"], Gd["wpe"], B, T, table=self.s_table)
             return None
         return dx
+
+    def _backward_sp(self, slot, dx_out, inv_mb, coef, loss_scale, accumulate_loss):
+        """Backward of one micro-batch with sequence-parallel layers.  Gradients of the residual stream are
+        row shards; each is written into this rank's rows of a symmetric [R, d] buffer, gathered by the
+        input-gradient product of the row-parallel layer (all-gather -> GEMM, which leaves the full matrix
+        behind for the weight gradient), and the input gradients of the column-parallel layers come back
+        as shards (GEMM -> reduce-scatter)."""
+        s = self.slots[slot]
+        cfg, tp, f = self.cfg, self.tp, self.sp
+        R, V = cfg.batch * cfg.seq, cfg.vocab
+        B, T, Hl, hd = cfg.batch, cfg.seq, cfg.n_head // tp, cfg.head_dim
+        P, Gd = self.params.c, self.params.grad
+        defer = self.group is not None
+        L = cfg.n_layer
+        # gathered-gradient buffers: per layer and slot under deferred weight gradients, else two shared ones
+        d_out = (lambda l: s.layers[l]["sym_d_out"]) if defer else (lambda l: self.sym_dx[1])
+        d_mid = (lambda l: s.layers[l]["sym_d_mid"]) if defer else (lambda l: self.sym_dx[2])
+        top = d_out(L - 1)
+        if self.last:
+            want_loss = loss_scale is not None and not self.skip_loss
+            if self.vp_group is None:
+                ops.xent(s.logits, V, s.tgt, coef=coef, uniform=inv_mb / R, write_grad=True,
+                         rowloss=s.rowloss if want_loss else None)
+                dl = s.logits[:, :V]
+                # replicated head: every rank holds the full input gradient, its own rows are the shard
+                ops.gemm(dl, self.head_weight(), self.s_dln_full, b_mn=True)
+                rs = R // tp
+                ops.plan_call(self.s_dln.copy_, self.s_dln_full[self.tp_rank * rs:(self.tp_rank + 1) * rs])
+                ops.gemm(dl, s.lnf, self.head_grad(), a_mn=True, b_mn=True, accumulate=True)
+            else:
+                v0, v1 = self.v0, self.v1
+                ops.xent_stats(s.logits, v1 - v0, s.tgt, v0, s.stats)
+                ops.plan_call(self._vp_combine, s)
+                ops.xent_grad(s.logits, v1 - v0, s.tgt, v0, s.gmax, s.gsum, coef=coef, uniform=inv_mb / R)
+                dl = s.logits[:, :v1 - v0]
+                f.gemm_rs(dl, self.head_weight()[v0:v1], self.s_dln, b_mn=True)
+                ops.gemm(dl, s.lnf, self.head_grad()[v0:v1], a_mn=True, b_mn=True, accumulate=True)
+            if want_loss:
+                ops.sum_f32(s.rowloss, self.loss_acc, scale=loss_scale / R, accumulate=accumulate_loss)
+            ops.layernorm_bwd(self.s_dln, s.x[L], P["lnf_w"], s.meanf, s.rstdf, None, top.mine, Gd["lnf_w"],
+                              Gd["lnf_b"], self.s_lnpart)
+        else:
+            ops.plan_call(top.mine.copy_, dx_out)
+        for l in reversed(range(L)):
+            a = s.layers[l]
+            so, sm = d_out(l), d_mid(l)
+            nxt = d_out(l - 1) if l > 0 else self.sym_dx[0]
+            d_pre = a["d_pre"] if defer else self.s_dpre
+            d_qkv = a["d_qkv"] if defer else self.s_dqkv
+            # x[l+1] = xmid + act @ Wfp^T + b: gather d x[l+1], d_pre = (dx Wfp) * gelu'(pre)
+            f.ag_gemm_sym(so, self.L(l, "fcproj_w"), d_pre, b_mn=True, epi=ops.EPI_DGELU, aux=a["pre"])
+            if not defer:
+                ops.gemm(so.t, a["act"], self.G(l, "fcproj_w"), a_mn=True, b_mn=True, accumulate=True,
+                         colsum=self.G(l, "fcproj_b"))
+                ops.gemm(d_pre, a["ln2"], self.G(l, "fc_w"), a_mn=True, b_mn=True, accumulate=True, colsum=self.G(l, "fc_b"))
+            f.gemm_rs(d_pre, self.L(l, "fc_w"), self.s_dln, b_mn=True)
+            ops.layernorm_bwd(self.s_dln, a["xmid"], self.L(l, "ln2_w"), a["mean2"], a["rstd2"], so.mine, sm.mine,
+                              self.G(l, "ln2_w"), self.G(l, "ln2_b"), self.s_lnpart)
+            # xmid = x + att @ Wp^T + b
+            f.ag_gemm_sym(sm, self.L(l, "proj_w"), self.s_datt, b_mn=True)
+            if not defer:
+                ops.gemm(sm.t, a["att"], self.G(l, "proj_w"), a_mn=True, b_mn=True, accumulate=True,
+                         colsum=self.G(l, "proj_b"))
+            ops.flash_bwd(a["qkv"], a["att"], self.s_datt, a["lse"], d_qkv, self.s_delta, B, T, Hl, hd)
+            if not defer:
+                ops.gemm(d_qkv, a["ln1"], self.G(l, "qkv_w"), a_mn=True, b_mn=True, accumulate=True,
+                         colsum=self.G(l, "qkv_b"))
+            f.gemm_rs(d_qkv, self.L(l, "qkv_w"), self.s_dln, b_mn=True)
+            ops.layernorm_bwd(self.s_dln, s.x[l], self.L(l, "ln1_w"), a["mean1"], a["rstd1"], sm.mine, nxt.mine,
+                              self.G(l, "ln1_w"), self.G(l, "ln1_b"), self.s_lnpart)
+            if not defer and self.on_layer_grads is not None:
+                ops.plan_call_host(self.on_layer_grads, l)
+        dx = self.sym_dx[0]
+        if self.first:
+            # the embedding backward is replicated (no gradient exchange for wte / wpe): gather dx first
+            f.all_gather_rows(dx)
+            ops.embed_bwd(s.tok, dx.t, Gd["wte"], Gd["wpe"], B, T, table=self.s_table)
+            return None
+        return dx.mine
+
+    def sp_partial_grads(self):
+        """Gradients of the replicated parameters that each rank formed from its own rows only under
+        sequence parallelism (LayerNorm gains and biases): to be summed over the TP group once per step."""
+        names = ["lnf_w", "lnf_b"] if self.last else []
+        for l in range(self.cfg.n_layer):
+            names += ["l%d.%s" % (l, n) for n in ("ln1_w", "ln1_b", "ln2_w", "ln2_b")]
+        return [self.params.grad[n] for n in names]
 
     def flush_dw(self, lo=0, hi=None):
         """Weight and bias gradients of all layers from the stashed output gradients of micro-batch

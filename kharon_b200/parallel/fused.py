@@ -91,7 +91,25 @@ class _Ctx:
         self.gathers = 0
 
 
+class SymRows:
+    """A [rows, cols] bf16 matrix whose row block r (``rows / tp`` rows) is produced by TP rank r and read
+    by all ranks: the operand of the all-gather -> GEMM kernel.  ``t`` is this rank's full-size buffer in
+    symmetric memory; the rank writes its own block (``mine``), ``ag_gemm_sym`` fills in the others, so
+    afterwards ``t`` is the complete gathered matrix (kept for the weight-gradient products)."""
+
+    def __init__(self, t, shard_ptrs, rank, tp):
+        self.t, self.ptrs, self.rank, self.tp = t, shard_ptrs, rank, tp
+        self.rs = t.shape[0] // tp
+
+    @property
+    def mine(self):
+        return self.t[self.rank * self.rs:(self.rank + 1) * self.rs]
+
+
 class FusedTP:
+    #: sequence-parallel operands come from symmetric memory and are moved by the kernels themselves
+    emulated = False
+
     def __init__(self, mesh, device):
         self.group = mesh.tp_group
         self.tp, self.rank = mesh.c.tp, mesh.c.tp_rank
@@ -99,8 +117,8 @@ class FusedTP:
         self.ctx = {}
         self.max_ctas = 0
 
-    def _get(self, M, N, mode):
-        key = (M, N, mode)
+    def _get(self, M, N, mode, K=0):
+        key = (M, N, mode, K)
         c = self.ctx.get(key)
         if c is None:
             c = self.ctx[key] = _Ctx(M, N, self.tp, self.rank, self.device, self.group, mode)
@@ -110,6 +128,36 @@ class FusedTP:
         """A [rows, cols] tensor in symmetric memory plus the peers' addresses of it (for ag_gemm)."""
         t, h = _symm_alloc(rows * cols * 2, self.device, self.group)
         return t.view(dtype).view(rows, cols), [int(p) for p in h.buffer_ptrs], h
+
+    def sym_rows(self, rows, cols, count=1, slots=1):
+        """``count`` x ``slots`` SymRows of [rows, cols] carved from ONE symmetric allocation.  The ``slots``
+        matrices of one group are contiguous ([slots * rows, cols], slot-major), so that a product over
+        several micro-batch slots can read them as one operand.  Returns (list of lists, slab tensor)."""
+        per = rows * cols * 2
+        buf, h = _symm_alloc(count * slots * per, self.device, self.group)
+        self._slabs = getattr(self, "_slabs", []) + [(buf, h)]
+        base = [int(p) for p in h.buffer_ptrs]
+        rs = rows // self.tp
+        out = []
+        for i in range(count):
+            grp = []
+            for j in range(slots):
+                off = (i * slots + j) * per
+                t = buf[off:off + per].view(torch.bfloat16).view(rows, cols)
+                grp.append(SymRows(t, [b + off + r * rs * cols * 2 for r, b in enumerate(base)], self.rank, self.tp))
+            out.append(grp)
+        slab = buf[:count * slots * per].view(torch.bfloat16).view(count, slots * rows, cols)
+        return out, slab
+
+    def ag_gemm_sym(self, sym, b, out, *, b_mn=False, epi=0, bias=None, aux=None):
+        """out = epilogue(gathered(sym) @ op(b)); leaves the gathered matrix in ``sym.t``."""
+        K = sym.t.shape[1]
+        return self.ag_gemm(sym.ptrs, K, sym.rs, b, out, b_mn=b_mn, K=K, epi=epi, bias=bias, aux=aux, gather_buf=sym.t)
+
+    def all_gather_rows(self, sym):
+        """Complete ``sym.t`` from the ranks' own row blocks without a following product (NCCL all-gather;
+        used once per micro-batch in front of the replicated embedding backward)."""
+        ops.plan_call(dist.all_gather_into_tensor, sym.t, sym.mine, self.group)
 
     def _gemm(self, a, b, out, a_mn, b_mn, mode, bias, resid):
         if a_mn:
@@ -154,7 +202,7 @@ class FusedTP:
 
     def _launch_ag(self, ptrs, lda, b, b_mn, out, M, N, K, epi=0, bias=None, aux=None, gather_buf=None):
         # gather mode uses a context of its own: its "reduction" is local-only (no staging)
-        c = self._get(M, N, 2)
+        c = self._get(M, N, 2, K)
         c.gathers += 1
         if getattr(c, "gbuf_k", None) != K:      # per-block delivery counters (+ default landing buffer)
             c.gbuf = None
@@ -181,3 +229,68 @@ def install(model, mesh):
     f = FusedTP(mesh, model.device)
     model.fused_tp = f
     return f
+
+
+def make(mesh, device):
+    """The fused operators for ``device``: the NVLink kernels on a GPU, the collective-based evaluation
+    of the same interface elsewhere."""
+    return FusedTP(mesh, device) if torch.device(device).type == "cuda" else FusedTPEmu(mesh, device)
+
+
+class FusedTPEmu:
+    """The FusedTP interface evaluated with ``torch.distributed`` collectives and the operator layer:
+    the execution path of CPU ranks (gloo) and the oracle of the fused kernels in multi-rank tests.
+    Partial products are rounded to the storage dtype before they are summed, as the kernels do."""
+    emulated = True
+
+    def __init__(self, mesh, device):
+        self.group = mesh.tp_group
+        self.tp, self.rank = mesh.c.tp, mesh.c.tp_rank
+        self.device = torch.device(device)
+
+    def sym_rows(self, rows, cols, count=1, slots=1, dtype=torch.bfloat16):
+        slab = torch.zeros(count, slots * rows, cols, dtype=dtype, device=self.device)
+        out = [[SymRows(slab[i, j * rows:(j + 1) * rows], None, self.rank, self.tp) for j in range(slots)]
+               for i in range(count)]
+        return out, slab
+
+    def _partial(self, a, b, a_mn, b_mn):
+        M = a.shape[1] if a_mn else a.shape[0]
+        N = b.shape[1] if b_mn else b.shape[0]
+        part = torch.empty(M, N, dtype=a.dtype, device=a.device)
+        ops.gemm(a, b, part, a_mn=a_mn, b_mn=b_mn)
+        full = part.float()
+        dist.all_reduce(full, group=self.group)
+        return full
+
+    def gemm_ar(self, a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None):
+        full = self._partial(a, b, a_mn, b_mn)
+        if bias is not None:
+            full = full + bias.float()
+        if resid is not None:
+            full = full + resid.float()
+        out.copy_(full)
+        return out
+
+    def gemm_rs(self, a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None):
+        full = self._partial(a, b, a_mn, b_mn)
+        rs = full.shape[0] // self.tp
+        mine = full[self.rank * rs:(self.rank + 1) * rs]
+        if bias is not None:
+            mine = mine + bias.float()
+        if resid is not None:
+            mine = mine + resid.float()
+        out.copy_(mine)
+        return out
+
+    def all_gather_rows(self, sym):
+        parts = [torch.empty_like(sym.mine) for _ in range(self.tp)]
+        dist.all_gather(parts, sym.mine.contiguous(), group=self.group)
+        for r, t in enumerate(parts):
+            if r != self.rank:
+                sym.t[r * sym.rs:(r + 1) * sym.rs].copy_(t)
+
+    def ag_gemm_sym(self, sym, b, out, *, b_mn=False, epi=0, bias=None, aux=None):
+        self.all_gather_rows(sym)
+        ops.gemm(sym.t, b, out, b_mn=b_mn, epi=epi, bias=bias, aux=aux)
+        return out

@@ -70,7 +70,30 @@ def _tp_checks(mesh, device, out):
         e_ag = max(e_ag, _rel(got, torch.cat(full, 0).float() @ w.float().t()))
         torch.cuda.synchronize(device)
         dist.barrier(group=grp)          # peers have finished reading this shard before it is rewritten
-    out.update(gemm_ar=e_ar, gemm_rs=e_rs, ag_gemm=e_ag)
+    # epilogues of the all-gather form, operand in a SymRows buffer (the sequence-parallel layer's use)
+    from . import fused as fused_mod
+    e_epi = 0.0
+    (grp_syms, _) = f.sym_rows(rows * tp, K, count=1)
+    sym = grp_syms[0][0]
+    for it in range(2):
+        sym.mine.copy_((rn(rows, K) * 0.5).bfloat16())
+        w = (rn(N, K, gen=gs) * 0.1).bfloat16()
+        bias = rn(N, gen=gs).bfloat16()
+        full = [torch.empty(rows, K, device=device, dtype=torch.bfloat16) for _ in range(tp)]
+        dist.all_gather(full, sym.mine.contiguous(), group=grp)
+        a_full = torch.cat(full, 0).float()
+        pre_want = (a_full @ w.float().t() + bias.float()).to(torch.bfloat16)
+        got = torch.zeros(rows * tp, N, device=device, dtype=torch.bfloat16)
+        pre = torch.zeros_like(got)
+        f.ag_gemm_sym(sym, w, got, epi=ops.EPI_BIAS_GELU, bias=bias, aux=pre)
+        from ..ops import reference as ref
+        e_epi = max(e_epi, _rel(pre, pre_want), _rel(got, ref.gelu(pre_want.float())), _rel(sym.t, a_full))
+        got2 = torch.zeros_like(got)
+        f.ag_gemm_sym(sym, w, got2, epi=ops.EPI_DGELU, aux=pre)
+        e_epi = max(e_epi, _rel(got2, (a_full @ w.float().t()) * ref.gelu_grad(pre.float())))
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)
+    out.update(gemm_ar=e_ar, gemm_rs=e_rs, ag_gemm=e_ag, ag_gemm_epilogues=e_epi)
     return same
 
 

@@ -89,16 +89,34 @@ def _worker(rank, world, port, out_dir, part):
               mesh=mesh)
     if part in ("tp", "all"):
         # engine: fused path vs NCCL baseline path, TP = world
-        losses = {}
-        for fused in (False, True):
-            e = TrainEngine(fused_comm=fused, **kw)
+        losses, grads = {}, {}
+        for name, opt in (("nccl", dict(fused_comm=False)), ("fused_ar", dict(fused_comm=True, sp=False)),
+                          ("fused_sp", dict(fused_comm=True, sp=True))):
+            e = TrainEngine(**opt, **kw)
+            assert e.sp == (name == "fused_sp")
             idx, tgt = Rng(5).batch(e.tokens_per_step, 512)
+            # gradients of the first step, before the optimizer consumes them
+            e._upload(idx, tgt)
+            m = e.model
+            for mb in range(e.M):
+                e._stage_input(mb)
+                m.forward(slot=0, compute_loss=False)
+                m.backward(slot=0, inv_mb=1.0 / e.M, loss_scale=1.0 / e.M, accumulate_loss=mb > 0)
+            m.sync_head_grad()
+            e._sync_sp_grads()
+            torch.cuda.synchronize()
+            grads[name] = m.params.g.clone().cpu()
+            m.params.g.zero_()
             ls = []
             for _ in range(6):
                 e.train_step(idx, tgt)
                 ls.append(e.loss())
-            losses[fused] = ls
-        res["losses"] = losses
+            losses[name] = ls
+        res["losses"] = {False: losses["nccl"], True: losses["fused_ar"]}
+        res["losses_sp"] = losses["fused_sp"]
+        gn = grads["nccl"].norm()
+        res["grad_err_ar"] = ((grads["fused_ar"] - grads["nccl"]).norm() / gn).item()
+        res["grad_err_sp"] = ((grads["fused_sp"] - grads["nccl"]).norm() / gn).item()
         # vocabulary-parallel head (the default) against the replicated head, odd vocabulary
         kv = dict(kw, vocab=509)
         vp = {}
@@ -179,9 +197,13 @@ def test_fused_tp_kernels_two_gpus():
 def test_tp_engine_fused_matches_nccl_two_gpus():
     res = _run("tp")
     for r in res:
-        a, b = r["losses"][False], r["losses"][True]
+        a, b, c = r["losses"][False], r["losses"][True], r["losses_sp"]
         assert max(abs(x - y) for x, y in zip(a, b)) < 3e-2, (a, b)
-        assert b[-1] < b[0]
+        assert max(abs(x - y) for x, y in zip(a, c)) < 3e-2, (a, c)
+        assert b[-1] < b[0] and c[-1] < c[0]
+        # one step's gradients against the NCCL path: bf16 partial sums are the only difference
+        assert r["grad_err_ar"] < 1e-2, r["grad_err_ar"]
+        assert r["grad_err_sp"] < 1e-2, r["grad_err_sp"]
         va, vb = r["vp_losses"][False], r["vp_losses"][True]
         assert max(abs(x - y) for x, y in zip(va, vb)) < 2e-2, (va, vb)
         assert r["vp_werr"] < 1e-2, r["vp_werr"]      # Adam turns bf16-level gradient noise into sign flips

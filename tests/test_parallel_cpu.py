@@ -62,6 +62,12 @@ def _worker(rank, world, port, tp, pp, dp, steps, out_dir, mode):
         extra = dict(defer_dw=True, eager_p2p=False)
     elif mode == "not_deferred":
         extra = dict(defer_dw=False)
+    elif mode == "sp":                  # sequence-parallel layers (collective-based evaluation of the fused operators)
+        extra = dict(sp=True)
+    elif mode == "sp_not_deferred":
+        extra = dict(sp=True, defer_dw=False)
+    elif mode == "sp_replicated_head":
+        extra = dict(sp=True, vocab_parallel=False)
     e = TrainEngine(mesh=mesh, pp_split="3,1" if mode == "uneven" else None, **extra, **KW)
     data = _batches(mesh.c.dp_rank, steps, e.tokens_per_step, KW["vocab"])
     losses = []
@@ -129,6 +135,33 @@ def test_mesh_matches_single_process(tp, pp, dp):
             assert torch.allclose(_view(r, "wte"), P["wte"], rtol=1e-4, atol=2e-5)
         if stage == pp - 1 and pp > 1:      # tied copy on the last stage stays equal to the embedding
             assert torch.allclose(_view(r, "head_w"), P["wte"], rtol=1e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("tp,pp,mode", [(2, 1, "sp"), (2, 2, "sp"), (2, 2, "sp_not_deferred"), (2, 1, "sp_replicated_head")])
+def test_sequence_parallel_matches_single_process(tp, pp, mode):
+    """Sequence-parallel tensor parallelism (activations as row shards between the products, all-gather in
+    front of the column-parallel products, reduce-scatter behind the row-parallel ones, LayerNorm
+    gradients summed over the TP group) trains exactly like one process: losses and weights."""
+    steps = 3
+    ref_e, ref_losses = _single(steps, 1)
+    with tempfile.TemporaryDirectory() as d:
+        res = _launch(tp, pp, 1, steps, d, mode)
+    P = ref_e.model.params.p
+    nl = KW["layers"] // pp
+    for r in res:
+        _, stage, t = r["coord"]
+        if stage == pp - 1:
+            assert max(abs(a - b) for a, b in zip(r["losses"], ref_losses)) < 2e-5
+        gl = stage * nl
+        for name in ("ln1_w", "ln2_b", "proj_b"):          # replicated parameters, gradients from row shards
+            assert torch.allclose(_view(r, "l0." + name), P["l%d.%s" % (gl, name)], rtol=1e-4, atol=2e-5), name
+        fp = _view(r, "l%d.fcproj_w" % (nl - 1))
+        d_ = KW["d_model"]
+        want = P["l%d.fcproj_w" % (gl + nl - 1)][:, t * 4 * d_ // tp:(t + 1) * 4 * d_ // tp]
+        assert torch.allclose(fp, want, rtol=1e-4, atol=2e-5)
+        if stage == 0:
+            assert torch.allclose(_view(r, "wte"), P["wte"], rtol=1e-4, atol=2e-5)
+            assert torch.allclose(_view(r, "wpe"), P["wpe"], rtol=1e-4, atol=2e-5)
 
 
 @pytest.mark.parametrize("mode", ["classic_deferred", "not_deferred"])
