@@ -611,7 +611,9 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
     kh_set_error("gemm_comm: the all-gather form has no reduction (mode must be 2)");
     return -1;
   }
-  if (N % 8 || ldo % 8 || ((uintptr_t)out & 15)) { kh_set_error("gemm_comm: N and the output pitch must be multiples of 8"); return -1; }
+  // the all-gather form without an epilogue writes its output only through clipped TMA stores: any N
+  const bool ragged_ok = mode == MODE_LOCAL && epi == EPI_NONE;
+  if ((N % 8 && !ragged_ok) || ldo % 8 || ((uintptr_t)out & 15)) { kh_set_error("gemm_comm: N and the output pitch must be multiples of 8"); return -1; }
   if (gather && (a_mn || lda != K || !gather_buf || !blk_ready || !epoch_ptr)) {
     kh_set_error("gemm_comm: gather mode needs row-major contiguous shards (lda == K), a gather buffer, block counters and an epoch word");
     return -1;
