@@ -150,6 +150,8 @@ class TrainEngine:
         if self.defer_dw and c.pp > 1 and eager_p2p is not False:
             from .parallel import p2p
             if self.device.type == "cuda" and fused_comm:
+                from .parallel import fused as fused_mod
+                fused_mod.align_allocation_counts(self.mesh, dev)      # the mailbox rendezvous spans stages
                 self.box = p2p.Mailbox(self.mesh, dev, n_micro, R, d_model, dtype)
             elif dist.get_backend() == "gloo":
                 self.box = p2p.DistMailbox(self.mesh, dev, n_micro, R, d_model, dtype)

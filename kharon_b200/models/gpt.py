@@ -178,10 +178,11 @@ class GPT:
             # per slot: LayerNorm outputs of every layer (unless the slot group holds them) and of the final
             # norm; shared: two gathered gradient buffers (outside the slot group) and the stage-input gradient
             kw = {} if not sp.emulated else dict(dtype=dtype)
-            per_slot = (0 if defer_dw else 2 * cfg.n_layer) + (1 if last else 0)
-            if per_slot:
-                syms, _ = sp.sym_rows(R, d, count=per_slot * n_slots, **kw)
-                sp_syms = [syms[i * per_slot:(i + 1) * per_slot] for i in range(n_slots)]
+            # (the final norm's buffer is allocated on every stage: ranks that later rendezvous on a group
+            # spanning stages must have made the same sequence of symmetric allocations)
+            per_slot = (0 if defer_dw else 2 * cfg.n_layer) + 1
+            syms, _ = sp.sym_rows(R, d, count=per_slot * n_slots, **kw)
+            sp_syms = [syms[i * per_slot:(i + 1) * per_slot] for i in range(n_slots)]
             (self.sym_dx, _) = sp.sym_rows(R, d, count=3, **kw)
             self.sym_dx = [g[0] for g in self.sym_dx]
         self.slots = [_Slot(cfg, tp, self.device, dtype, first, last, self.Vp, self.group, i, sp, sp_syms[i])

@@ -30,6 +30,38 @@ MODE_AR, MODE_RS = 0, 1
 
 
 _alloc_seq = {}      # per process group: allocations rendezvoused on it so far (identical on its ranks)
+_alloc_total = 0     # symmetric allocations of this process, over all groups
+
+
+def align_allocation_counts(mesh, device):
+    """The symmetric-memory rendezvous pairs the buffers of a group's ranks by each process's running
+    allocation number, so two ranks can only rendezvous when they have made the same number of symmetric
+    allocations before -- over ALL groups.  Pipeline stages differ there (only the last stage owns the
+    head's buffers, contexts are created at first use), so before a rendezvous that spans stages every
+    rank pads its count to the maximum of the job with small allocations on its TP group (whose ranks
+    share a stage and therefore a count).  Collective over the world; raises instead of letting a
+    mismatched rendezvous run into the store time-out."""
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return
+    t = torch.tensor([_alloc_total, -_alloc_total], dtype=torch.int64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    mx, mn = int(t[0]), -int(t[1])
+    if mx == mn:
+        return
+    if mesh.tp_group is None:
+        raise RuntimeError("symmetric allocation counts differ between ranks (%d..%d) and there is no TP group to pad on"
+                           % (mn, mx))
+    keep = []
+    while _alloc_total < mx:
+        keep.append(_symm_alloc(16, device, mesh.tp_group))
+    _pads.extend(keep)
+    t = torch.tensor([_alloc_total, -_alloc_total], dtype=torch.int64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if int(t[0]) != -int(t[1]):
+        raise RuntimeError("symmetric allocation counts still differ after padding (%d..%d)" % (-int(t[1]), int(t[0])))
+
+
+_pads = []
 
 
 def _symm_alloc(nbytes, device, group):
@@ -44,6 +76,8 @@ def _symm_alloc(nbytes, device, group):
     eleven did.  The stamps turn a handle that pairs the buffer with anything but the peers'
     buffers of the same allocation into an error."""
     import torch.distributed._symmetric_memory as symm_mem
+    global _alloc_total
+    _alloc_total += 1
     t = symm_mem.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
     name = group.group_name if hasattr(group, "group_name") else group
     h = symm_mem.rendezvous(t, name)

@@ -122,7 +122,9 @@ class Mesh:
 
 
 def init_distributed(device_type=None, timeout_s=600):
-    """Join the job described by the torchrun environment.  Returns (rank, world, device)."""
+    """Join the job described by the torchrun environment.  Returns (rank, world, device).  The
+    collective / store time-out is ``timeout_s`` seconds unless KHARON_DIST_TIMEOUT_S overrides it."""
+    timeout_s = int(os.environ.get("KHARON_DIST_TIMEOUT_S", timeout_s))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
