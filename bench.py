@@ -127,7 +127,7 @@ def run_ours():
         gc.collect()
     eng = TrainEngine(L, d, H, V, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                       init=arg("init", "device", str), fused_comm=fused_comm, pp_split=arg("pp-split", "auto", str),
-                      sp=False if "--no-sp" in sys.argv else None)
+                      sp="--sp" in sys.argv)
     seq_par = bool(eng.sp)
     ntok = M * mb * S                                    # per replica and step
     data = Rng(42 + mesh.c.dp_rank)
@@ -205,7 +205,7 @@ def run_ours():
             Kr = min(K, 10)
             e2 = TrainEngine(L, d, H, 256, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                              init=arg("init", "device", str), fused_comm=fused_comm, untied_head=True,
-                             pp_split=arg("pp-split", "auto", str), sp=False if "--no-sp" in sys.argv else None)
+                             pp_split=arg("pp-split", "auto", str), sp="--sp" in sys.argv)
             data.batch_into(host_idx[0], host_tgt[0], 256)
             dev_idx.copy_(host_idx[0]); dev_tgt.copy_(host_tgt[0])
             for _ in range(W):

@@ -64,7 +64,7 @@ def main(argv=None):
     data_path, ckpt = f.str("data", "data/input.bin"), f.str("ckpt", "")
     synthetic, untied, resume = f.has("synthetic"), f.has("untied-head"), f.has("resume")
     fused = not f.has("no-fused-comm")
-    no_sp = f.has("no-sp", "keep activations replicated over the TP group (fused GEMM + all-reduce) instead of sequence-parallel")
+    use_sp = f.has("sp", "sequence-parallel TP layers (all-gather -> GEMM, GEMM -> reduce-scatter) instead of the fused GEMM + all-reduce")
     report = not f.has("no-report")
     dev_flag = f.str("device", "")
     trace = f.has("trace", "print a per-phase device-time table (CUDA events) at the end")
@@ -83,7 +83,7 @@ def main(argv=None):
     mlog = JsonlLogger(jsonl if rank == world - 1 else "")
     eng = TrainEngine(L, d, H, vocab, seq, mb, M, mesh=mesh, device=device,
                       dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, untied_head=untied,
-                      fused_comm=fused, trace=trace, heartbeat=hb, pp_split=pp_split, sp=False if no_sp else None)
+                      fused_comm=fused, trace=trace, heartbeat=hb, pp_split=pp_split, sp=use_sp)
     if synthetic or not os.path.exists(data_path):
         data = SyntheticData(vocab, M * mb, seq, 42)
     else:

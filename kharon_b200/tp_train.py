@@ -24,13 +24,13 @@ def main(argv=None):
     log, lr, vocab = f.int("log", 50), f.float("lr", 3e-4), f.int("vocab", 256)
     data_path, synthetic = f.str("data", "data/input.bin"), f.has("synthetic")
     fused = not f.has("no-fused-comm")
-    no_sp = f.has("no-sp")
+    use_sp = f.has("sp")
     dev_flag = f.str("device", "")
     f.maybe_help()
     rank, world, device = init_distributed(dev_flag or None)
     mesh = Mesh(world, 1, 1) if world > 1 else Mesh.single()
     eng = TrainEngine(L, d, H, vocab, seq, batch, 1, mesh=mesh, device=device,
-                      dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, fused_comm=fused, sp=False if no_sp else None)
+                      dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, fused_comm=fused, sp=use_sp)
     data = (SyntheticData(vocab, batch, seq, 42) if synthetic or not os.path.exists(data_path)
             else ByteData(data_path, batch, seq, 42))
     pin = device.type == "cuda"
