@@ -31,13 +31,16 @@ __device__ __forceinline__ float warp_max(float v) {
 // ------------------------------------------------------------------------------ embedding
 // out[r, :] = wte[tok[r], :] + wpe[pos[r], :]   (pos == nullptr: position r % T)
 __global__ void embed_fwd_k(const int* __restrict__ tok, const int* __restrict__ pos, const bf16* __restrict__ wte,
-                            const bf16* __restrict__ wpe, bf16* __restrict__ out, int rows, int d, int T, int V) {
+                            const bf16* __restrict__ wpe, bf16* __restrict__ out, int rows, int d, int T, int V, int* err) {
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.x;
   int t = tok[r];
-  t = min(max(t, 0), V - 1);
   int ps = pos ? pos[r] : r % T;
+  // index guard (the reference indexes wte / wpe unchecked, src/kernels/paged.cu:28): an id or position
+  // outside the tables is recorded in the status word (code 8) and clamped, never dereferenced
+  if ((t < 0 || t >= V || ps < 0 || ps >= T) && threadIdx.x == 0) atomicCAS(err, 0, 8);
+  t = min(max(t, 0), V - 1);
   ps = min(max(ps, 0), T - 1);
   const uint4* a = reinterpret_cast<const uint4*>(wte + (size_t)t * d);
   const uint4* b = reinterpret_cast<const uint4*>(wpe + (size_t)ps * d);
@@ -55,7 +58,7 @@ extern "C" int kh_embed_fwd(const void* tok, const void* pos, const void* wte, c
                             int d, int T, int V, void* stream) {
   if (d % 8) { kh_set_error("embed: d must be a multiple of 8"); return -1; }
   KH_LAUNCH(embed_fwd_k, rows, 128, 0, (cudaStream_t)stream, (const int*)tok, (const int*)pos, (const bf16*)wte,
-                                                      (const bf16*)wpe, (bf16*)out, rows, d, T, V);
+                                                      (const bf16*)wpe, (bf16*)out, rows, d, T, V, kh_error_word_dev());
   KH_LAUNCH_CHECK("embed_fwd");
   return 0;
 }
@@ -874,5 +877,58 @@ __global__ void fill_u32_k(uint32_t* p, long n, uint32_t v) {
 extern "C" int kh_fill_u32(void* p, long n, unsigned v, void* stream) {
   KH_LAUNCH(fill_u32_k, 1184, 256, 0, (cudaStream_t)stream, (uint32_t*)p, n, v);
   KH_LAUNCH_CHECK("fill_u32");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------ GRPO
+// Group-relative advantages and per-token loss coefficients on the device (host versions:
+// kh_grpo_advantages / kh_grpo_coef of the runtime library; reference src/core/grpo.c:7-20 and
+// src/grpo_train.c:164-174, which round-trip p_cur / p_ref through the host every step).
+//   adv[g, i]  = (r[g, i] - mean_g) / (std_g (population) + eps)                 one thread per group, in double
+//   coef[r, t] = (adv[r] - beta (1 - p_ref / max(p_cur, 1e-8))) / N   for t0 <= t <= t1, else 0;  N = rows (t1 - t0 + 1)
+__global__ void grpo_adv_k(const float* __restrict__ rew, float* __restrict__ adv, int n_groups, int group, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_groups) return;
+  const float* r = rew + (size_t)g * group;
+  double mean = 0.0;
+  for (int i = 0; i < group; i++) mean += r[i];
+  mean /= group;
+  double var = 0.0;
+  for (int i = 0; i < group; i++) { const double d = r[i] - mean; var += d * d; }
+  const double sd = sqrt(var / group);
+  for (int i = 0; i < group; i++) adv[(size_t)g * group + i] = (float)((r[i] - mean) / (sd + (double)eps));
+}
+__global__ void grpo_coef_k(const float* __restrict__ adv, const float* __restrict__ p_cur, const float* __restrict__ p_ref,
+                            float* __restrict__ coef, int rows, int T, int t0, int t1, float beta, float inv) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long)rows * T) return;
+  const int r = (int)(i / T), t = (int)(i % T);
+  float c = 0.f;
+  if (t >= t0 && t <= t1) {
+    const float pc = fmaxf(p_cur[i], 1e-8f);
+    c = (adv[r] - beta * (1.f - p_ref[i] / pc)) * inv;
+  }
+  coef[i] = c;
+}
+extern "C" int kh_grpo_advantages_dev(const void* rew, void* adv, int n_groups, int group, float eps, void* stream) {
+  if (n_groups <= 0 || group <= 0) { kh_set_error("grpo_advantages: empty problem"); return -1; }
+  KH_LAUNCH(grpo_adv_k, cdiv(n_groups, 128), 128, 0, (cudaStream_t)stream, (const float*)rew, (float*)adv, n_groups, group, eps);
+  KH_LAUNCH_CHECK("grpo_advantages");
+  return 0;
+}
+extern "C" int kh_grpo_coef_dev(const void* adv, const void* p_cur, const void* p_ref, void* coef, int rows, int T, int t0,
+                                int t1, float beta, void* stream) {
+  if (rows <= 0 || T <= 0) { kh_set_error("grpo_coef: empty problem"); return -1; }
+  t0 = t0 < 0 ? 0 : t0;
+  t1 = t1 > T - 1 ? T - 1 : t1;
+  const long n_masked = (long)rows * (t1 - t0 + 1 > 0 ? t1 - t0 + 1 : 0);
+  const float inv = n_masked > 0 ? 1.f / (float)n_masked : 0.f;
+  KH_LAUNCH(grpo_coef_k, cdiv((long)rows * T, 256), 256, 0, (cudaStream_t)stream, (const float*)adv, (const float*)p_cur,
+            (const float*)p_ref, (float*)coef, rows, T, t0, t1, beta, inv);
+  KH_LAUNCH_CHECK("grpo_coef");
   return 0;
 }

@@ -22,7 +22,7 @@ static inline int cdiv(long a, long b) { return (int)((a + b - 1) / b); }
 // One thread per 8 elements: copies k and v of every new token into its block slot.
 __global__ void append_kv_k(const bf16* __restrict__ qkv, int ld, bf16* __restrict__ kc, bf16* __restrict__ vc,
                             const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ btab,
-                            int max_lb, int bs, int d, int ntok) {
+                            int max_lb, int bs, int d, int ntok, int* err) {
   pdl_wait();
   pdl_launch_dependents();
   const int per = d / 8;
@@ -30,6 +30,8 @@ __global__ void append_kv_k(const bf16* __restrict__ qkv, int ld, bf16* __restri
   if (i >= (long)ntok * per) return;
   const int t = (int)(i / per), c = (int)(i % per) * 8;
   const int p = pos[t];
+  // index guard: a position beyond the block table is recorded (status code 8) and its store skipped
+  if (p < 0 || p / bs >= max_lb || slot[t] < 0) { atomicCAS(err, 0, 8); return; }
   const int blk = btab[(size_t)slot[t] * max_lb + p / bs];
   const size_t dst = ((size_t)blk * bs + (p % bs)) * d + c;
   const bf16* src = qkv + (size_t)t * ld;
@@ -41,7 +43,8 @@ extern "C" int kh_append_kv(const void* qkv, int ld, void* kc, void* vc, const v
   const int d = H * hd;
   if (d % 8) { kh_set_error("append_kv: H*hd must be a multiple of 8"); return -1; }
   KH_LAUNCH(append_kv_k, cdiv((long)ntok * d / 8, 256), 256, 0, (cudaStream_t)stream, 
-      (const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, d, ntok);
+      (const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, d, ntok,
+      kh_error_word_dev());
   KH_LAUNCH_CHECK("append_kv");
   return 0;
 }
@@ -59,9 +62,15 @@ template <int HD>
 __global__ void __launch_bounds__(128)
 paged_attn_k(const bf16* __restrict__ qkv, int ld, bf16* __restrict__ kc, bf16* __restrict__ vc,
              bf16* __restrict__ out, const int* __restrict__ pos, const int* __restrict__ slot,
-             const int* __restrict__ btab, int max_lb, int bs, int H, float scale, int max_ctx, int append) {
+             const int* __restrict__ btab, int max_lb, int bs, int H, float scale, int max_ctx, int append, int* err) {
   pdl_wait();
   pdl_launch_dependents();
+  // index guard: a context longer than the score buffer or the block table is recorded (status code 8)
+  // and the token skipped (uniform over the CTA)
+  if (pos[blockIdx.x] < 0 || pos[blockIdx.x] >= max_ctx || pos[blockIdx.x] / bs >= max_lb || slot[blockIdx.x] < 0) {
+    if (threadIdx.x == 0) atomicCAS(err, 0, 8);
+    return;
+  }
   extern __shared__ float sm[];
   constexpr int TPR = HD / 8;               // threads per value row
   constexpr int GROUPS = 128 / TPR;         // value rows in flight
@@ -151,7 +160,7 @@ extern "C" int kh_paged_attn(const void* qkv, int ld, void* kc, void* vc, void* 
     if (smem > attr) { cudaFuncSetAttribute(paged_attn_k<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; } \
     KH_LAUNCH((paged_attn_k<HD>), grid, 128, smem, st, (const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (bf16*)out,                 \
                                               (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, H,    \
-                                              scale, max_ctx, append);                                               \
+                                              scale, max_ctx, append, kh_error_word_dev());                          \
   }
   if (hd == 128) LAUNCH(128)
   else if (hd == 64) LAUNCH(64)

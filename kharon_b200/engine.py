@@ -95,6 +95,7 @@ class TrainEngine:
         fused_comm = bool(fused_comm and dtype == torch.bfloat16)
         self.tracer = Tracer(enabled=bool(trace))     # per-phase CUDA-event timeline (forward / backward / p2p / optimizer)
         self.heartbeat = heartbeat                     # utils.watchdog.Heartbeat: peers are checked before every step
+        self.p2p_timeout_s = 120.0                     # guarded NCCL / gloo point-to-point waits (with a heartbeat)
         c = self.mesh.c
         self.device = torch.device(device)
         self.stage_layers = stage_split(layers, c.pp, d_model, vocab // (c.tp if vocab_parallel else 1), pp_split)
@@ -222,7 +223,12 @@ class TrainEngine:
     def _p2p(self, ops_):
         if not ops_:
             return
-        for w in dist.batch_isend_irecv(ops_):
+        works = dist.batch_isend_irecv(ops_)
+        if self.heartbeat is not None:      # a dead neighbour becomes an exception instead of a blocked rank
+            from .utils.watchdog import guarded
+            guarded(works, self.heartbeat, timeout_s=self.p2p_timeout_s, what="pipeline send/recv")
+            return
+        for w in works:
             w.wait()
 
     def _stage_input(self, mb):

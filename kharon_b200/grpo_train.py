@@ -22,6 +22,7 @@ def main(argv=None):
     log, sft, rllr = f.int("log", 20), f.int("sft", 200), f.float("rllr", 1e-4)
     task_name = f.str("task", "add")
     seq = f.int("seq", 0)
+    hb_s = f.float("heartbeat", 0.0, "seconds after which a silent rank counts as dead (0 = off)")
     dev_flag = f.str("device", "")
     f.maybe_help()
     rank, world, device = init_distributed(dev_flag or None)
@@ -31,6 +32,11 @@ def main(argv=None):
     tr = GRPOTrainer(task, L, d, H, seq or None, G, NP // world, lr, rllr, temp, beta, device=device,
                      dtype=torch.bfloat16 if device.type == "cuda" else torch.float32,
                      dp_group=dist.group.WORLD if world > 1 else None, dp_rank=rank, dp=world)
+    hb = None
+    if hb_s > 0 and world > 1:      # checked before every step's gradient exchange
+        from .utils.watchdog import Heartbeat
+        hb = Heartbeat(rank, world, interval_s=min(1.0, hb_s / 4), timeout_s=hb_s)
+    tr.heartbeat = hb
     say = print if rank == 0 else (lambda *a, **k: None)
     say("GRPO %s: L=%d d=%d H=%d  G=%d prompts=%d (B=%d per rank, %d ranks) T=%d  lr=%g temp=%g beta=%g sft=%d" %
         (task_name, L, d, H, G, NP, tr.B, world, tr.T, lr, temp, beta, sft))

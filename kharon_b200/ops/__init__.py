@@ -331,6 +331,27 @@ def sum_f32(x, out, scale=1.0, accumulate=False):
     _call(_lib().kh_sum_f32, 1, x.data_ptr(), x.numel(), float(scale), out.data_ptr(), int(accumulate), _stream())
 
 
+# ----------------------------------------------------------------------------------- GRPO
+def grpo_advantages(rew, n_groups, group, eps, out):
+    """out[g, i] = (rew[g, i] - mean_g) / (population std_g + eps) (src/core/grpo.c:7-20), where the rewards live."""
+    if not rew.is_cuda:
+        _native.rt().kh_grpo_advantages(rew.data_ptr(), n_groups, group, eps, out.data_ptr())
+        return out
+    _call(_lib().kh_grpo_advantages_dev, 1, rew.data_ptr(), out.data_ptr(), n_groups, group, float(eps), _stream())
+    return out
+
+
+def grpo_coef(adv, p_cur, p_ref, rows, T, t0, t1, beta, out):
+    """Per-token coefficient of the GRPO gradient (src/grpo_train.c:164-174): for the completion positions
+    t0..t1 (adv[row] - beta (1 - p_ref / max(p_cur, 1e-8))) / (rows (t1 - t0 + 1)), zero elsewhere."""
+    if not adv.is_cuda:
+        _native.rt().kh_grpo_coef(adv.data_ptr(), p_cur.data_ptr(), p_ref.data_ptr(), rows, T, t0, t1, beta, out.data_ptr())
+        return out
+    _call(_lib().kh_grpo_coef_dev, 1, adv.data_ptr(), p_cur.data_ptr(), p_ref.data_ptr(), out.data_ptr(), rows, T, t0, t1,
+          float(beta), _stream())
+    return out
+
+
 # ---------------------------------------------------------------------------------- AdamW
 def adamw(p, g, m, v, pb, *, lr, beta1, beta2, eps, wd, step, grad_scale=1.0, zero_grad=True):
     """One fused pass: moments, decoupled decay on every element, fp32 master update, bf16

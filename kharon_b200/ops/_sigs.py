@@ -39,6 +39,8 @@ def declare(lib):
 # entry points that live in translation units added after the first ones; declared when present
 _OPTIONAL = {
     "kh_gemm_f32": (i32, vp, long_, long_, vp, long_, long_, vp, long_, i32, i32, i32, vp),
+    "kh_grpo_advantages_dev": (i32, vp, vp, i32, i32, f32, vp),
+    "kh_grpo_coef_dev": (i32, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp),
     "kh_xent_stats": (i32, vp, i32, i32, vp, i32, vp, i32, vp),
     "kh_xent_grad": (i32, vp, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp),
     "kh_wait_probe": (i32, vp, u32, u32, vp, vp),

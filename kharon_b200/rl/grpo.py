@@ -102,6 +102,10 @@ class GRPOTrainer:
         self.h_idx = torch.zeros(self.B * self.T, dtype=torch.int32, pin_memory=pin)
         self.h_tgt = torch.zeros(self.B * self.T, dtype=torch.int32, pin_memory=pin)
         self.d_coef = torch.zeros(self.B * self.T, dtype=torch.float32, device=self.device)
+        self.h_rew = torch.zeros(self.B, dtype=torch.float32, pin_memory=pin)
+        self.d_rew = torch.zeros(self.B, dtype=torch.float32, device=self.device)
+        self.d_adv = torch.zeros(self.B, dtype=torch.float32, device=self.device)
+        self.d_pcur = torch.zeros(self.B * self.T, dtype=torch.float32, device=self.device)
         self.stats = {}
 
     def _make(self, seed, dtype):
@@ -113,15 +117,24 @@ class GRPOTrainer:
 
     # ------------------------------------------------------------------ helpers
     def _fill_rows(self, rows):
-        T = self.T
-        for r, seq in enumerate(rows):
-            for t in range(T):
-                self.h_idx[r * T + t] = seq[t]
-                self.h_tgt[r * T + t] = seq[t + 1] if t < T - 1 else 0
+        """Token rows -> the pinned input / target staging buffers (target = next token, 0 after the last)."""
+        t = torch.tensor(rows, dtype=torch.int32)                     # [B, T]
+        self.h_idx.view(self.B, self.T).copy_(t)
+        tg = self.h_tgt.view(self.B, self.T)
+        tg[:, :-1].copy_(t[:, 1:])
+        tg[:, -1].zero_()
+
+    heartbeat = None        # utils.watchdog.Heartbeat of the job, when the entry point set one up
 
     def _sync_grads(self):
         if self.dp > 1:
-            dist.all_reduce(self.policy.params.g, group=self.dp_group)
+            if self.heartbeat is not None:
+                from ..utils.watchdog import guarded
+                self.heartbeat.check()
+                guarded(dist.all_reduce(self.policy.params.g, group=self.dp_group, async_op=True), self.heartbeat,
+                        timeout_s=120.0, group=self.dp_group, what="gradient all-reduce")
+            else:
+                dist.all_reduce(self.policy.params.g, group=self.dp_group)
             self.policy.params.g.div_(self.dp)
 
     def sft_step(self):
@@ -155,23 +168,24 @@ class GRPOTrainer:
         self.engine.set_sampling(self.temp, 0x1234 * step + 1 + 7919 * self.dp_rank)
         probs = [task.sample(self.rng) for _ in range(NP)]
         outs, st, ms = self.engine.generate_groups([p for p, _ in probs], G, task.nnew)
-        rows, rew = [], torch.zeros(B)
+        rows, rew = [], self.h_rew
         for pi, (p, ans) in enumerate(probs):
             for g in range(G):
                 seq = (outs[pi][g] + [0] * T)[:T]
                 rows.append(seq)
                 rew[pi * G + g] = task.reward(seq[task.plen:task.plen + task.nnew], ans)
-        adv = advantages(rew, NP, G, 1e-4)
+        # rewards go up (B floats); advantages, p(action) of both models and the coefficients stay on the device
+        self.d_rew.copy_(rew, non_blocking=True)
+        ops.grpo_advantages(self.d_rew, NP, G, 1e-4, self.d_adv)
         self._fill_rows(rows)
         m, ref = self.policy, self.ref
         m.set_input(self.h_idx, self.h_tgt)
         m.forward(compute_loss=False)
-        p_cur = m.gather_prob().clone()
+        self.d_pcur.copy_(m.gather_prob())
         ref.set_input(self.h_idx, self.h_tgt)
         ref.forward(compute_loss=False)
         p_ref = ref.gather_prob()
-        coef = coefficients(adv, p_cur, p_ref, B, T, task.plen - 1, T - 2, self.beta)
-        self.d_coef.copy_(coef, non_blocking=True)
+        ops.grpo_coef(self.d_adv, self.d_pcur, p_ref, B, T, task.plen - 1, T - 2, self.beta, self.d_coef)
         m.backward(coef=self.d_coef)
         self._sync_grads()
         m.adamw_step(self.rllr, 0.9, 0.95, 1e-8, 0.0)

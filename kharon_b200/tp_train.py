@@ -25,12 +25,18 @@ def main(argv=None):
     data_path, synthetic = f.str("data", "data/input.bin"), f.has("synthetic")
     fused = not f.has("no-fused-comm")
     use_sp = f.has("sp")
+    hb_s = f.float("heartbeat", 0.0, "seconds after which a silent rank counts as dead (0 = off)")
     dev_flag = f.str("device", "")
     f.maybe_help()
     rank, world, device = init_distributed(dev_flag or None)
     mesh = Mesh(world, 1, 1) if world > 1 else Mesh.single()
+    hb = None
+    if hb_s > 0 and world > 1:
+        from .utils.watchdog import Heartbeat
+        hb = Heartbeat(rank, world, interval_s=min(1.0, hb_s / 4), timeout_s=hb_s)
     eng = TrainEngine(L, d, H, vocab, seq, batch, 1, mesh=mesh, device=device,
-                      dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, fused_comm=fused, sp=use_sp)
+                      dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, fused_comm=fused, sp=use_sp,
+                      heartbeat=hb)
     data = (SyntheticData(vocab, batch, seq, 42) if synthetic or not os.path.exists(data_path)
             else ByteData(data_path, batch, seq, 42))
     pin = device.type == "cuda"

@@ -63,3 +63,47 @@ class Heartbeat:
         dead = self.dead_ranks()
         if dead:
             raise RankFailure("ranks %s stopped sending heartbeats" % dead)
+
+
+class CollectiveTimeout(RuntimeError):
+    pass
+
+
+def abort_group(group=None):
+    """Best effort: tear the communicator of ``group`` down so that kernels of a collective that can no
+    longer complete leave the stream (NCCL: ncclCommAbort through the process group; other backends have
+    nothing to abort).  Never raises."""
+    try:
+        pg = group if group is not None else dist.distributed_c10d._get_default_group()
+        backend = pg._get_backend(__import__("torch").device("cuda")) if dist.get_backend(pg) == "nccl" else None
+        if backend is not None and hasattr(backend, "abort"):
+            backend.abort()
+            return True
+    except Exception:
+        pass
+    return False
+
+
+def guarded(work, heartbeat=None, timeout_s=60.0, group=None, poll_s=0.02, what="collective"):
+    """Wait for an asynchronous collective (``async_op=True`` work handle, or a list of them) the way a
+    job that must not hang waits: poll its completion from the host, and between polls look at the
+    peers' heartbeats.  A peer that died turns into ``RankFailure`` within the heartbeat time-out, a
+    collective that does not finish within ``timeout_s`` into ``CollectiveTimeout``; in both cases the
+    communicator is aborted first (the reference's NCCL_CK only prints and exits on a local error and
+    blocks forever on a remote one, src/parallel/comms.cu:7-14)."""
+    works = list(work) if isinstance(work, (list, tuple)) else [work]
+    t0 = time.monotonic()
+    while True:
+        if all(w.is_completed() for w in works):
+            for w in works:
+                w.wait()            # surfaces an asynchronous error of the collective as an exception
+            return
+        if heartbeat is not None:
+            dead = heartbeat.dead_ranks()
+            if dead:
+                abort_group(group)
+                raise RankFailure("%s cannot complete: ranks %s stopped sending heartbeats" % (what, dead))
+        if time.monotonic() - t0 > timeout_s:
+            abort_group(group)
+            raise CollectiveTimeout("%s did not complete within %.0f s" % (what, timeout_s))
+        time.sleep(poll_s)

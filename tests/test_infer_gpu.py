@@ -106,3 +106,28 @@ def test_fp32_engine_on_gpu_is_token_exact():
     g, st, _ = InferEngine(gpu, block_size=4, max_seqs=16).generate_group(prompts[0], 8, 20)
     assert all(x == want[0] for x in g) and st["prefix_blocks_saved"] == 7 * (6 // 4)
     assert ops.error_word() == 0
+
+
+def test_index_guards_record_a_status_code_instead_of_reading_out_of_range():
+    """Token ids / positions outside the embedding tables and positions beyond a sequence's block table are
+    caught by the kernels' index guards: status word 8, the offending access clamped or skipped, no fault."""
+    V, T, d = 64, 16, 64
+    wte = torch.randn(V, d, device="cuda").bfloat16(); wpe = torch.randn(T, d, device="cuda").bfloat16()
+    tok = torch.tensor([3, 64, 5, -1], device="cuda", dtype=torch.int32)
+    pos = torch.tensor([0, 1, 16, 2], device="cuda", dtype=torch.int32)
+    out = torch.zeros(4, d, device="cuda", dtype=torch.bfloat16)
+    assert ops.error_word() == 0
+    ops.embed_fwd(tok, pos, wte, wpe, out, T)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 8 and ops.error_word() == 0          # reported once, then cleared
+    assert torch.equal(out[0], (wte[3].float() + wpe[0].float()).bfloat16())
+    H, hd, bs, max_lb = 2, 64, 4, 2
+    kc = torch.zeros(4, bs, H, hd, device="cuda", dtype=torch.bfloat16); vc = torch.zeros_like(kc)
+    btab = torch.tensor([[0, 1]], device="cuda", dtype=torch.int32)
+    qkv = torch.randn(2, 3 * H * hd, device="cuda").bfloat16()
+    p2 = torch.tensor([1, 9], device="cuda", dtype=torch.int32)         # position 9 needs a third block
+    sl = torch.zeros(2, device="cuda", dtype=torch.int32)
+    ops.append_kv(qkv, kc, vc, p2, sl, btab, bs, H, hd, 2)
+    torch.cuda.synchronize()
+    assert ops.error_word() == 8
+    assert torch.equal(kc[0, 1].reshape(-1), qkv[0, H * hd:2 * H * hd]) and float(kc[2:].abs().max()) == 0.0

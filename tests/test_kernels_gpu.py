@@ -460,3 +460,22 @@ def test_merge_attention_equals_attention_over_all_keys():
     o2, l2 = attn(k[:, 40:], v[:, 40:])
     o, l = ops.merge_attention(o1, l1, o2, l2)
     assert torch.allclose(o, o_all, atol=1e-5) and torch.allclose(l, l_all, atol=1e-5)
+
+
+def test_grpo_device_advantages_and_coefficients_match_host():
+    """Device versions of the group-relative advantages and the per-token GRPO coefficients against the
+    runtime library's host functions (reference src/core/grpo.c:7-20, src/grpo_train.c:164-174)."""
+    torch.manual_seed(30)
+    NP, G, T = 6, 8, 18
+    rows = NP * G
+    rew = torch.rand(rows)
+    rew[8:16] = 0.5                                   # a group with zero variance
+    p_cur, p_ref = torch.rand(rows * T) * 0.9 + 1e-3, torch.rand(rows * T) * 0.9 + 1e-3
+    adv_h, coef_h = torch.empty(rows), torch.empty(rows * T)
+    ops.grpo_advantages(rew, NP, G, 1e-4, adv_h)
+    ops.grpo_coef(adv_h, p_cur, p_ref, rows, T, 8, T - 2, 0.04, coef_h)
+    adv_d, coef_d = torch.empty(rows, device=DEV), torch.empty(rows * T, device=DEV)
+    ops.grpo_advantages(rew.to(DEV), NP, G, 1e-4, adv_d)
+    ops.grpo_coef(adv_d, p_cur.to(DEV), p_ref.to(DEV), rows, T, 8, T - 2, 0.04, coef_d)
+    assert torch.allclose(adv_d.cpu(), adv_h, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(coef_d.cpu(), coef_h, rtol=1e-4, atol=1e-7)

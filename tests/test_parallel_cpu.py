@@ -246,3 +246,44 @@ def test_dead_rank_is_detected_on_the_host():
         codes = [p.exitcode for p in ctx.processes]
         assert codes[1] == 3 and codes[0] == 0 and codes[2] == 0, codes
         assert open(os.path.join(d, "seen_0")).read() == "1"
+
+
+def _guard_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from kharon_b200.utils.watchdog import CollectiveTimeout, Heartbeat, RankFailure, guarded
+    hb = Heartbeat(rank, world, interval_s=0.2, timeout_s=1.5)
+    t = torch.ones(4)
+    guarded(dist.all_reduce(t, async_op=True), hb, timeout_s=20)          # a healthy collective passes through
+    assert t[0].item() == world
+    if rank == 1:
+        hb.stop()                 # the rank goes silent between steps and never joins the next collective
+        time.sleep(6)
+        os._exit(3)
+    t0 = time.time()
+    try:
+        guarded(dist.all_reduce(t, async_op=True), hb, timeout_s=30)
+        verdict = "completed"
+    except RankFailure as e:
+        verdict = "rank_failure:" + str(e)
+    except CollectiveTimeout:
+        verdict = "timeout"
+    open(os.path.join(out_dir, "guard_%d" % rank), "w").write("%s|%.1f" % (verdict, time.time() - t0))
+    hb.stop()
+    os._exit(0)
+
+
+def test_guarded_collective_raises_when_a_peer_never_joins():
+    """A collective whose peer went silent ends in RankFailure within the heartbeat time-out instead of
+    blocking until the process-group time-out (60 s here)."""
+    with tempfile.TemporaryDirectory() as d:
+        ctx = mp.spawn(_guard_worker, args=(3, _free_port(), d), nprocs=3, join=False)
+        for p in ctx.processes:
+            p.join(60)
+        for r in (0, 2):
+            verdict, secs = open(os.path.join(d, "guard_%d" % r)).read().split("|")
+            assert verdict.startswith("rank_failure") and "[1]" in verdict, verdict
+            assert float(secs) < 10, secs
