@@ -103,3 +103,26 @@ def test_fp32_gpu_step_matches_fp32_cpu():
     for m in ms:
         m.adamw_step(3e-4)
     assert torch.allclose(gpu.params.w.cpu(), cpu.params.w, rtol=1e-4, atol=3e-5)
+
+
+def test_two_stream_step_is_independent_of_stream_priorities():
+    """Race smoke test of the multi-stream step (optimizer buckets on a side stream under the backward pass,
+    input staging on a copy stream): the same run with the side streams at the opposite priority, and with
+    the optimizer kept on the compute stream, must give identical bits."""
+    from kharon_b200.engine import TrainEngine
+    outs = []
+    for variant in ("default", "high_priority_side_streams", "single_stream"):
+        e = TrainEngine(layers=3, d_model=128, heads=2, vocab=300, seq=64, mbatch=2, n_micro=2, device="cuda",
+                        bucket_optimizer=variant != "single_stream")
+        assert e.bucketed == (variant != "single_stream")
+        if variant == "high_priority_side_streams":
+            e.opt_stream = torch.cuda.Stream(e.device, priority=-1)
+            e.copy_stream = torch.cuda.Stream(e.device, priority=-1)
+        idx, tgt = Rng(11).batch(e.tokens_per_step, 300)
+        hi, ht = idx.pin_memory(), tgt.pin_memory()
+        for _ in range(5):
+            e.train_step(hi, ht)
+        outs.append((e.loss(), e.model.params.w.clone(), e.model.params.wb.clone()))
+    for o in outs[1:]:
+        assert o[0] == outs[0][0]
+        assert torch.equal(o[1], outs[0][1]) and torch.equal(o[2], outs[0][2])
