@@ -6,7 +6,7 @@
 // token rows are the narrow "B" operand, the accumulator in TMEM is out^T [128 weights x M]) and
 // splits K across CTAs so that every SM streams a slice of W:
 //
-//   grid = (ceil(N/128) n-tiles) x (split-K slices), one tile per CTA, at most 8 k-blocks of 64
+//   grid = (ceil(N/128) n-tiles) x (split-K slices), one tile per CTA, at most 4 k-blocks of 64
 //   per CTA, all of whose TMA loads are issued up front (no ring to recycle);
 //   split > 1: every CTA writes its fp32 partial to scratch; the CTA that arrives last at its
 //   n-tile (integer ticket) adds the slices in index order and runs the epilogue -- the result is
@@ -28,7 +28,7 @@
   } while (0)
 
 namespace {
-constexpr int TN = 128, BK = 64, UMMA_K = 16, MAX_KB = 8;
+constexpr int TN = 128, BK = 64, UMMA_K = 16, MAX_KB = 4;      // <= 4 k-blocks per CTA: two to three CTAs fit on an SM
 constexpr int COUNTER_SLOTS = 1024;
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_BIAS_RESID = 3 };
 
@@ -41,6 +41,7 @@ struct SkinnyParams {
   bf16* aux; int ldaux;
   const bf16* x; int ldx;            // raw activation rows (LayerNorm prologue only)
   const bf16* ln_w; const bf16* ln_b;  // non-null: y = LayerNorm(x) * ln_w + ln_b feeds the product
+  int w_static;         // the weights are not written by the kernel launched just before this one: stream them before it ends
   int* counters;        // [n_tiles], zero between launches
   float* partials;      // [split][MP][N]
   int* err;
@@ -50,8 +51,6 @@ template <int MP>   // padded row count = MMA N (16, 32 or 64)
 __global__ void __launch_bounds__(128, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const SkinnyParams p) {
-  pdl_wait();
-  pdl_launch_dependents();
   constexpr int W_BYTES = TN * BK * 2, X_BYTES = MP * BK * 2, STAGE = W_BYTES + X_BYTES;
   constexpr int TMEM_COLS = MP < 32 ? 32 : MP;
   extern __shared__ uint8_t smem_raw[];
@@ -84,11 +83,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   bool ok = true;
   const bool fuse_ln = (MP == 16) && p.ln_w != nullptr;
+  // Programmatic dependent launch: this CTA may be resident while the previous kernel of the stream is
+  // still running.  Weights that the previous kernel cannot have written (decode steps: the engine says
+  // so) are requested right away, so the weight stream of this product overlaps the tail of the previous
+  // one; everything an earlier kernel produces (the token rows) is touched after the wait.
+  if (tid == 0) {
+    for (int i = 0; i < nkb; i++) {
+      mbar_expect_tx(bar_full + 8 * i, fuse_ln ? W_BYTES : STAGE);
+      if (p.w_static) tma_load_2d(base + i * STAGE, &map_w, bar_full + 8 * i, (kb0 + i) * BK, nt * TN);
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int i = 0; i < nkb; i++) {
       const uint32_t sw = base + i * STAGE, sx = sw + W_BYTES;
-      mbar_expect_tx(bar_full + 8 * i, fuse_ln ? W_BYTES : STAGE);
-      tma_load_2d(sw, &map_w, bar_full + 8 * i, (kb0 + i) * BK, nt * TN);
+      if (!p.w_static) tma_load_2d(sw, &map_w, bar_full + 8 * i, (kb0 + i) * BK, nt * TN);
       if (!fuse_ln) tma_load_2d(sx, &map_x, bar_full + 8 * i, (kb0 + i) * BK, 0);
     }
   }
@@ -261,9 +271,11 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const SkinnyParams& p, 
 extern "C" long kh_gemm_skinny_scratch_elems(int M, int N, int K) {
   return COUNTER_SLOTS + (long)pick_split(N, K) * pad_rows(M) * N;
 }
-extern "C" int kh_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
-                              int epi, const void* bias, void* aux, int ldaux, void* scratch, const void* ln_w,
-                              const void* ln_b, void* stream) {
+// `weights_static` != 0: W is not written by the kernel that precedes this launch on the stream (true for
+// every product of a decode step); the kernel then starts streaming W before that kernel has finished.
+extern "C" int kh_gemm_skinny2(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
+                               int epi, const void* bias, void* aux, int ldaux, void* scratch, const void* ln_w,
+                               const void* ln_b, int weights_static, void* stream) {
   if (M < 1 || M > 64) { kh_set_error("gemm_skinny: M=%d outside [1, 64]", M); return -1; }
   if ((ln_w != nullptr) != (ln_b != nullptr)) { kh_set_error("gemm_skinny: LayerNorm needs both weight and bias"); return -1; }
   if (ln_w && (M > 16 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15))) {
@@ -285,10 +297,17 @@ extern "C" int kh_gemm_skinny(const void* x, int ldx, const void* W, int ldw, vo
   p.kb_per_cta = (p.num_kb + split - 1) / split;
   p.out = (bf16*)out; p.ldo = ldo; p.epi = epi; p.bias = (const bf16*)bias; p.aux = (bf16*)aux; p.ldaux = ldaux;
   p.x = (const bf16*)x; p.ldx = ldx; p.ln_w = (const bf16*)ln_w; p.ln_b = (const bf16*)ln_b;
+  p.w_static = weights_static;
   p.counters = (int*)scratch; p.partials = (float*)scratch + COUNTER_SLOTS;
   p.err = kh_error_word_dev();
   cudaStream_t st = (cudaStream_t)stream;
   if (MP == 16) return launch<16>(mw, mx, p, n_tiles, split, st);
   if (MP == 32) return launch<32>(mw, mx, p, n_tiles, split, st);
   return launch<64>(mw, mx, p, n_tiles, split, st);
+}
+
+extern "C" int kh_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
+                              int epi, const void* bias, void* aux, int ldaux, void* scratch, const void* ln_w,
+                              const void* ln_b, void* stream) {
+  return kh_gemm_skinny2(x, ldx, W, ldw, out, ldo, M, N, K, epi, bias, aux, ldaux, scratch, ln_w, ln_b, 0, stream);
 }

@@ -144,7 +144,7 @@ class InferEngine:
     def _lin(self, x, w, out, epi=ops.EPI_NONE, bias=None, aux=None):
         """Column-parallel / replicated linear layer: skinny kernel for decode-sized inputs."""
         if self.skinny is not None and x.shape[0] <= ops.SKINNY_BEST_ROWS:
-            ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux)
+            ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux, weights_static=True)
         else:
             ops.gemm(x, w, out, epi=epi, bias=bias, aux=aux)
 
@@ -152,7 +152,7 @@ class InferEngine:
         """LayerNorm followed by a linear layer: for decode-sized inputs the skinny kernel normalises
         the rows itself (no LayerNorm launch, ``ln_out`` stays unused)."""
         if self.skinny is not None and x.shape[0] <= ops.SKINNY_BEST_ROWS and x.shape[1] % 8 == 0:
-            ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux, ln_w=ln_w, ln_b=ln_b)
+            ops.gemm_skinny(x, w, out, self.skinny, epi=epi, bias=bias, aux=aux, ln_w=ln_w, ln_b=ln_b, weights_static=True)
         else:
             ops.layernorm_fwd(x, ln_w, ln_b, ln_out)
             self._lin(ln_out, w, out, epi, bias, aux)

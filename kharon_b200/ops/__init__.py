@@ -194,12 +194,14 @@ def gemm_skinny_scratch_elems(M, N, K):
     return int(_lib().kh_gemm_skinny_scratch_elems(M, N, K)) if torch.cuda.is_available() else 0
 
 
-def gemm_skinny(x, w, out, scratch, *, epi=EPI_NONE, bias=None, aux=None, ln_w=None, ln_b=None):
+def gemm_skinny(x, w, out, scratch, *, epi=EPI_NONE, bias=None, aux=None, ln_w=None, ln_b=None, weights_static=False):
     """out[M,N] = x[M,K] @ w[N,K]^T (+ epilogue) for M <= 64: the weight-streaming split-K kernel used
     by decode steps.  ``scratch`` (gemm_skinny_scratch_elems fp32, zeroed once) holds ticket counters
     and split-K partials.  Epilogues: EPI_NONE, EPI_BIAS, EPI_BIAS_GELU (aux = pre-activation out),
     EPI_BIAS_RESID (aux = residual in).  With ``ln_w``/``ln_b`` (M <= SKINNY_BEST_ROWS) the product is
-    taken of LayerNorm(x) * ln_w + ln_b, normalised inside the kernel."""
+    taken of LayerNorm(x) * ln_w + ln_b, normalised inside the kernel.  ``weights_static``: the kernel
+    launched just before this one on the stream does not write ``w`` (always true inside a decode step);
+    the weight stream then starts under that kernel's tail."""
     M, K = x.shape
     N = w.shape[0]
     if _use_reference(x):
@@ -208,9 +210,9 @@ def gemm_skinny(x, w, out, scratch, *, epi=EPI_NONE, bias=None, aux=None, ln_w=N
             ref.layernorm_fwd(x, ln_w, ln_b, y, None, None)
             x = y
         return ref.gemm(x, w, out, False, False, False, epi, bias, aux, 1.0)
-    _call(_lib().kh_gemm_skinny, 1, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+    _call(_lib().kh_gemm_skinny2, 1, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
           M, N, K, epi, _p(bias), _p(aux), aux.stride(0) if aux is not None else 0, scratch.data_ptr(), _p(ln_w),
-          _p(ln_b), _stream())
+          _p(ln_b), int(weights_static), _stream())
     return out
 
 

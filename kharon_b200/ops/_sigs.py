@@ -45,6 +45,7 @@ _OPTIONAL = {
     "kh_xent_grad": (i32, vp, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp),
     "kh_wait_probe": (i32, vp, u32, u32, vp, vp),
     "kh_gemm_skinny": (i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp),
+    "kh_gemm_skinny2": (i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, i32, vp),
     "kh_gemm_skinny_scratch_elems": (long_, i32, i32, i32),
     "kh_zero1_step": (i32, vp, vp, vp, vp, vp, vp, long_, i32, i32, f32, f32, f32, f32, f32, f32, f32, u32, i32, vp),
     "kh_gemm_comm": (i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, u32, u32,
