@@ -366,6 +366,15 @@ class GPT:
         self.v1 = min(self.cfg.vocab, self.v0 + vs)
         self.vp_group, self.vp_src, self.vp_block = group, list(src_ranks), vs
 
+    def _vp_stats_combine(self, s):
+        """Global row maximum, sum and loss from the ranks' vocabulary-slice statistics: one kernel over
+        peer memory when the fused operators are installed, else ``_vp_combine`` (collective + PyTorch)."""
+        f = self.fused_tp
+        if f is not None and hasattr(f, "vp_combine") and s.stats.is_cuda:
+            f.vp_combine(s.stats, s.tgt, s.gmax, s.gsum, s.rowloss)
+        else:
+            ops.plan_call(self._vp_combine, s)
+
     def _vp_combine(self, s):
         import torch.distributed as dist
         dist.all_gather([s.stats_all[r] for r in range(self.tp)], s.stats, group=self.vp_group)
@@ -481,7 +490,7 @@ class GPT:
             else:
                 v0, v1 = self.v0, self.v1
                 ops.xent_stats(s.logits, v1 - v0, s.tgt, v0, s.stats)
-                ops.plan_call(self._vp_combine, s)
+                self._vp_stats_combine(s)
                 ops.xent_grad(s.logits, v1 - v0, s.tgt, v0, s.gmax, s.gsum, coef=coef, uniform=inv_mb / R)
                 dl = s.logits[:, :v1 - v0]
                 self._row_parallel(dl, self.head_weight()[v0:v1], self.s_dln, b_mn=True)
@@ -567,7 +576,7 @@ class GPT:
             else:
                 v0, v1 = self.v0, self.v1
                 ops.xent_stats(s.logits, v1 - v0, s.tgt, v0, s.stats)
-                ops.plan_call(self._vp_combine, s)
+                self._vp_stats_combine(s)
                 ops.xent_grad(s.logits, v1 - v0, s.tgt, v0, s.gmax, s.gsum, coef=coef, uniform=inv_mb / R)
                 dl = s.logits[:, :v1 - v0]
                 f.gemm_rs(dl, self.head_weight()[v0:v1], self.s_dln, b_mn=True)

@@ -50,6 +50,7 @@ _OPTIONAL = {
     "kh_zero1_step": (i32, vp, vp, vp, vp, vp, vp, long_, i32, i32, f32, f32, f32, f32, f32, f32, f32, u32, i32, vp),
     "kh_gemm_comm": (i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, u32, u32,
                      C.c_uint64, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp),
+    "kh_vp_combine": (i32, vp, vp, vp, C.c_uint64, vp, vp, vp, vp, i32, i32, i32, vp),
     "kh_tmap_cache_limit": (long_, long_),
     "kh_zero1_max_grid": (i32,),
     "kh_set_pdl": (i32, i32),

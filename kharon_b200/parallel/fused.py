@@ -107,7 +107,7 @@ class _Ctx:
         self.M, self.N, self.tp, self.rank = M, N, tp, rank
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         # the all-gather form (mode 2) reduces nothing: no partial-tile staging
-        self.slot_bytes = tp * M * N * 2 if mode != 2 else 0
+        self.slot_bytes = tp * tiles * 128 * 256 * 2 if mode != 2 else 0      # whole tiles per source rank
         self.flag_bytes = tp * tiles * 4 * 4          # one counter per (source rank, tile, 64-column chunk)
         total = 2 * self.slot_bytes + self.flag_bytes + 256
         self.buf, self.h = _symm_alloc(total, device, group)
@@ -149,6 +149,7 @@ class FusedTP:
         self.tp, self.rank = mesh.c.tp, mesh.c.tp_rank
         self.device = torch.device(device)
         self.ctx = {}
+        self._vp = {}
         self.max_ctas = 0
 
     def _get(self, M, N, mode, K=0):
@@ -192,6 +193,26 @@ class FusedTP:
         """Complete ``sym.t`` from the ranks' own row blocks without a following product (NCCL all-gather;
         used once per micro-batch in front of the replicated embedding backward)."""
         ops.plan_call(dist.all_gather_into_tensor, sym.t, sym.mine, self.group)
+
+    def vp_combine(self, stats, tgt, gmax, gsum, rowloss):
+        """Vocabulary-parallel softmax statistics: push this rank's per-row (max, sum exp, target logit)
+        ``stats [R, 3]`` to the peers, wait for theirs and write the global ``gmax``, ``gsum`` and the
+        row losses -- one kernel (``csrc/comm/vp_combine.cu``), an ordinary recordable native call."""
+        R = stats.shape[0]
+        c = self._vp.get(R)
+        if c is None:
+            nblk = (R + 255) // 256
+            data = 2 * self.tp * R * 3 * 4
+            buf, h = _symm_alloc(data + self.tp * nblk * 4, self.device, self.group)
+            buf.zero_()
+            torch.cuda.synchronize(self.device)
+            h.barrier()
+            base = [int(p) for p in h.buffer_ptrs]
+            U = C.c_uint64 * self.tp
+            c = self._vp[R] = (buf, h, U(*base), U(*[b + data for b in base]),
+                               torch.zeros(2, dtype=torch.int32, device=self.device))
+        ops._call(_native.cuda().kh_vp_combine, 1, stats.data_ptr(), c[2], c[3], c[4].data_ptr(), tgt.data_ptr(),
+                  gmax.data_ptr(), gsum.data_ptr(), rowloss.data_ptr(), R, self.tp, self.rank, ops._stream())
 
     def _gemm(self, a, b, out, a_mn, b_mn, mode, bias, resid):
         if a_mn:

@@ -8,6 +8,7 @@ wherever the benchmark ran, not only where the 2-GPU test suite did.
 
 * ``gemm_ar`` / ``gemm_rs`` / ``ag_gemm``  (tp > 1) 1024 x 512 x 384 products, both operand layouts
   of B, with and without bias + residual, two calls each so that both staging parities are used;
+  ``vp_combine``: the vocabulary-parallel softmax statistics kernel against all_gather + PyTorch;
 * ``zero1_step``  (dp > 1) two optimizer steps of a small arena: fused pull-reduce + AdamW + bf16
   push kernel against reduce_scatter / AdamW kernel / all_gather over NCCL;
 * ``mailbox``  (pp > 1) a message put into the next stage's slot against an NCCL send / recv.
@@ -93,7 +94,25 @@ def _tp_checks(mesh, device, out):
         e_epi = max(e_epi, _rel(got2, (a_full @ w.float().t()) * ref.gelu_grad(pre.float())))
         torch.cuda.synchronize(device)
         dist.barrier(group=grp)
-    out.update(gemm_ar=e_ar, gemm_rs=e_rs, ag_gemm=e_ag, ag_gemm_epilogues=e_epi)
+    # vocabulary-parallel softmax statistics: exchange + combine kernel against all_gather + PyTorch
+    e_vp = 0.0
+    for it in range(2):
+        R = 1000
+        st = rn(R, 3)
+        st[:, 1] = st[:, 1].abs() + 0.1
+        tg = torch.randint(0, 2 * tp, (R,), device=device, dtype=torch.int32, generator=gs)
+        st[:, 2] = torch.where(tg % tp == r, st[:, 2], torch.full_like(st[:, 2], float("-inf")))
+        gm, gsum, rl = (torch.zeros(R, device=device) for _ in range(3))
+        f.vp_combine(st, tg, gm, gsum, rl)
+        allst = [torch.empty_like(st) for _ in range(tp)]
+        dist.all_gather(allst, st, group=grp)
+        allst = torch.stack(allst)
+        m, sm, xt = allst[..., 0], allst[..., 1], allst[..., 2]
+        wm = m.max(0).values
+        ws = (sm * torch.exp(m - wm)).sum(0)
+        wl = torch.log(ws) + wm - xt.max(0).values
+        e_vp = max(e_vp, float((gm - wm).abs().max()), float(((gsum - ws) / ws).abs().max()), float((rl - wl).abs().max()))
+    out.update(gemm_ar=e_ar, gemm_rs=e_rs, ag_gemm=e_ag, ag_gemm_epilogues=e_epi, vp_combine=e_vp)
     return same
 
 

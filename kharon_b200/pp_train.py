@@ -34,7 +34,11 @@ def _max_ms(ms, device, world):
     return float(t.item())
 
 
-def _timed(fn, n, device, world):
+def _timed(fn, n, device, world, warmup=2):
+    """Mean device time of ``fn`` over ``n`` calls after ``warmup`` untimed ones (which absorb launch-plan
+    recording, tensor-map creation and the first load of kernels a variant uses), maximum over ranks."""
+    for _ in range(warmup):
+        fn()
     if world > 1:
         dist.barrier()
     if device.type == "cuda":

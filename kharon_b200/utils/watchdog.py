@@ -27,6 +27,7 @@ class Heartbeat:
         self.store = store if store is not None else dist.distributed_c10d._get_default_store()
         self._stop = threading.Event()
         self._seen = {}        # rank -> (counter, time it last changed)
+        self._lock = threading.Lock()
         self.store.add("hb/%d" % rank, 1)
         self._t = threading.Thread(target=self._beat, daemon=True)
         self._t.start()
@@ -35,29 +36,36 @@ class Heartbeat:
         while not self._stop.wait(self.interval):
             try:
                 self.store.add("hb/%d" % self.rank, 1)
+                self._poll()          # keep "last seen moving" current, so that one later query is enough
             except Exception:
                 return
 
     def stop(self):
         self._stop.set()
 
-    def dead_ranks(self):
+    def _poll(self):
+        """Read the peers' counters; returns the ranks whose counter has not moved for ``timeout`` seconds
+        (or whose key cannot be read)."""
         now = time.monotonic()
         dead = []
-        for r in range(self.world):
-            if r == self.rank:
-                continue
-            try:
-                c = self.store.add("hb/%d" % r, 0)
-            except Exception:
-                dead.append(r)
-                continue
-            last = self._seen.get(r)
-            if last is None or last[0] != c:
-                self._seen[r] = (c, now)
-            elif now - last[1] > self.timeout:
-                dead.append(r)
+        with self._lock:
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                try:
+                    c = self.store.add("hb/%d" % r, 0)
+                except Exception:
+                    dead.append(r)
+                    continue
+                last = self._seen.get(r)
+                if last is None or last[0] != c:
+                    self._seen[r] = (c, now)
+                elif now - last[1] > self.timeout:
+                    dead.append(r)
         return dead
+
+    def dead_ranks(self):
+        return self._poll()
 
     def check(self):
         dead = self.dead_ranks()

@@ -80,6 +80,28 @@ def _worker(rank, world, port, out_dir, part):
         errs_ag.append(rel(out, want))
         torch.cuda.synchronize()
         dist.barrier()          # the shard is rewritten next iteration
+    # vocabulary-parallel softmax statistics: exchange + combine kernel against all_gather + PyTorch
+    errs_vp = []
+    for it in range(3 if part == "kernels" else 0):
+        R = 700                                       # three row blocks, the last one partial
+        st = torch.randn(R, 3, device=dev)
+        st[:, 1] = st[:, 1].abs() + 0.1
+        tg = torch.randint(0, 2 * world, (R,), device=dev, dtype=torch.int32)
+        dist.broadcast(tg, 0)
+        st[:, 2] = torch.where(tg % world == rank, st[:, 2], torch.full_like(st[:, 2], float("-inf")))
+        tg = torch.where(tg >= 2 * world - 1, torch.full_like(tg, -1), tg)      # some ignored rows
+        gm, gs, rl = (torch.zeros(R, device=dev) for _ in range(3))
+        f.vp_combine(st, tg, gm, gs, rl)
+        allst = [torch.empty_like(st) for _ in range(world)]
+        dist.all_gather(allst, st)
+        allst = torch.stack(allst)
+        m, sm, xt = allst[..., 0], allst[..., 1], allst[..., 2]
+        wm = m.max(0).values
+        ws = (sm * torch.exp(m - wm)).sum(0)
+        wl = torch.where(tg >= 0, torch.log(ws) + wm - xt.max(0).values, torch.zeros_like(wm))
+        torch.cuda.synchronize()
+        errs_vp.append(max(float((gm - wm).abs().max()), float(((gs - ws) / ws).abs().max()), float((rl - wl).abs().max())))
+    res["errs_vp"] = errs_vp
     torch.cuda.synchronize()
     res["errs"], res["errs_rs"], res["errs_ag"], res["same"], res["word"] = errs, errs_rs, errs_ag, same, ops.error_word()
 
@@ -190,7 +212,9 @@ def test_fused_tp_kernels_two_gpus():
         assert max(r["errs"]) < 1e-2, ("gemm_ar", r["errs"])
         assert max(r["errs_rs"]) < 1e-2, ("gemm_rs", r["errs_rs"])
         assert max(r["errs_ag"]) < 1e-2, ("ag_gemm", r["errs_ag"])
+        assert max(r["errs_vp"]) < 1e-5, ("vp_combine", r["errs_vp"])
         assert all(r["same"])
+        assert r["word"] == 0
 
 
 @needs2

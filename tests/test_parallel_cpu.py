@@ -215,6 +215,65 @@ def test_per_rank_checkpoint_resume_is_bit_exact():
             assert a["losses"][-1] == b["losses"][-1]
 
 
+def _leaving_worker(rank, world, port, steps, out_dir):
+    """PP2: every rank saves its checkpoint after step steps/2; then the last rank leaves (between steps,
+    nothing in flight).  The survivor's next step must end in an exception, not in a blocked send."""
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    from kharon_b200.engine import TrainEngine
+    from kharon_b200.parallel.mesh import Mesh
+    from kharon_b200.utils.watchdog import CollectiveTimeout, Heartbeat, RankFailure
+    mesh = Mesh(1, world, 1, timeout_s=30)
+    hb = Heartbeat(rank, world, interval_s=0.2, timeout_s=2.0)
+    e = TrainEngine(mesh=mesh, heartbeat=hb, **KW)
+    e.p2p_timeout_s = 10.0
+    data = _batches(0, steps, e.tokens_per_step, KW["vocab"])
+    code = 4
+    try:
+        for s in range(steps):
+            e.train_step(*data[s])
+            e.loss() if mesh.c.last else None
+            if e.model.step == steps // 2:
+                e.save(os.path.join(out_dir, "ck"))
+                dist.barrier()                       # both files are complete before anybody leaves
+                if rank == world - 1:
+                    hb.stop()
+                    os._exit(3)
+                time.sleep(3.0)                      # the peer's heartbeat goes stale
+    except (RankFailure, CollectiveTimeout) as ex:
+        open(os.path.join(out_dir, "raised_%d" % rank), "w").write("%s at step %d" % (type(ex).__name__, e.model.step))
+        code = 0
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+    hb.stop()
+    os._exit(code)
+
+
+def test_rank_leaving_after_a_save_is_detected_and_the_job_resumes_bit_exactly():
+    tp, pp, dp, steps = 1, 2, 1, 4
+    with tempfile.TemporaryDirectory() as d:
+        full = _launch(tp, pp, dp, steps, d, "run")
+        ctx = mp.spawn(_leaving_worker, args=(2, _free_port(), steps, d), nprocs=2, join=False)
+        for p in ctx.processes:
+            p.join(120)
+        codes = [p.exitcode for p in ctx.processes]
+        assert codes == [0, 3], codes
+        assert open(os.path.join(d, "raised_0")).read().endswith("at step %d" % (steps // 2))
+        assert os.path.exists(os.path.join(d, "ck.r0")) and os.path.exists(os.path.join(d, "ck.r1"))
+        res = _launch(tp, pp, dp, steps, d, "resume")          # the restarted job continues from the files
+    for a, b in zip(full, res):
+        assert b["step"] == steps
+        assert torch.equal(a["w"], b["w"])
+        if a["losses"][-1] is not None:
+            assert a["losses"][-1] == b["losses"][-1]
+
+
 def _failing_worker(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
     import datetime
@@ -235,6 +294,9 @@ def _failing_worker(rank, world, port, out_dir):
         dead = hb.dead_ranks()
     open(os.path.join(out_dir, "seen_%d" % rank), "w").write(",".join(map(str, dead)))
     hb.stop()
+    if rank == 0:                 # rank 0 hosts the store: it stays until the other survivor has reported too
+        while time.time() < deadline and not os.path.exists(os.path.join(out_dir, "seen_2")):
+            time.sleep(0.1)
     os._exit(0 if dead == [1] else 4)
 
 
