@@ -16,11 +16,13 @@
 //   warp 0      TMA producer (operand tiles -> 128-byte-swizzled shared-memory ring)
 //   warp 1      tcgen05.mma issuer, two TMEM accumulator buffers
 //   warps 2-5   epilogue: TMEM -> bf16 partial tile in 16 KB shared-memory chunks (128 rows x 64
-//               columns, 128-byte swizzled); each chunk goes to the local output with a TMA tensor
-//               store (if this rank reduces the tile) and to every rank that reduces it as ONE linear
-//               16 KB bulk store into that rank's staging, which is laid out (tile, chunk)-major so
-//               that a chunk is contiguous in peer memory; then fence + one red.release.sys on that
-//               rank's arrival counter for (source rank, tile)
+//               columns), each stored with TMA tensor stores to the local output (if this rank
+//               reduces the tile) and into the staging slot of every rank that reduces it; then
+//               fence + one red.release.sys on that rank's arrival counter for (source rank, tile).
+//               (Measured alternatives that lost: 128-column tiles so that a CTA has two tiles to
+//               overlap -- the narrower MMA runs at about half rate; staging laid out chunk by
+//               chunk so that a push is one linear 16 KB bulk store -- 20 % slower than the
+//               tensor store of the same bytes.)
 //   warps 6-9   reducer: for each finished tile, wait (bounded) until every peer's partial has
 //               arrived, add the partials in rank order in fp32, add bias / residual, store.
 //               Runs concurrently with the main loop of the following tiles, so the NVLink
@@ -65,9 +67,8 @@ struct CommParams {
   const bf16* resid; int ldr;  // residual rows aligned with `out`, or null
   int epi;                     // all-gather form only: EPI_NONE / EPI_BIAS / EPI_BIAS_GELU / EPI_DGELU
   bf16* aux; int ldaux;        // EPI_BIAS_GELU: pre-activation out [M, N]; EPI_DGELU: pre-activation in
-  bf16* stage[MAX_TP];         // stage[r]: rank r's staging base for parity 0 (tp slots of whole tiles); parity 1 follows
-  size_t slot_elems;           // tp * src_elems
-  size_t src_elems;            // tiles * 128 * 256: one source rank's partial, stored tile by tile (see the epilogue)
+  bf16* stage[MAX_TP];         // stage[r]: rank r's staging base for parity 0 (tp slots of M*N); parity 1 follows
+  size_t slot_elems;           // tp * M * N
   uint32_t* epoch;             // local: [0] calls completed on this buffer set, [1] CTAs finished; null: host counts
   uint32_t* flags[MAX_TP];     // flags[r]: rank r's arrival counters [tp][num_tiles]
   uint32_t* ready[MAX_TP];     // gather mode: ready[r]: rank r's "shard published" counters [tp]
@@ -82,7 +83,7 @@ struct CommParams {
 };
 
 // out: the local output; st[r]: slot `rank` of rank r's staging (where this rank's partial goes)
-struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap g; };
+struct Maps { CUtensorMap a[MAX_TP]; CUtensorMap b; CUtensorMap out; CUtensorMap st[2][MAX_TP]; CUtensorMap g; };
 
 constexpr int COPY_CHUNK = 32 * 1024, COPY_SLOTS = 4;
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
@@ -452,13 +453,9 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
         epi_bar_sync();
         if (issuer) {
           if (mine) tma_store_2d(&maps.out, sbuf, col, out_row0);
-          // to the peers: the 16 KB staging chunk as it is (swizzled image), into the contiguous block of
-          // (tile, chunk) in the peer's staging slot for this rank -- one linear NVLink write per chunk
           for (int pr = 0; pr < p.tp && p.mode != MODE_LOCAL; pr++) {
             if (pr == p.rank || (owner >= 0 && pr != owner)) continue;
-            bf16* dst = p.stage[pr] + (size_t)par * p.slot_elems + (size_t)p.rank * p.src_elems +
-                        ((size_t)t * (BN / 64) + (c0 >> 6)) * (EPI_CHUNK_BYTES / 2);
-            bulk_store_1d(dst, sbuf, EPI_CHUNK_BYTES);
+            tma_store_2d(&maps.st[par][pr], sbuf, col, tm * BM);
           }
           tma_store_commit();
           if (chunk_no == 0 && pend_t >= 0) {
@@ -522,13 +519,9 @@ gemm_comm_kernel(const __grid_constant__ Maps maps, const CommParams p) {
           for (int i = 0; i < RB; i++) {
             const int row = row0 + i;
             const int out_row = p.mode == MODE_RS ? row - p.rank * rows_per_rank : row;
-            const int r_in = row - tm * BM;
-            // a peer's partial: block (tile, lane's 64-column chunk), row r_in, 16-byte unit swizzled as in shared memory
             const uint4* src = (r == p.rank)
                                    ? reinterpret_cast<const uint4*>(p.out + (size_t)out_row * p.ldo + col)
-                                   : reinterpret_cast<const uint4*>(my_stage + (size_t)r * p.src_elems +
-                                                                    ((size_t)t * (BN / 64) + (lane >> 3)) * (EPI_CHUNK_BYTES / 2) +
-                                                                    (size_t)r_in * 64 + (((lane & 7) ^ (r_in & 7)) << 3));
+                                   : reinterpret_cast<const uint4*>(my_stage + ((size_t)r * p.M + row) * p.N + col);
             v[i] = row < row_end ? __ldcg(src) : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
@@ -596,9 +589,9 @@ int num_sms() {
 // Fused tensor-parallel GEMM.  `a_ptrs`: one pointer (local A) or, when gather != 0, tp pointers
 // to the per-rank row shards [M/tp, K] (or [K, M/tp] when a_mn) mapped into this process.
 // `stage_ptrs`, `flag_ptrs`, `ready_ptrs`: tp entries each, index r = rank r's buffer as seen from
-// this process (own entry = local buffer).  Staging is two parities of tp slots, a slot being
-// ceil(M/128) * ceil(N/256) whole tiles of 128 x 256 bf16; `stage_ptrs` are the parity-0 bases; flags hold
-// tp * ceil(M/128) * ceil(N/256) counters; ready holds tp counters.  The call count of the buffer set
+// this process (own entry = local buffer).  Staging holds tp slots of M*N bf16; flags hold
+// tp * ceil(M/128) * ceil(N/256) counters; ready holds tp counters.  Staging is two parities of
+// tp * M * N bf16 each; `stage_ptrs` are the parity-0 bases.  The call count of the buffer set
 // (identical on all ranks) is either kept by the kernel in the two zero-initialised words at
 // `epoch_ptr` (local device memory) or, when that is 0, passed as the 1-based `call_no`.
 // `epi` / `aux` / `ldaux`: epilogue of the all-gather form (mode 2): 0 none, 1 + bias, 2 + bias then GELU
@@ -651,8 +644,14 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   const CUtensorMap* to = kh_tmap_2d_bf16(out, out_rows, N, ldo, BM, 64);
   if (!to) return -1;
   maps.out = *to;
-  const size_t src_elems = (size_t)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * BM * BN;
-  const size_t slot_elems = (size_t)tp * src_elems;
+  const size_t slot_elems = (size_t)tp * M * N;
+  for (int par = 0; par < 2; par++)
+    for (int r = 0; r < tp; r++) {
+      if (r == rank || mode == MODE_LOCAL) continue;
+      const CUtensorMap* ts = kh_tmap_2d_bf16((const bf16*)stage_ptrs[r] + par * slot_elems + (size_t)rank * M * N, M, N, N, BM, 64);
+      if (!ts) return -1;
+      maps.st[par][r] = *ts;
+    }
   CommParams p = {};
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.tp = tp; p.rank = rank; p.gather = gather;
   p.out = (bf16*)out; p.ldo = ldo; p.bias = (const bf16*)bias; p.resid = (const bf16*)resid; p.ldr = ldr;
@@ -672,7 +671,6 @@ extern "C" int kh_gemm_comm(const unsigned long long* a_ptrs, int lda, int a_mn,
   p.n_copy = n_copy;
   p.call_no = call_no;
   p.slot_elems = slot_elems;
-  p.src_elems = src_elems;
   p.epoch = (uint32_t*)epoch_ptr;
   p.ready_target = gather_no;
   p.wait_ns = kh_peer_wait_limit_ns();

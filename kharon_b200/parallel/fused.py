@@ -107,7 +107,7 @@ class _Ctx:
         self.M, self.N, self.tp, self.rank = M, N, tp, rank
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         # the all-gather form (mode 2) reduces nothing: no partial-tile staging
-        self.slot_bytes = tp * tiles * 128 * 256 * 2 if mode != 2 else 0      # whole tiles per source rank
+        self.slot_bytes = tp * M * N * 2 if mode != 2 else 0
         self.flag_bytes = tp * tiles * 4 * 4          # one counter per (source rank, tile, 64-column chunk)
         total = 2 * self.slot_bytes + self.flag_bytes + 256
         self.buf, self.h = _symm_alloc(total, device, group)
