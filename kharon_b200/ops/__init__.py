@@ -190,6 +190,26 @@ SKINNY_MAX_ROWS = 64          # what the kernel accepts
 SKINNY_BEST_ROWS = 16         # above this the 128-row tile kernel is faster (measured on B200)
 
 
+def decode_layers_ok(G, d, H, hd, max_ctx):
+    """Whether the persistent decode kernel (all layers of a step in one launch) takes this shape."""
+    return bool(torch.cuda.is_available() and _lib().kh_decode_layers_ok(G, d, H, hd, max_ctx))
+
+
+def decode_layers(x, xmid, qkv, att, act, layers, n_layer, H, hd, kc, vc, pos, slot, btab, bs, max_ctx, bar, *,
+                  head_w=None, lnf_w=None, lnf_b=None, logits=None, vocab=0, rows=None, n_rows=0):
+    """All transformer layers of one decode step (one new token per sequence) in one persistent kernel:
+    ``x [G, d]`` holds the embedded tokens on entry and the last layer's output on return; k and v of the
+    new tokens are appended to the paged cache ``kc``, ``vc`` ``[L, blocks, bs, H, hd]``.  ``layers`` is the
+    int64 device table of twelve bf16 pointers per layer, ``bar`` four zeroed int32 words.  With ``head_w``
+    the kernel also writes ``logits[i, :vocab] = LayerNorm_f(x[rows[i]]) @ head_w^T`` for ``i < n_rows``."""
+    G, d = x.shape
+    _call(_lib().kh_decode_layers, 1, x.data_ptr(), xmid.data_ptr(), qkv.data_ptr(), att.data_ptr(), act.data_ptr(),
+          layers.data_ptr(), n_layer, G, d, H, hd, kc.data_ptr(), vc.data_ptr(), kc.stride(0), pos.data_ptr(),
+          slot.data_ptr(), btab.data_ptr(), btab.shape[1], bs, max_ctx, 1.0 / float(hd) ** 0.5,
+          _p(head_w), _p(lnf_w), _p(lnf_b), _p(logits), logits.stride(0) if logits is not None else 0, vocab,
+          _p(rows), n_rows, bar.data_ptr(), _stream())
+
+
 def gemm_skinny_scratch_elems(M, N, K):
     return int(_lib().kh_gemm_skinny_scratch_elems(M, N, K)) if torch.cuda.is_available() else 0
 

@@ -58,6 +58,9 @@ _OPTIONAL = {
     "kh_p2p_put": (i32, vp, vp, C.c_longlong, vp, vp, vp),
     "kh_p2p_wait": (i32, vp, vp, u32, vp),
     "kh_append_kv": (i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp),
+    "kh_decode_layers_ok": (i32, i32, i32, i32, i32, i32),
+    "kh_decode_layers": (i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, long_, vp, vp, vp, i32, i32, i32, f32,
+                         vp, vp, vp, vp, i32, i32, vp, i32, vp, vp),
     "kh_paged_attn": (i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, i32, vp),
     "kh_gather_rows": (i32, vp, vp, vp, i32, i32, vp),
     "kh_copy_blocks": (i32, vp, vp, vp, i32, i32, long_, long_, vp),
