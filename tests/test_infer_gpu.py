@@ -108,9 +108,13 @@ def test_persistent_decode_kernel_matches_the_kernel_chain(d, heads, groups):
             toks, _, _ = e.generate(prompts, 2)          # prefill, then one decode step
             torch.cuda.synchronize()
             out[name] = (toks, e.logits[:G, :600].float().clone())
-        assert out["chain"][0] == out["fused"][0]
-        err = ((out["chain"][1] - out["fused"][1]).norm() / out["chain"][1].norm()).item()
+        lc, lf = out["chain"][1], out["fused"][1]
+        err = ((lc - lf).norm() / lc.norm()).item()
         assert err < 3e-2, (G, err)
+        # the sampled token may differ only where the chain's own top two logits are closer than that error
+        picked = torch.tensor([t[-1] for t in out["fused"][0]], device=lc.device)
+        gap = lc.max(-1).values - lc.gather(1, picked[:, None])[:, 0]
+        assert float(gap.max()) <= 3e-2 * float(lc.abs().max()), (G, gap.max().item())
         chain = InferEngine(m, block_size=8, max_seqs=G + 1, persistent_decode=False)
         fused = InferEngine(m, block_size=8, max_seqs=G + 1, persistent_decode=True)
         fused.persistent_max = 32
