@@ -372,3 +372,12 @@ def smoke_decode():
     ops.check_device_status()
     print("smoke: paged decode 4 x 12 tokens, %d blocks peak, %d prefix blocks shared" % (st["blocks_peak"],
                                                                                       st["prefix_blocks_saved"]))
+    # a width the persistent decode kernel takes (all layers and the head of a step in one launch)
+    cfg = Config(2, 512, 8, 512, 128, 1)
+    m = GPT(cfg, "cuda:0", torch.bfloat16)
+    m.init_weights(1234)
+    eng = InferEngine(m, block_size=16, max_seqs=5)
+    outs, st, ms = eng.generate_group(prompt, 4, 12)
+    assert eng.persistent and all(len(o) == 32 for o in outs) and all(o == outs[0] for o in outs)
+    ops.check_device_status()
+    print("smoke: persistent decode kernel, 4 x 12 tokens")
