@@ -116,6 +116,7 @@ def run_ours():
     L, d, H, V = arg("layers", 24), arg("d", 2048), arg("heads", 16), arg("vocab", 50257)
     S, mb, M = arg("seq", 512), arg("mbatch", 4), arg("M", 8)
     fuse = "--no-fuse" not in sys.argv
+    pp_fuse = arg("pp-fuse", 2 if fuse else 1)          # pipeline meshes: micro-batches that travel through the stages together
     fused_comm = "--no-fused-comm" not in sys.argv     # in-kernel NVLink collectives (product path) vs NCCL baseline
     mesh = Mesh(tp, pp, dp) if world > 1 else Mesh.single()
     extras = "--no-extras" not in sys.argv
@@ -127,8 +128,9 @@ def run_ours():
         gc.collect()
     eng = TrainEngine(L, d, H, V, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                       init=arg("init", "device", str), fused_comm=fused_comm, pp_split=arg("pp-split", "auto", str),
-                      sp="--sp" in sys.argv)
+                      sp="--sp" in sys.argv, pp_fuse=pp_fuse)
     seq_par = bool(eng.sp)
+    pp_fused = int(eng.pp_fuse)
     ntok = M * mb * S                                    # per replica and step
     data = Rng(42 + mesh.c.dp_rank)
     pin = device.type == "cuda"
@@ -205,7 +207,7 @@ def run_ours():
             Kr = min(K, 10)
             e2 = TrainEngine(L, d, H, 256, S, mb, M, mesh=mesh, device=device, lr=3e-4, wd=0.1, fuse_microbatches=fuse,
                              init=arg("init", "device", str), fused_comm=fused_comm, untied_head=True,
-                             pp_split=arg("pp-split", "auto", str), sp="--sp" in sys.argv)
+                             pp_split=arg("pp-split", "auto", str), sp="--sp" in sys.argv, pp_fuse=pp_fuse)
             data.batch_into(host_idx[0], host_tgt[0], 256)
             dev_idx.copy_(host_idx[0]); dev_tgt.copy_(host_tgt[0])
             for _ in range(W):
@@ -249,7 +251,8 @@ def run_ours():
             "mfu_peak_tflops_per_gpu": round(peak / 1e12, 1),
             "config": {"model": "GPT L%d d%d H%d V%d tied" % (L, d, H, V), "global_batch": mb * M * dp, "seq_len": S,
                        "micro_batch": mb, "micro_batches": M, "parallelism": "tp%d pp%d dp%d(zero1)" % (tp, pp, dp),
-                       "microbatches_fused_on_single_stage": fused_mb, "fused_comm": fused_comm,
+                       "microbatches_fused_on_single_stage": fused_mb, "microbatches_per_pipeline_turn": pp_fused,
+                       "fused_comm": fused_comm,
                        "sequence_parallel": seq_par, "layers_per_stage": stage_layers,
                        "l2": "inputs larger than L2 (step working set > 20 GB)", "loss_last_step": round(final_loss, 4)},
             "clocks": clocks,

@@ -87,7 +87,7 @@ class TrainEngine:
     def __init__(self, layers, d_model, heads, vocab, seq, mbatch, n_micro, mesh: Mesh | None = None, device="cuda",
                  dtype=torch.bfloat16, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, untied_head=False,
                  fuse_microbatches=False, seed=1337, init="host", fused_comm=False, trace=False, heartbeat=None, pp_split=None, vocab_parallel=True,
-                 defer_dw=None, eager_p2p=None, bucket_optimizer=True, sp=None):
+                 defer_dw=None, eager_p2p=None, bucket_optimizer=True, sp=None, pp_fuse=1):
         from .utils.trace import Tracer
         self.mesh = mesh or Mesh.single()
         # The in-kernel collectives move bf16 activations / weights; an fp32 model (the oracle
@@ -104,6 +104,14 @@ class TrainEngine:
         self.fused_mb = bool(fuse_microbatches and c.pp == 1)
         if self.fused_mb:            # one pass over M x mbatch sequences: identical math, larger GEMMs
             mbatch, n_micro = mbatch * n_micro, 1
+        # Pipeline meshes: ``pp_fuse`` consecutive micro-batches travel through the stages as one (identical
+        # math: the loss is a mean over tokens and gradients add).  Halving the number of micro-batches grows
+        # the 1F1B bubble from (P-1)/(M+P-1) to (P-1)/(M/2+P-1), but every kernel and every fused collective
+        # of a stage runs on twice the rows; the deferred weight-gradient pass fills the larger bubble.
+        self.pp_fuse = 1
+        if c.pp > 1 and pp_fuse and pp_fuse > 1 and n_micro % pp_fuse == 0 and n_micro // pp_fuse >= c.pp:
+            self.pp_fuse = int(pp_fuse)
+            mbatch, n_micro = mbatch * self.pp_fuse, n_micro // self.pp_fuse
         self.M, self.mbatch, self.seq = n_micro, mbatch, seq
         self.opt = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=wd)
         nl = self.stage_layers[c.stage]

@@ -75,6 +75,7 @@ def main(argv=None):
     jsonl = f.str("jsonl", "", "append one JSON object per logged step to this file")
     hb_s = f.float("heartbeat", 0.0, "seconds after which a silent rank counts as dead (0 = off)")
     pp_split = f.str("pp-split", "even", "layers per stage: even | auto | a,b,... (auto balances the head's cost)")
+    pp_fuse = f.int("pp-fuse", 1, "micro-batches that travel through the pipeline stages together (identical math)")
     f.maybe_help()
     rank, world, device = init_distributed(dev_flag or None)
     mesh = Mesh(tp, None, dp) if world > 1 else Mesh.single()
@@ -87,7 +88,7 @@ def main(argv=None):
     mlog = JsonlLogger(jsonl if rank == world - 1 else "")
     eng = TrainEngine(L, d, H, vocab, seq, mb, M, mesh=mesh, device=device,
                       dtype=torch.bfloat16 if device.type == "cuda" else torch.float32, lr=lr, untied_head=untied,
-                      fused_comm=fused, trace=trace, heartbeat=hb, pp_split=pp_split, sp=use_sp)
+                      fused_comm=fused, trace=trace, heartbeat=hb, pp_split=pp_split, sp=use_sp, pp_fuse=pp_fuse)
     if synthetic or not os.path.exists(data_path):
         data = SyntheticData(vocab, M * mb, seq, 42)
     else:
@@ -125,7 +126,7 @@ def main(argv=None):
     def one_micro():
         x = eng.recv_act[0] if not c.first else None
         m.forward(slot=0, x_in=x, compute_loss=False)
-        m.backward(slot=0, dx_out=None if c.last else eng.recv_grad[0], inv_mb=1.0 / M, loss_scale=None)
+        m.backward(slot=0, dx_out=None if c.last else eng.recv_grad[0], inv_mb=1.0 / eng.M, loss_scale=None)
 
     if c.pp > 1:
         for b in eng.recv_act + eng.recv_grad:
@@ -137,7 +138,8 @@ def main(argv=None):
     m.tp_allreduce, m.fused_tp = saved_ar, saved_fused
     m.zero_grads()
     t_dp = _timed(eng.optimizer_step, 5, device, world) if c.dp > 1 else 0.0
-    ideal = M * t_micro
+    Mt = eng.M                      # pipeline turns per step (M / pp_fuse)
+    ideal = Mt * t_micro
     P = c.pp
     tokens_replica = M * mb * seq
     full = t_step
@@ -150,11 +152,11 @@ def main(argv=None):
         pass
     flops_gpu = 6.0 * Np * tokens_replica / (tp * P)
     if rank == 0:
-        print("bubble %.1f%% (theory %.1f%%)" % (100 * max(0.0, 1 - ideal / t_step), 100 * (P - 1) / (M + P - 1)))
+        print("bubble %.1f%% (theory %.1f%%)" % (100 * max(0.0, 1 - ideal / t_step), 100 * (P - 1) / (Mt + P - 1)))
         print("tok/s per replica %.0f   mesh %.0f" % (tokens_replica / full * 1e3, dp * tokens_replica / full * 1e3))
         print("params(matmul) %.1fM  MFU %.1f%% of %.0f TFLOP/s per GPU" % (Np / 1e6, 100 * flops_gpu / (full / 1e3) / peak, peak / 1e12))
         print("step %.1f ms = compute %.1f + TP %.1f + PP %.1f ; optimizer+DP comm %.1f (inside the step)" %
-              (t_step, M * t_comp, M * (t_micro - t_comp), max(0.0, t_step - ideal - t_dp), t_dp))
+              (t_step, Mt * t_comp, Mt * (t_micro - t_comp), max(0.0, t_step - ideal - t_dp), t_dp))
         rep = eng.memory_report()
         print("memory %.2f GB/rank  optimizer state %.0f MB/rank" % (rep.get("cuda_allocated_gb", 0.0), rep["optimizer_state_mb"]))
     if world > 1:

@@ -62,6 +62,8 @@ def _worker(rank, world, port, tp, pp, dp, steps, out_dir, mode):
         extra = dict(defer_dw=True, eager_p2p=False)
     elif mode == "not_deferred":
         extra = dict(defer_dw=False)
+    elif mode == "pp_fuse":             # pairs of micro-batches travel through the pipeline as one
+        extra = dict(pp_fuse=2)
     elif mode == "sp":                  # sequence-parallel layers (collective-based evaluation of the fused operators)
         extra = dict(sp=True)
     elif mode == "sp_not_deferred":
@@ -164,7 +166,7 @@ def test_sequence_parallel_matches_single_process(tp, pp, mode):
             assert torch.allclose(_view(r, "wpe"), P["wpe"], rtol=1e-4, atol=2e-5)
 
 
-@pytest.mark.parametrize("mode", ["classic_deferred", "not_deferred"])
+@pytest.mark.parametrize("mode", ["classic_deferred", "not_deferred", "pp_fuse"])
 def test_pipeline_variants_match_single_process(mode):
     """The default pipeline path defers the weight gradients and sends without waiting; the 1F1B
     order with a final weight-gradient pass and the per-micro-batch form give the same training."""
