@@ -122,8 +122,9 @@ __device__ __forceinline__ bool grid_barrier(const DecodeParams& p, uint32_t bas
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = sh->abort_flag ? 0 : 1;
-    __threadfence();
-    atomicAdd(p.bar, 1u);
+    // arrive: a release reduction (no value comes back, so nothing waits for the atomic's round trip); it orders
+    // the CTA's earlier writes, which the barrier above made visible to this thread, before the increment
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.bar), "r"(1u) : "memory");
     const uint32_t target = base + (uint32_t)k * gridDim.x;
     uint64_t t0 = 0;
     for (uint32_t it = 0; ok && (int32_t)(ld_acquire_gpu(p.bar) - target) < 0; ++it) {
