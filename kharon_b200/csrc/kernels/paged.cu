@@ -172,6 +172,155 @@ extern "C" int kh_paged_attn(const void* qkv, int ld, void* kc, void* vc, void* 
   return 0;
 }
 
+// ------------------------------------------------------------------------------- split-KV attention
+// Long contexts: the keys of a token are cut into `n_split` equal ranges, one CTA per (token, head,
+// range) computes the softmax-weighted value sum over its range and its log-sum-exp, and a merge
+// kernel combines the ranges (weights exp(lse_s - max lse)).  More CTAs per token than heads when a
+// decode step has few sequences, and a score buffer of one range instead of the whole context.
+// The range that holds position `pos` appends the token's k, v first (decode steps).
+template <int HD>
+__global__ void __launch_bounds__(128)
+paged_attn_split_k(const bf16* __restrict__ qkv, int ld, bf16* __restrict__ kc, bf16* __restrict__ vc,
+                   float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ pos,
+                   const int* __restrict__ slot, const int* __restrict__ btab, int max_lb, int bs, int H, float scale,
+                   int max_ctx, int chunk, int append, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y, sp = blockIdx.z, n_split = gridDim.z, tid = threadIdx.x;
+  float* op = o_part + (((size_t)t * H + h) * n_split + sp) * HD;
+  float* lp = lse_part + ((size_t)t * H + h) * n_split + sp;
+  if (pos[t] < 0 || pos[t] >= max_ctx || pos[t] / bs >= max_lb || slot[t] < 0) {
+    if (tid == 0) { atomicCAS(err, 0, 8); *lp = -INFINITY; }
+    for (int e = tid; e < HD; e += 128) op[e] = 0.f;
+    return;
+  }
+  extern __shared__ float sm[];
+  constexpr int TPR = HD / 8, GROUPS = 128 / TPR;
+  float* s_q = sm;
+  float* s_p = sm + HD;              // `chunk` scores
+  float* s_red = s_p + chunk;
+  const int d = H * HD;
+  const int ctx = pos[t] + 1;
+  const int j0 = sp * chunk, j1 = min(ctx, j0 + chunk);
+  const int* bt = btab + (size_t)slot[t] * max_lb;
+  if (append && tid < 2 * TPR && ctx - 1 >= j0 && ctx - 1 < j1) {
+    const int p = ctx - 1, which = tid / TPR, c = (tid % TPR) * 8;
+    const size_t dst = ((size_t)bt[p / bs] * bs + (p % bs)) * d + h * HD + c;
+    *reinterpret_cast<uint4*>((which ? vc : kc) + dst) =
+        *reinterpret_cast<const uint4*>(qkv + (size_t)t * ld + (which + 1) * d + h * HD + c);
+  }
+  if (j1 <= j0) {                    // no keys in this range
+    if (tid == 0) *lp = -INFINITY;
+    for (int e = tid; e < HD; e += 128) op[e] = 0.f;
+    return;
+  }
+  for (int e = tid; e < HD; e += 128) s_q[e] = __bfloat162float(qkv[(size_t)t * ld + h * HD + e]) * scale;
+  __syncthreads();
+  float lmax = -INFINITY;
+  for (int j = j0 + tid; j < j1; j += 128) {
+    const bf16* kp = kc + ((size_t)bt[j / bs] * bs + (j % bs)) * d + h * HD;
+    float acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < HD; c += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(kp + c);
+      const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), e = unpack_bf16(v.w);
+      acc += a.x * s_q[c] + a.y * s_q[c + 1] + b.x * s_q[c + 2] + b.y * s_q[c + 3] + cc.x * s_q[c + 4] +
+             cc.y * s_q[c + 5] + e.x * s_q[c + 6] + e.y * s_q[c + 7];
+    }
+    s_p[j - j0] = acc;
+    lmax = fmaxf(lmax, acc);
+  }
+  s_red[tid] = lmax;
+  __syncthreads();
+  for (int o = 64; o > 0; o >>= 1) {
+    if (tid < o) s_red[tid] = fmaxf(s_red[tid], s_red[tid + o]);
+    __syncthreads();
+  }
+  const float gmax = s_red[0];
+  __syncthreads();
+  float lsum = 0.f;
+  for (int j = j0 + tid; j < j1; j += 128) {
+    const float e = __expf(s_p[j - j0] - gmax);
+    s_p[j - j0] = e;
+    lsum += e;
+  }
+  s_red[tid] = lsum;
+  __syncthreads();
+  for (int o = 64; o > 0; o >>= 1) {
+    if (tid < o) s_red[tid] += s_red[tid + o];
+    __syncthreads();
+  }
+  const float tot = s_red[0];
+  __syncthreads();
+  const int c8 = (tid % TPR) * 8, grp = tid / TPR;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) acc[k] = 0.f;
+  for (int j = j0 + grp; j < j1; j += GROUPS) {
+    const uint4 v = *reinterpret_cast<const uint4*>(vc + ((size_t)bt[j / bs] * bs + (j % bs)) * d + h * HD + c8);
+    const float pj = s_p[j - j0];
+    const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), e = unpack_bf16(v.w);
+    acc[0] += pj * a.x; acc[1] += pj * a.y; acc[2] += pj * b.x; acc[3] += pj * b.y;
+    acc[4] += pj * cc.x; acc[5] += pj * cc.y; acc[6] += pj * e.x; acc[7] += pj * e.y;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; k++) s_red[grp * HD + c8 + k] = acc[k];
+  __syncthreads();
+  if (tid < HD) {
+    float o = 0.f;
+    for (int g = 0; g < GROUPS; g++) o += s_red[g * HD + tid];
+    op[tid] = o / tot;
+  }
+  if (tid == 0) *lp = gmax + logf(tot);
+}
+// out[t, h, :] = sum_s w_s o_part[t, h, s, :] / sum_s w_s with w_s = exp(lse_s - max_s lse_s), ranges in index order
+__global__ void paged_attn_merge_k(const float* __restrict__ o_part, const float* __restrict__ lse_part, bf16* __restrict__ out,
+                                   int H, int HD, int n_split) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y, e = threadIdx.x;
+  const float* lp = lse_part + ((size_t)t * H + h) * n_split;
+  float m = -INFINITY;
+  for (int s = 0; s < n_split; s++) m = fmaxf(m, lp[s]);
+  float num = 0.f, den = 0.f;
+  if (m > -INFINITY)
+    for (int s = 0; s < n_split; s++) {
+      const float w = lp[s] == -INFINITY ? 0.f : __expf(lp[s] - m);
+      num += w * o_part[(((size_t)t * H + h) * n_split + s) * HD + e];
+      den += w;
+    }
+  out[((size_t)t * H + h) * HD + e] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+}
+// `o_part`: ntok * H * n_split * hd floats, `lse_part`: ntok * H * n_split floats (scratch).
+extern "C" int kh_paged_attn_split(const void* qkv, int ld, void* kc, void* vc, void* out, void* o_part, void* lse_part,
+                                   const void* pos, const void* slot, const void* btab, int max_lb, int bs, int H, int hd,
+                                   float scale, int ntok, int max_ctx, int n_split, int append, void* stream) {
+  if (n_split < 1 || n_split > 64) { kh_set_error("paged_attn_split: n_split %d out of range", n_split); return -1; }
+  const int chunk = (max_ctx + n_split - 1) / n_split;
+  const size_t smem = (size_t)(hd + chunk + 1024 + 8) * sizeof(float);
+  if (smem > 200 * 1024) { kh_set_error("paged_attn_split: a range of %d positions does not fit in shared memory", chunk); return -1; }
+  dim3 grid(ntok, H, n_split);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(HD)                                                                                                        \
+  {                                                                                                                       \
+    static size_t attr = 48 * 1024;                                                                                       \
+    if (smem > attr) { cudaFuncSetAttribute(paged_attn_split_k<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; } \
+    KH_LAUNCH((paged_attn_split_k<HD>), grid, 128, smem, st, (const bf16*)qkv, ld, (bf16*)kc, (bf16*)vc, (float*)o_part,  \
+              (float*)lse_part, (const int*)pos, (const int*)slot, (const int*)btab, max_lb, bs, H, scale, max_ctx, chunk, \
+              append, kh_error_word_dev());                                                                               \
+  }
+  if (hd == 128) LAUNCH(128)
+  else if (hd == 64) LAUNCH(64)
+  else if (hd == 32) LAUNCH(32)
+  else if (hd == 16) LAUNCH(16)
+  else { kh_set_error("paged_attn_split: head dim %d is not supported", hd); return -1; }
+#undef LAUNCH
+  KH_LAUNCH_CHECK("paged_attn_split");
+  KH_LAUNCH(paged_attn_merge_k, dim3(ntok, H), hd, 0, st, (const float*)o_part, (const float*)lse_part, (bf16*)out, H, hd, n_split);
+  KH_LAUNCH_CHECK("paged_attn_merge");
+  return 0;
+}
+
 // ------------------------------------------------------------------------------- gather / copy
 __global__ void gather_rows_k(const bf16* __restrict__ x, const int* __restrict__ rows, bf16* __restrict__ out, int d) {
   pdl_wait();

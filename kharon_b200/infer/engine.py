@@ -35,7 +35,7 @@ class InferStats(dict):
 
 class InferEngine:
     def __init__(self, model: GPT, block_size=16, n_blocks=None, max_tokens=None, max_seqs=33, use_graphs=True,
-                 persistent_decode=None):
+                 persistent_decode=None, attn_splits=None, flash_prefill=True):
         cfg = model.cfg
         self.model, self.cfg = model, cfg
         self.dev, self.dt = model.device, model.dtype
@@ -100,6 +100,18 @@ class InferEngine:
             self.layer_table = torch.tensor([[model.L(l, n).data_ptr() for n in names] for l in range(L)],
                                             dtype=torch.int64, device=self.dev)
             self.grid_bar = torch.zeros(4, dtype=torch.int32, **z)
+        # Contexts beyond 2048 positions: the keys of a token are cut into ranges with a CTA each (split-KV) and merged
+        self.attn_splits = int(attn_splits) if attn_splits else (1 if cfg.seq <= 2048 else min(16, (cfg.seq + 2047) // 2048))
+        self.attn_scratch = None
+        if self.attn_splits > 1 and self.dev.type == "cuda":
+            self.attn_scratch = torch.zeros(self.max_tokens * self.Hl * self.attn_splits * (self.hd + 1), dtype=torch.float32, **z)
+        # Steps made of whole fresh prompts (every listed token belongs to a sequence that starts at position 0 in this
+        # step) run their attention on the tensor cores with the training forward kernel, one launch per prompt;
+        # everything else (decode steps, chunked prompts, mixed steps) goes through the paged kernel.
+        self.flash_prefill = bool(flash_prefill and self.dev.type == "cuda" and self.dt == torch.bfloat16
+                                  and self.hd in (64, 128))
+        self.lse_buf = torch.zeros(self.Hl * self.max_tokens, dtype=torch.float32, **z) if self.flash_prefill else None
+        self._fresh = None
         self.temperature, self.seed, self.step_no = 0.0, 0, 0
         # under TP the captured step contains the fused GEMM + all-reduce kernels (their call counter
         # is a device word); the NCCL seam is left to eager launches
@@ -146,14 +158,18 @@ class InferEngine:
                               vocab=cfg.vocab, rows=self.d_rows, n_rows=nseq)
             ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq)
             return
-        for l in range(0 if fused_layers else cfg.n_layer):
+        for l in range(cfg.n_layer):
             ln, qkv, att, xmid = self.ln[:ntok], self.qkv[:ntok], self.att[:ntok], self.xmid[:ntok]
             self._ln_lin(xs, m.L(l, "ln1_w"), m.L(l, "ln1_b"), ln, m.L(l, "qkv_w"), qkv, ops.EPI_BIAS, m.L(l, "qkv_b"))
             decode = ntok == nseq        # one new token per sequence: the attention kernel appends k, v itself
             if not decode:
                 ops.append_kv(qkv, self.kc[l], self.vc[l], pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok)
-            ops.paged_attn(qkv, self.kc[l], self.vc[l], att, pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok,
-                           cfg.seq, append=decode)
+            if not decode and self._fresh:
+                for r0, T in self._fresh:
+                    ops.flash_fwd(qkv[r0:r0 + T], att[r0:r0 + T], self.lse_buf, 1, T, self.Hl, self.hd)
+            else:
+                ops.paged_attn(qkv, self.kc[l], self.vc[l], att, pos, slot, self.d_btab, self.bs, self.Hl, self.hd, ntok,
+                               cfg.seq, append=decode, n_split=self.attn_splits, scratch=self.attn_scratch)
             # row-parallel products: one GEMM, or under TP the fused GEMM + all-reduce kernel / NCCL seam
             self._row(att, m.L(l, "proj_w"), xmid, m.L(l, "proj_b"), xs)
             self._ln_lin(xmid, m.L(l, "ln2_w"), m.L(l, "ln2_b"), ln, m.L(l, "fc_w"), self.act[:ntok], ops.EPI_BIAS_GELU,
@@ -190,8 +206,24 @@ class InferEngine:
         else:
             self.model._row_parallel(x, w, out, bias, resid)
 
+    def _fresh_prompts(self, ntok, nseq):
+        """[(first row, length)] when every token of the step belongs to a prompt that starts at position 0 and is
+        listed whole and contiguously; None otherwise (read from the host copy of the step's metadata)."""
+        if not self.flash_prefill or ntok == nseq:
+            return None
+        pos = self.h_meta[self._o_pos:self._o_pos + ntok]
+        slot = self.h_meta[self._o_slot:self._o_slot + ntok]
+        cuts = [0] + (torch.nonzero(slot[1:] != slot[:-1]).flatten() + 1).tolist() + [ntok]
+        out = []
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            if int(pos[a]) != 0 or int(pos[b - 1]) != b - a - 1 or b - a < 64:     # (short prompts: not worth a launch each)
+                return None
+            out.append((a, b - a))
+        return out if len(out) == nseq else None
+
     def _run(self, ntok, nseq, rep=1):
         """Metadata is already in ``h_meta``; runs one step and returns the sampled ids (host)."""
+        self._fresh = self._fresh_prompts(ntok, nseq)
         self.d_meta.copy_(self.h_meta, non_blocking=True)
         key = (ntok, nseq, rep)
         greedy = self.temperature <= 0

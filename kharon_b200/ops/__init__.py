@@ -512,15 +512,24 @@ def append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok):
                              slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd, ntok, _stream())
 
 
-def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx, append=False):
+def paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx, append=False, n_split=1, scratch=None):
     """Causal attention of each listed token over positions 0..pos of its own sequence, K/V read
     through the block table.  ``append``: the kernel itself stores each token's k, v into the cache
     first (valid when no two listed tokens belong to one sequence, i.e. decode steps); otherwise
-    ``append_kv`` must have run."""
+    ``append_kv`` must have run.  ``n_split`` > 1 (long contexts): the keys are cut into that many equal
+    ranges of ``max_ctx``, each handled by its own CTA, and merged by their log-sum-exps; ``scratch`` is a
+    float32 buffer of at least ``ntok * H * n_split * (hd + 1)`` elements."""
     if _use_reference(qkv):
         if append:
             ref.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
         return ref.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok)
+    if n_split > 1:
+        n_o = ntok * H * n_split * hd
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= n_o + ntok * H * n_split
+        _call(_lib().kh_paged_attn_split, 1, qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+              scratch.data_ptr(), scratch.data_ptr() + 4 * n_o, pos.data_ptr(), slot.data_ptr(), btab.data_ptr(),
+              btab.stride(0), bs, H, hd, 1.0 / math.sqrt(hd), ntok, max_ctx, n_split, int(append), _stream())
+        return
     _call(_lib().kh_paged_attn, 1, qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
                               pos.data_ptr(), slot.data_ptr(), btab.data_ptr(), btab.stride(0), bs, H, hd,
                               1.0 / math.sqrt(hd), ntok, max_ctx, int(append), _stream())

@@ -61,6 +61,7 @@ _OPTIONAL = {
     "kh_decode_layers_ok": (i32, i32, i32, i32, i32, i32),
     "kh_decode_layers": (i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, long_, vp, vp, vp, i32, i32, i32, f32,
                          vp, vp, vp, vp, i32, i32, vp, i32, vp, vp),
+    "kh_paged_attn_split": (i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, i32, i32, vp),
     "kh_paged_attn": (i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, i32, vp),
     "kh_gather_rows": (i32, vp, vp, vp, i32, i32, vp),
     "kh_copy_blocks": (i32, vp, vp, vp, i32, i32, long_, long_, vp),

@@ -42,6 +42,76 @@ def test_paged_kernels(hd, H):
         assert err < 1e-2, err
 
 
+@pytest.mark.parametrize("hd,H,n_split", [(64, 4, 3), (128, 2, 8)])
+def test_split_kv_attention_matches_the_single_range_kernel(hd, H, n_split):
+    """Keys cut into ranges with a CTA each and merged by log-sum-exp: same result as one CTA per (token, head),
+    for prefill tokens and for a decode step that appends its own k, v; ranges beyond a short context are empty."""
+    torch.manual_seed(2)
+    d, bs, nb, nseq, max_lb, max_ctx = H * hd, 8, 120, 3, 36, 288
+    kc = torch.zeros(nb, bs, H, hd, device="cuda", dtype=torch.bfloat16); vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    btab = torch.randperm(nb, device="cuda")[:nseq * max_lb].int().view(nseq, max_lb)
+    lens = [201, 40, 5]
+    for phase in range(2):
+        tok_pos, tok_slot = [], []
+        for s_, n in enumerate(lens):
+            rng = range(n) if phase == 0 else [n]
+            tok_pos += list(rng); tok_slot += [s_] * len(rng)
+        ntok = len(tok_pos)
+        pos = torch.tensor(tok_pos, device="cuda", dtype=torch.int32)
+        slot = torch.tensor(tok_slot, device="cuda", dtype=torch.int32)
+        qkv = torch.randn(ntok, 3 * d, device="cuda").bfloat16()
+        out = torch.empty(ntok, d, device="cuda", dtype=torch.bfloat16); out2 = torch.empty_like(out)
+        scratch = torch.zeros(ntok * H * n_split * (hd + 1), device="cuda")
+        if phase == 0:
+            ops.append_kv(qkv, kc, vc, pos, slot, btab, bs, H, hd, ntok)
+            ops.append_kv(qkv, kc2, vc2, pos, slot, btab, bs, H, hd, ntok)
+        ops.paged_attn(qkv, kc, vc, out, pos, slot, btab, bs, H, hd, ntok, max_ctx, append=phase == 1, n_split=n_split,
+                       scratch=scratch)
+        ops.paged_attn(qkv, kc2, vc2, out2, pos, slot, btab, bs, H, hd, ntok, max_ctx, append=phase == 1)
+        torch.cuda.synchronize()
+        assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+        err = ((out.float() - out2.float()).norm() / out2.float().norm()).item()
+        assert err < 5e-3, (phase, err)
+    assert ops.error_word() == 0
+
+
+def test_split_kv_engine_generates_the_same_tokens():
+    cfg = Config(2, 128, 2, 300, 96, 1)
+    gpu = GPT(cfg, "cuda", torch.bfloat16); gpu.init_weights(1234); gpu.params.w.mul_(6.0); gpu.sync_bf16()
+    prompts = [[5, 17, 3, 9], [9, 1, 44, 23, 8, 61, 2], [70, 1]]
+    a, _, _ = InferEngine(gpu, block_size=8, max_seqs=5).generate(prompts, 12)
+    e = InferEngine(gpu, block_size=8, max_seqs=5, attn_splits=4)
+    assert e.attn_splits == 4
+    b, _, _ = e.generate(prompts, 12)
+    agree = sum(x == y for s_, t in zip(a, b) for x, y in zip(s_, t)) / sum(len(s_) for s_ in a)
+    assert agree > 0.9, agree
+    assert ops.error_word() == 0
+
+
+def test_tensor_core_prefill_of_fresh_prompts_matches_the_paged_kernel():
+    """Whole fresh prompts take the training attention kernel (one launch per prompt, ragged lengths); the logits of
+    the prefill step and the generated tokens match the paged kernel's."""
+    cfg = Config(2, 256, 4, 400, 320, 1)
+    m = GPT(cfg, "cuda", torch.bfloat16); m.init_weights(99); m.params.w.mul_(5.0); m.sync_bf16()
+    gen = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 400, (n,), generator=gen).tolist() for n in (64, 131, 200)]
+    out = {}
+    for flag in (False, True):
+        e = InferEngine(m, block_size=8, max_seqs=4, max_tokens=512, flash_prefill=flag)
+        toks, _, _ = e.generate(prompts, 1)            # the prefill step alone
+        torch.cuda.synchronize()
+        assert (e._fresh is not None) == flag
+        out[flag] = (toks, e.logits[:3, :400].float().clone())
+        more, _, _ = e.generate(prompts, 10)
+        out[flag] += (more,)
+    err = ((out[True][1] - out[False][1]).norm() / out[False][1].norm()).item()
+    assert err < 2e-2, err
+    agree = sum(x == y for s_, t in zip(out[True][2], out[False][2]) for x, y in zip(s_, t)) / sum(len(s_) for s_ in out[True][2])
+    assert agree > 0.9, agree
+    assert ops.error_word() == 0
+
+
 def test_sampler_and_gather_and_copy():
     torch.manual_seed(1)
     V, ld, n = 50257, 50304, 5
