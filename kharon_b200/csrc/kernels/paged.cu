@@ -371,9 +371,13 @@ __device__ __forceinline__ uint32_t mix32(uint64_t x) {
 }
 __global__ void __launch_bounds__(256)
 sample_k(const bf16* __restrict__ logits, int ld, int V, float temperature, unsigned long long seed, int step,
-         int rep, int* __restrict__ out) {
+         const int* __restrict__ step_dev, int rep, int* __restrict__ out) {
   pdl_wait();
   pdl_launch_dependents();
+  if (step_dev) {      // step number and seed kept in device memory: a captured launch draws fresh numbers
+    step = step_dev[0];
+    seed = (unsigned long long)(unsigned)step_dev[1] | ((unsigned long long)(unsigned)step_dev[2] << 32);
+  }
   __shared__ float s_v[256];
   __shared__ int s_i[256];
   __shared__ float s_scan[257];
@@ -428,10 +432,17 @@ sample_k(const bf16* __restrict__ logits, int ld, int V, float temperature, unsi
     }
   }
 }
-extern "C" int kh_sample(const void* logits, int ld, int V, float temperature, unsigned long long seed, int step,
-                         int rep, void* out, int nseq, void* stream) {
+// `step_dev` (optional): three device words {step number, seed low, seed high}; when given they replace
+// `step` and `seed`, so that the launch can be replayed from a CUDA graph with new values each time.
+extern "C" int kh_sample2(const void* logits, int ld, int V, float temperature, unsigned long long seed, int step,
+                          const void* step_dev, int rep, void* out, int nseq, void* stream) {
   if (rep < 1 || rep > 256) { kh_set_error("sample: rep must be in [1, 256]"); return -1; }
-  KH_LAUNCH(sample_k, nseq, 256, 0, (cudaStream_t)stream, (const bf16*)logits, ld, V, temperature, seed, step, rep, (int*)out);
+  KH_LAUNCH(sample_k, nseq, 256, 0, (cudaStream_t)stream, (const bf16*)logits, ld, V, temperature, seed, step,
+            (const int*)step_dev, rep, (int*)out);
   KH_LAUNCH_CHECK("sample");
   return 0;
+}
+extern "C" int kh_sample(const void* logits, int ld, int V, float temperature, unsigned long long seed, int step,
+                         int rep, void* out, int nseq, void* stream) {
+  return kh_sample2(logits, ld, V, temperature, seed, step, nullptr, rep, out, nseq, stream);
 }

@@ -60,7 +60,8 @@ class InferEngine:
         self._o_rows = 3 * mt
         self._o_btab = 3 * mt + ms_
         self._o_pairs = self._o_btab + ms_ * self.max_lb
-        self._n_meta = self._o_pairs + 2 * ms_ * 4
+        self._o_step = self._o_pairs + 2 * ms_ * 4          # the step number: sampled steps replayed from a graph read it here
+        self._n_meta = self._o_step + 4                      # {step number, seed low, seed high, unused}
         pin = self.dev.type == "cuda"
         self.h_meta = torch.zeros(self._n_meta, dtype=torch.int32, pin_memory=pin)
         self.h_seq_ids = torch.zeros(ms_, dtype=torch.int32)
@@ -70,6 +71,7 @@ class InferEngine:
         self.d_rows = v(self.d_meta, self._o_rows, ms_)
         self.d_btab = v(self.d_meta, self._o_btab, ms_ * self.max_lb).view(ms_, self.max_lb)
         self.d_pairs = v(self.d_meta, self._o_pairs, 2 * ms_ * 4)
+        self.d_stepno = v(self.d_meta, self._o_step, 3)
         e = lambda *s: torch.empty(*s, dtype=self.dt, **z)
         self.x = [e(mt, d), e(mt, d)]
         self.xmid, self.ln, self.qkv, self.att = e(mt, d), e(mt, d), e(mt, 3 * dl), e(mt, dl)
@@ -135,8 +137,8 @@ class InferEngine:
 
     def set_sampling(self, temperature: float, seed: int):
         """temperature <= 0: greedy.  Otherwise categorical draws seeded by (seed, step, row)."""
-        self.temperature, self.seed = float(temperature), int(seed)
-        self.graphs.clear()          # the temperature is baked into captured steps
+        self.temperature, self.seed = float(temperature), int(seed)       # (captured steps are keyed by the temperature;
+                                                                          #  seed and step number travel in d_meta)
 
     def set_eos(self, eos: int):
         _native.rt().kh_eng_set_eos(self._h, eos)
@@ -156,7 +158,8 @@ class InferEngine:
                               cfg.n_layer, self.Hl, self.hd, self.kc, self.vc, pos, slot, self.d_btab, self.bs, cfg.seq,
                               self.grid_bar, head_w=m.head_weight(), lnf_w=P["lnf_w"], lnf_b=P["lnf_b"], logits=self.logits,
                               vocab=cfg.vocab, rows=self.d_rows, n_rows=nseq)
-            ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq)
+            ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq,
+                       step_dev=self.d_stepno)
             return
         for l in range(cfg.n_layer):
             ln, qkv, att, xmid = self.ln[:ntok], self.qkv[:ntok], self.att[:ntok], self.xmid[:ntok]
@@ -181,7 +184,8 @@ class InferEngine:
         ops.gather_rows(xs, self.d_rows, self.last, nseq)
         self._ln_lin(self.last[:nseq], P["lnf_w"], P["lnf_b"], self.lnf[:nseq], m.head_weight(),
                      self.logits[:nseq, :cfg.vocab])
-        ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq)
+        ops.sample(self.logits, cfg.vocab, self.temperature, self.seed, self.step_no, rep, self.d_out, nseq,
+                       step_dev=self.d_stepno)
 
     def _lin(self, x, w, out, epi=ops.EPI_NONE, bias=None, aux=None):
         """Column-parallel / replicated linear layer: skinny kernel for decode-sized inputs."""
@@ -224,10 +228,14 @@ class InferEngine:
     def _run(self, ntok, nseq, rep=1):
         """Metadata is already in ``h_meta``; runs one step and returns the sampled ids (host)."""
         self._fresh = self._fresh_prompts(ntok, nseq)
+        sd = self.seed & 0xFFFFFFFFFFFFFFFF
+        to_i32 = lambda u: u - (1 << 32) if u >= (1 << 31) else u
+        self.h_meta[self._o_step] = self.step_no & 0x7FFFFFFF
+        self.h_meta[self._o_step + 1] = to_i32(sd & 0xFFFFFFFF)
+        self.h_meta[self._o_step + 2] = to_i32(sd >> 32)
         self.d_meta.copy_(self.h_meta, non_blocking=True)
-        key = (ntok, nseq, rep)
-        greedy = self.temperature <= 0
-        if self.use_graphs and greedy and ntok == nseq:
+        key = (ntok, nseq, rep, self.temperature)
+        if self.use_graphs and ntok == nseq:           # greedy and sampled steps alike: the step number lives in d_meta
             g = self.graphs.get(key)
             if g is None and key in self._warm:
                 torch.cuda.synchronize()

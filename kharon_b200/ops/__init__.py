@@ -556,9 +556,11 @@ def copy_blocks(kc, vc, pairs, npairs):
                                kc[0, 0].numel(), kc[0].numel(), _stream())
 
 
-def sample(logits, V, temperature, seed, step, rep, out, nseq):
-    """Greedy argmax (temperature <= 0) or a categorical draw from softmax(logits / T), on device."""
+def sample(logits, V, temperature, seed, step, rep, out, nseq, step_dev=None):
+    """Greedy argmax (temperature <= 0) or a categorical draw from softmax(logits / T), on device.  With
+    ``step_dev`` (three int32 words on the device: step number, low and high half of the seed) both are read
+    from device memory at launch time, so a captured step can be replayed with fresh random numbers."""
     if _use_reference(logits):
         return ref.sample(logits, V, temperature, seed, step, rep, out, nseq)
-    _call(_lib().kh_sample, 1, logits.data_ptr(), logits.stride(0), V, float(temperature), int(seed), int(step), rep,
-                          out.data_ptr(), nseq, _stream())
+    _call(_lib().kh_sample2, 1, logits.data_ptr(), logits.stride(0), V, float(temperature), int(seed), int(step),
+                           _p(step_dev), rep, out.data_ptr(), nseq, _stream())

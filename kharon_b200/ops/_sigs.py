@@ -65,6 +65,7 @@ _OPTIONAL = {
     "kh_paged_attn": (i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, i32, vp),
     "kh_gather_rows": (i32, vp, vp, vp, i32, i32, vp),
     "kh_copy_blocks": (i32, vp, vp, vp, i32, i32, long_, long_, vp),
+    "kh_sample2": (i32, vp, i32, i32, f32, C.c_uint64, i32, vp, i32, vp, i32, vp),
     "kh_sample": (i32, vp, i32, i32, f32, C.c_uint64, i32, i32, vp, i32, vp),
     "kh_flash_fwd": (i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp),
     "kh_flash_bwd": (i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp),

@@ -112,6 +112,30 @@ def test_tensor_core_prefill_of_fresh_prompts_matches_the_paged_kernel():
     assert ops.error_word() == 0
 
 
+def test_sampled_generation_from_captured_steps_matches_eager_launches():
+    """Temperature sampling replayed from CUDA graphs (step number and seed read from device memory) draws the
+    same tokens as eager launches, and a second generation with another seed differs."""
+    cfg = Config(2, 512, 8, 300, 96, 1)
+    m = GPT(cfg, "cuda", torch.bfloat16); m.init_weights(5); m.sync_bf16()
+    prompts = [[5, 17, 3, 9], [9, 1, 44, 23, 8, 61, 2], [70, 1], [3, 3, 3]]
+    outs = {}
+    for graphs in (False, True):
+        e = InferEngine(m, block_size=8, max_seqs=6, use_graphs=graphs)
+        e.set_sampling(1.0, 1234)
+        a, _, _ = e.generate(prompts, 16)
+        e.set_sampling(1.0, 99)
+        b, _, _ = e.generate(prompts, 16)
+        e.set_sampling(1.0, 1234)
+        e.step_no = 0
+        c, _, _ = e.generate(prompts, 16)
+        outs[graphs] = (a, b, c)
+        assert a != b and a == c
+        if graphs:
+            assert len(e.graphs) > 0
+    assert outs[False][0] == outs[True][0] and outs[False][1] == outs[True][1]
+    assert ops.error_word() == 0
+
+
 def test_sampler_and_gather_and_copy():
     torch.manual_seed(1)
     V, ld, n = 50257, 50304, 5
