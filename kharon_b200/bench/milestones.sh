@@ -48,12 +48,16 @@ m7_3d() { data; local SMALL="--layers 8 --kh-d 512 --heads 8 --seq 256 --mbatch 
           run 8 kharon_b200.pp_train $SMALL --tp 2 --dp 2 --M 16 --steps 40 --kh-log 20 --ckpt /tmp/m7ck --resume
           # the headline: 1.2B, TP2 x PP2 x ZeRO-1 DP2
           run 8 kharon_b200.pp_train --tp 2 --dp 2 --layers 24 --kh-d 2048 --heads 16 --seq 512 --mbatch 4 --M 8 \
-              --steps 200 --kh-log 50 --vocab 50257 --synthetic; }
+              --steps 200 --kh-log 50 --vocab 50257 --synthetic
+          # same, micro-batches travelling through the stages in pairs (identical math, larger kernels)
+          run 8 kharon_b200.pp_train --tp 2 --dp 2 --layers 24 --kh-d 2048 --heads 16 --seq 512 --mbatch 4 --M 8 \
+              --steps 200 --kh-log 50 --vocab 50257 --synthetic --pp-fuse 2; }
 m8_infer() { $PY -m pytest tests/test_infer_gpu.py -q -m gpu
              run 1 kharon_b200.bench_infer --layers 24 --d 1024 --heads 16 --vocab 50257 --seq 1024 --prompt 128 --new 256 --block 16 --bf16 1
              run 1 kharon_b200.bench_infer --layers 24 --d 2048 --heads 16 --vocab 50257 --seq 1024 --prompt 256 --new 256 --block 16 --bf16 1
              for B in 8 16 32 64; do run 1 kharon_b200.bench_infer --layers 24 --block $B --G 16 | grep "G=16:"; done
-             run 2 kharon_b200.bench_infer --layers 24 --tp 2; }
+             run 2 kharon_b200.bench_infer --layers 24 --tp 2; run 4 kharon_b200.bench_infer --layers 24 --tp 4
+             KHARON_PERSISTENT_DECODE=0 $PY -m kharon_b200.bench_infer --layers 24; }      # the five-kernel chain for comparison
 m9_grpo() { $PY -m pytest tests/test_grpo_cpu.py -q
             run 1 kharon_b200.grpo_train --layers 6 --d 512 --heads 8 --G 16 --prompts 32 --sft 200 --steps 400 --log 50 \
                 --lr 1e-3 --rllr 1e-4 --temp 0.7 --beta 0.02
