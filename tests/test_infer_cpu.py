@@ -115,3 +115,28 @@ def test_temperature_sampling_is_seeded(pair):
     b, _, _ = eng.generate_group(PROMPTS[1], 4, 6)
     assert a == b
     assert len({tuple(x) for x in a}) > 1        # samples differ from one another
+
+
+def test_fresh_prompt_detection_reads_the_step_metadata():
+    """The tensor-core prefill is taken only when every token of a step belongs to a prompt that is listed whole,
+    contiguously and from position 0 (and is long enough to be worth a launch)."""
+    import torch
+    from kharon_b200.infer import InferEngine
+    from kharon_b200.models import GPT, Config
+    m = GPT(Config(1, 32, 2, 64, 256, 1), "cpu", torch.float32)
+    m.init_weights(1)
+    e = InferEngine(m, block_size=8, max_seqs=4, max_tokens=400)
+    e.flash_prefill = True                     # (off on CPU; only the host-side test of the metadata is exercised)
+
+    def fill(segments):
+        pos, slot = [], []
+        for s_, (p0, n) in enumerate(segments):
+            pos += list(range(p0, p0 + n)); slot += [s_] * n
+        e.h_meta[e._o_pos:e._o_pos + len(pos)] = torch.tensor(pos, dtype=torch.int32)
+        e.h_meta[e._o_slot:e._o_slot + len(slot)] = torch.tensor(slot, dtype=torch.int32)
+        return len(pos), len(segments)
+
+    assert e._fresh_prompts(*fill([(0, 64), (0, 100), (0, 70)])) == [(0, 64), (64, 100), (164, 70)]
+    assert e._fresh_prompts(*fill([(0, 64), (5, 100)])) is None          # a chunk that continues a prompt
+    assert e._fresh_prompts(*fill([(0, 64), (0, 10)])) is None           # a short prompt
+    assert e._fresh_prompts(*fill([(7, 1), (9, 1)])) is None             # decode step
