@@ -18,9 +18,9 @@
 // streaming its 512-wide K slice of the 8 weight rows straight from global memory into registers
 // (sixteen 16-byte loads per lane in flight -- weights are read exactly once, so they bypass shared
 // memory), and a CTA works on 8 / S units at a time.  The activation rows come into shared memory
-// with one bulk copy per row (all in flight together, completion on an mbarrier) and are LayerNorm'ed
-// in place where the phase has one; rows are padded by 64 bytes so that fragment loads are
-// conflict-free.  The products run on the tensor cores as mma.sync m16n8k16 (G <= 32 rows are one or
+// either by plain loads past L1 (a handful of rows: one trip to L2, LayerNorm on the row held in
+// registers) or with one bulk copy per row (all in flight together, completion on an mbarrier, then
+// LayerNorm in place); rows are padded by 64 bytes so that fragment loads are conflict-free.  The products run on the tensor cores as mma.sync m16n8k16 (G <= 32 rows are one or
 // two m16 tiles: tcgen05's 128-row tiles, TMEM round trip and shared-memory operand staging are what
 // this kernel exists to avoid; the large-M GEMMs of training and prefill use them).  The K order inside
 // a 32-wide block is permuted identically for both operands so that every lane fetches 16 contiguous
