@@ -178,6 +178,19 @@ def test_pipeline_variants_match_single_process(mode):
     assert max(abs(a - b) for a, b in zip(last["losses"], ref_losses)) < 2e-5
 
 
+def test_paired_microbatches_on_the_3d_mesh_match_single_process():
+    """TP2 x PP2 x DP2 with micro-batches travelling through the stages in pairs: losses of the mesh equal the
+    single-process run on the concatenated batch (vocabulary-parallel head, ZeRO-1 and tied embedding included)."""
+    steps = 3
+    _, ref_losses = _single(steps, 2)
+    with tempfile.TemporaryDirectory() as d:
+        res = _launch(2, 2, 2, steps, d, "pp_fuse")
+    last = [r for r in res if r["coord"][1] == 1]
+    for s in range(steps):
+        vals = [r["losses"][s] for r in last if r["coord"][2] == 0]
+        assert len(vals) == 2 and abs(sum(vals) / len(vals) - ref_losses[s]) < 2e-5
+
+
 def test_deferred_weight_gradients_single_process():
     from kharon_b200.engine import TrainEngine
     out = {}
