@@ -299,7 +299,8 @@ def decode_numbers(device):
         out["G%d_tok_s" % G] = round(st["tokens_decoded"] * 1000.0 / best, 1)
         out["kv_ratio"] = round(G * seq / (st["blocks_peak"] * bs), 2)
         eng.close()
-    out["config"] = "L24 d1024 H16 V50257 prompt 128 new 256 block 16 bf16, 1 GPU, CUDA-graph decode steps, device sampler"
+    out["config"] = ("L24 d1024 H16 V50257 prompt 128 new 256 block 16 bf16, 1 GPU, CUDA-graph decode steps, device sampler; "
+                     "up to %d sequences a step is one persistent kernel" % (eng.persistent_max if eng.persistent else 0))
     return out
 
 
